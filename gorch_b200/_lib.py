@@ -1,0 +1,73 @@
+"""ctypes binding of libgorchcuda.so (the C ABI in include/gorch_cuda_shim.h).
+
+There is no fallback: if the shared library is missing or cannot be loaded,
+importing a symbol raises. The library is looked up in-tree only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libgorchcuda.so")
+
+# every symbol include/gorch_cuda_shim.h declares
+EXPORTS = [
+    "gorch_cuda_device_count", "gorch_cuda_create_ctx", "gorch_cuda_release",
+    "gorch_cuda_free_string", "gorch_cuda_sync", "gorch_cuda_set_stream",
+    "gorch_cuda_set_timing", "gorch_cuda_get_counters",
+    "gorch_cuda_buffer_alloc", "gorch_cuda_buffer_free", "gorch_cuda_buffer_length",
+    "gorch_cuda_buffer_device_ptr", "gorch_cuda_buffer_upload", "gorch_cuda_buffer_download",
+    "gorch_cuda_sample_host", "gorch_cuda_sample_dev", "gorch_cuda_sample_row",
+    "gorch_cuda_argmax_host", "gorch_cuda_argmax_dev",
+]
+
+
+class Counters(C.Structure):
+    _fields_ = [
+        ("sample_launches", C.c_uint64), ("argmax_launches", C.c_uint64), ("rows", C.c_uint64),
+        ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64), ("last_kernel_ms", C.c_float),
+    ]
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load libgorchcuda.so; raises RuntimeError when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m gorch_b200.build` "
+            "(there is no CPU fallback)")
+    L = C.CDLL(LIB_PATH)
+    p, i32, i64, f32, f64 = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_double
+    err = C.POINTER(C.c_void_p)
+    sig = {
+        "gorch_cuda_device_count": (i32, [C.POINTER(i32), err]),
+        "gorch_cuda_create_ctx": (p, [i32, err]),
+        "gorch_cuda_release": (None, [p]),
+        "gorch_cuda_free_string": (None, [p]),
+        "gorch_cuda_sync": (i32, [p, err]),
+        "gorch_cuda_set_stream": (i32, [p, p, err]),
+        "gorch_cuda_set_timing": (i32, [p, i32]),
+        "gorch_cuda_get_counters": (i32, [p, C.POINTER(Counters)]),
+        "gorch_cuda_buffer_alloc": (p, [p, C.c_uint64, err]),
+        "gorch_cuda_buffer_free": (None, [p]),
+        "gorch_cuda_buffer_length": (C.c_uint64, [p]),
+        "gorch_cuda_buffer_device_ptr": (p, [p]),
+        "gorch_cuda_buffer_upload": (i32, [p, C.c_uint64, p, C.c_uint64, err]),
+        "gorch_cuda_buffer_download": (i32, [p, C.c_uint64, p, C.c_uint64, err]),
+        "gorch_cuda_sample_host": (i32, [p, p, i32, i64, i64, i64, p, p, p, p, err]),
+        "gorch_cuda_sample_dev": (i32, [p, p, i32, i64, i64, i64, p, p, p, p, p, p, err]),
+        "gorch_cuda_sample_row": (i64, [p, p, i64, f32, i64, f32, i32, f64, C.POINTER(C.c_uint32), err]),
+        "gorch_cuda_argmax_host": (i32, [p, p, i32, i64, i64, i64, p, err]),
+        "gorch_cuda_argmax_dev": (i32, [p, p, i32, i64, i64, i64, p, err]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(L, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = L
+    return L

@@ -1,0 +1,427 @@
+// libgorchcuda.so: implementation of include/gorch_cuda_shim.h.
+//
+// Host-side conventions mirror the reference's Metal shim (metal/shim.m):
+// opaque handles, strdup'd error strings, int return codes, a blocking default.
+// There is no CPU fallback anywhere in this file: every entry point either
+// runs the CUDA kernels or returns an error.
+
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <limits>
+#include <new>
+
+#include "../../include/gorch_cuda_shim.h"
+#include "sample_kernel.cuh"
+
+namespace {
+
+struct Buffer {
+  int device;
+  void* ptr;
+  uint64_t bytes;
+};
+
+struct Scratch {  // grow-only device allocation
+  void* ptr = nullptr;
+  size_t cap = 0;
+};
+
+struct Ctx {
+  int device = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  double* exp_table = nullptr;
+  Scratch st_logits, st_cfgs, st_uniforms, st_ids, st_flags;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  int timing = 0;
+  GorchCudaCounters counters{};
+};
+
+void set_err(char** errOut, const char* fmt, ...) {
+  if (!errOut) return;
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  *errOut = strdup(buf);
+}
+
+#define CUDA_TRY(expr, errOut)                                                   \
+  do {                                                                           \
+    cudaError_t e__ = (expr);                                                    \
+    if (e__ != cudaSuccess) {                                                    \
+      set_err(errOut, "%s failed: %s", #expr, cudaGetErrorString(e__));          \
+      return GORCH_CUDA_ERR_CUDA;                                                \
+    }                                                                            \
+  } while (0)
+
+int ensure(Scratch& s, size_t bytes, char** errOut) {
+  if (bytes <= s.cap) return GORCH_CUDA_OK;
+  if (s.ptr) {
+    CUDA_TRY(cudaFree(s.ptr), errOut);
+    s.ptr = nullptr;
+    s.cap = 0;
+  }
+  size_t want = bytes + (bytes >> 3);
+  cudaError_t e = cudaMalloc(&s.ptr, want);
+  if (e != cudaSuccess) {
+    want = bytes;
+    e = cudaMalloc(&s.ptr, want);
+  }
+  if (e != cudaSuccess) {
+    s.ptr = nullptr;
+    set_err(errOut, "cudaMalloc(%zu bytes) failed: %s", bytes, cudaGetErrorString(e));
+    return GORCH_CUDA_ERR_CUDA;
+  }
+  s.cap = want;
+  return GORCH_CUDA_OK;
+}
+
+int check_shape(int dtype, int64_t B, int64_t V, int64_t row_stride, char** errOut) {
+  if (dtype != GORCH_CUDA_F32 && dtype != GORCH_CUDA_BF16) {
+    set_err(errOut, "gorch_cuda: unknown dtype %d", dtype);
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  if (B < 0 || V < 1 || row_stride < V) {
+    set_err(errOut, "gorch_cuda: bad shape B=%lld V=%lld row_stride=%lld", (long long)B,
+            (long long)V, (long long)row_stride);
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  if (V > 0x7fffff00ll || B > 0x7fffffffll) {
+    set_err(errOut, "gorch_cuda: shape beyond 31-bit row / batch limit");
+    return GORCH_CUDA_ERR_LIMIT;
+  }
+  return GORCH_CUDA_OK;
+}
+
+size_t elem_size(int dtype) { return dtype == GORCH_CUDA_BF16 ? 2 : 4; }
+
+int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int64_t row_stride,
+                const GorchSampleCfg* cfgs, const double* uniforms, int32_t* out_ids,
+                uint32_t* out_flags, double* out_probs, GorchSampleDebug* out_debug,
+                int force_greedy, char** errOut) {
+  if (B == 0) return GORCH_CUDA_OK;
+  static_assert(sizeof(GorchSampleCfg) == sizeof(gs::RowCfg), "cfg layout");
+  static_assert(sizeof(GorchSampleDebug) == sizeof(gs::RowDebug), "debug layout");
+  if ((reinterpret_cast<uintptr_t>(logits) % elem_size(dtype)) != 0) {
+    set_err(errOut, "gorch_cuda: logits pointer not aligned to its element size");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  gs::KernelArgs a;
+  a.logits = logits;
+  a.row_stride = row_stride;
+  a.V = static_cast<int32_t>(V);
+  a.force_greedy = force_greedy;
+  a.cfgs = reinterpret_cast<const gs::RowCfg*>(cfgs);
+  a.uniforms = uniforms;
+  a.out_ids = out_ids;
+  a.out_flags = out_flags;
+  a.out_probs = out_probs;
+  a.out_debug = reinterpret_cast<gs::RowDebug*>(out_debug);
+  a.exp_table = c->exp_table;
+  a.row_offset = 0;
+  if (c->timing) CUDA_TRY(cudaEventRecord(c->ev0, c->stream), errOut);
+  dim3 grid(static_cast<unsigned>(B)), block(gs::NT);
+  if (dtype == GORCH_CUDA_F32) {
+    gs::sample_rows_kernel<float><<<grid, block, gs::POOL_BYTES, c->stream>>>(a);
+  } else {
+    gs::sample_rows_kernel<uint16_t><<<grid, block, gs::POOL_BYTES, c->stream>>>(a);
+  }
+  CUDA_TRY(cudaGetLastError(), errOut);
+  if (force_greedy) c->counters.argmax_launches++; else c->counters.sample_launches++;
+  c->counters.rows += static_cast<uint64_t>(B);
+  if (c->timing) {
+    CUDA_TRY(cudaEventRecord(c->ev1, c->stream), errOut);
+    CUDA_TRY(cudaEventSynchronize(c->ev1), errOut);
+    CUDA_TRY(cudaEventElapsedTime(&c->counters.last_kernel_ms, c->ev0, c->ev1), errOut);
+  }
+  return GORCH_CUDA_OK;
+}
+
+int validate_host_cfgs(const GorchSampleCfg* cfgs, int64_t B, char** errOut) {
+  for (int64_t b = 0; b < B; b++) {
+    float t = cfgs[b].temperature;
+    if (!(t >= 0.0f) || !(t < std::numeric_limits<float>::infinity())) {
+      set_err(errOut, "gorch_cuda: row %lld temperature %g is negative, NaN or infinite",
+              (long long)b, (double)t);
+      return GORCH_CUDA_ERR_BAD_ARG;
+    }
+    if (cfgs[b].topp_mode != GORCH_TOPP_MODE_A && cfgs[b].topp_mode != GORCH_TOPP_MODE_B) {
+      set_err(errOut, "gorch_cuda: row %lld unknown topp_mode %d", (long long)b, cfgs[b].topp_mode);
+      return GORCH_CUDA_ERR_BAD_ARG;
+    }
+  }
+  return GORCH_CUDA_OK;
+}
+
+int host_run(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int64_t row_stride,
+             const GorchSampleCfg* cfgs, const double* uniforms, int32_t* out_ids,
+             uint32_t* out_flags, int force_greedy, char** errOut) {
+  int rc = check_shape(dtype, B, V, row_stride, errOut);
+  if (rc) return rc;
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!logits || !out_ids || (!force_greedy && (!cfgs || !uniforms))) {
+    set_err(errOut, "gorch_cuda: null pointer argument");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  if (!force_greedy) {
+    rc = validate_host_cfgs(cfgs, B, errOut);
+    if (rc) return rc;
+  }
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  const size_t es = elem_size(dtype);
+  const size_t lbytes = (static_cast<size_t>(B - 1) * row_stride + V) * es;
+  if ((rc = ensure(c->st_logits, lbytes, errOut))) return rc;
+  if ((rc = ensure(c->st_ids, B * sizeof(int32_t), errOut))) return rc;
+  if ((rc = ensure(c->st_flags, B * sizeof(uint32_t), errOut))) return rc;
+  CUDA_TRY(cudaMemcpyAsync(c->st_logits.ptr, logits, lbytes, cudaMemcpyHostToDevice, c->stream), errOut);
+  c->counters.h2d_bytes += lbytes;
+  if (!force_greedy) {
+    if ((rc = ensure(c->st_cfgs, B * sizeof(GorchSampleCfg), errOut))) return rc;
+    if ((rc = ensure(c->st_uniforms, B * sizeof(double), errOut))) return rc;
+    CUDA_TRY(cudaMemcpyAsync(c->st_cfgs.ptr, cfgs, B * sizeof(GorchSampleCfg), cudaMemcpyHostToDevice, c->stream), errOut);
+    CUDA_TRY(cudaMemcpyAsync(c->st_uniforms.ptr, uniforms, B * sizeof(double), cudaMemcpyHostToDevice, c->stream), errOut);
+    c->counters.h2d_bytes += B * (sizeof(GorchSampleCfg) + sizeof(double));
+  }
+  rc = launch_rows(c, c->st_logits.ptr, dtype, B, V, row_stride,
+                   static_cast<const GorchSampleCfg*>(c->st_cfgs.ptr),
+                   static_cast<const double*>(c->st_uniforms.ptr),
+                   static_cast<int32_t*>(c->st_ids.ptr), static_cast<uint32_t*>(c->st_flags.ptr),
+                   nullptr, nullptr, force_greedy, errOut);
+  if (rc) return rc;
+  CUDA_TRY(cudaMemcpyAsync(out_ids, c->st_ids.ptr, B * sizeof(int32_t), cudaMemcpyDeviceToHost, c->stream), errOut);
+  c->counters.d2h_bytes += B * sizeof(int32_t);
+  if (out_flags) {
+    CUDA_TRY(cudaMemcpyAsync(out_flags, c->st_flags.ptr, B * sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream), errOut);
+    c->counters.d2h_bytes += B * sizeof(uint32_t);
+  }
+  CUDA_TRY(cudaStreamSynchronize(c->stream), errOut);
+  return GORCH_CUDA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int gorch_cuda_device_count(int* count, char** errOut) {
+  if (!count) { set_err(errOut, "gorch_cuda: null count"); return GORCH_CUDA_ERR_BAD_ARG; }
+  CUDA_TRY(cudaGetDeviceCount(count), errOut);
+  return GORCH_CUDA_OK;
+}
+
+GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n <= 0) {
+    set_err(errOut, "gorch_cuda: no CUDA device (%s)", cudaGetErrorString(e));
+    return nullptr;
+  }
+  if (device < 0 || device >= n) {
+    set_err(errOut, "gorch_cuda: device %d out of range [0,%d)", device, n);
+    return nullptr;
+  }
+  Ctx* c = new (std::nothrow) Ctx();
+  if (!c) { set_err(errOut, "gorch_cuda: out of host memory"); return nullptr; }
+  c->device = device;
+  auto fail = [&](const char* what, cudaError_t err) -> GorchCudaCtxRef {
+    set_err(errOut, "gorch_cuda: %s failed: %s", what, cudaGetErrorString(err));
+    gorch_cuda_release(c);
+    return nullptr;
+  };
+  if ((e = cudaSetDevice(device)) != cudaSuccess) return fail("cudaSetDevice", e);
+  cudaDeviceProp prop;
+  if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) return fail("cudaGetDeviceProperties", e);
+  if (prop.major < 10) {
+    set_err(errOut, "gorch_cuda: device %d is sm_%d%d; this library is built for sm_100a only",
+            device, prop.major, prop.minor);
+    gorch_cuda_release(c);
+    return nullptr;
+  }
+  if ((e = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking)) != cudaSuccess) return fail("cudaStreamCreate", e);
+  c->stream = c->own_stream;
+  if ((e = cudaEventCreate(&c->ev0)) != cudaSuccess) return fail("cudaEventCreate", e);
+  if ((e = cudaEventCreate(&c->ev1)) != cudaSuccess) return fail("cudaEventCreate", e);
+  double tab[256];
+  for (int j = 0; j < 256; j++) tab[j] = static_cast<double>(exp2l(static_cast<long double>(j) / 256.0L));
+  if ((e = cudaMalloc(&c->exp_table, sizeof tab)) != cudaSuccess) return fail("cudaMalloc(exp table)", e);
+  if ((e = cudaMemcpy(c->exp_table, tab, sizeof tab, cudaMemcpyHostToDevice)) != cudaSuccess) return fail("cudaMemcpy(exp table)", e);
+  if ((e = cudaFuncSetAttribute(gs::sample_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::POOL_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::sample_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::POOL_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  return c;
+}
+
+void gorch_cuda_release(GorchCudaCtxRef ctx) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) return;
+  cudaSetDevice(c->device);
+  if (c->own_stream) { cudaStreamSynchronize(c->own_stream); }
+  for (Scratch* s : {&c->st_logits, &c->st_cfgs, &c->st_uniforms, &c->st_ids, &c->st_flags}) {
+    if (s->ptr) cudaFree(s->ptr);
+  }
+  if (c->exp_table) cudaFree(c->exp_table);
+  if (c->ev0) cudaEventDestroy(c->ev0);
+  if (c->ev1) cudaEventDestroy(c->ev1);
+  if (c->own_stream) cudaStreamDestroy(c->own_stream);
+  delete c;
+}
+
+void gorch_cuda_free_string(char* s) { free(s); }
+
+int gorch_cuda_sync(GorchCudaCtxRef ctx, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  CUDA_TRY(cudaStreamSynchronize(c->stream), errOut);
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_set_stream(GorchCudaCtxRef ctx, void* stream, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  c->stream = stream ? static_cast<cudaStream_t>(stream) : c->own_stream;
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_set_timing(GorchCudaCtxRef ctx, int on) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) return GORCH_CUDA_ERR_BAD_ARG;
+  c->timing = on ? 1 : 0;
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_get_counters(GorchCudaCtxRef ctx, GorchCudaCounters* out) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c || !out) return GORCH_CUDA_ERR_BAD_ARG;
+  *out = c->counters;
+  return GORCH_CUDA_OK;
+}
+
+GorchCudaBufferRef gorch_cuda_buffer_alloc(GorchCudaCtxRef ctx, uint64_t bytes, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return nullptr; }
+  Buffer* b = new (std::nothrow) Buffer{c->device, nullptr, bytes};
+  if (!b) { set_err(errOut, "gorch_cuda: out of host memory"); return nullptr; }
+  cudaError_t e = cudaSetDevice(c->device);
+  if (e == cudaSuccess) e = cudaMalloc(&b->ptr, bytes ? bytes : 1);
+  if (e != cudaSuccess) {
+    set_err(errOut, "gorch_cuda: cudaMalloc(%llu) failed: %s", (unsigned long long)bytes, cudaGetErrorString(e));
+    delete b;
+    return nullptr;
+  }
+  return b;
+}
+
+void gorch_cuda_buffer_free(GorchCudaBufferRef buf) {
+  Buffer* b = static_cast<Buffer*>(buf);
+  if (!b) return;
+  cudaSetDevice(b->device);
+  cudaFree(b->ptr);
+  delete b;
+}
+
+uint64_t gorch_cuda_buffer_length(GorchCudaBufferRef buf) {
+  Buffer* b = static_cast<Buffer*>(buf);
+  return b ? b->bytes : 0;
+}
+
+void* gorch_cuda_buffer_device_ptr(GorchCudaBufferRef buf) {
+  Buffer* b = static_cast<Buffer*>(buf);
+  return b ? b->ptr : nullptr;
+}
+
+int gorch_cuda_buffer_upload(GorchCudaBufferRef buf, uint64_t offset, const void* host,
+                             uint64_t bytes, char** errOut) {
+  Buffer* b = static_cast<Buffer*>(buf);
+  if (!b || (!host && bytes) || offset > b->bytes || bytes > b->bytes - offset) {
+    set_err(errOut, "gorch_cuda: upload out of range");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  CUDA_TRY(cudaSetDevice(b->device), errOut);
+  CUDA_TRY(cudaMemcpy(static_cast<char*>(b->ptr) + offset, host, bytes, cudaMemcpyHostToDevice), errOut);
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_buffer_download(GorchCudaBufferRef buf, uint64_t offset, void* host,
+                               uint64_t bytes, char** errOut) {
+  Buffer* b = static_cast<Buffer*>(buf);
+  if (!b || (!host && bytes) || offset > b->bytes || bytes > b->bytes - offset) {
+    set_err(errOut, "gorch_cuda: download out of range");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  CUDA_TRY(cudaSetDevice(b->device), errOut);
+  CUDA_TRY(cudaMemcpy(host, static_cast<char*>(b->ptr) + offset, bytes, cudaMemcpyDeviceToHost), errOut);
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_sample_host(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                           int64_t V, int64_t row_stride, const GorchSampleCfg* cfgs,
+                           const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
+                           char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  return host_run(c, logits, dtype, B, V, row_stride, cfgs, uniforms, out_ids, out_flags, 0, errOut);
+}
+
+int gorch_cuda_sample_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                          int64_t V, int64_t row_stride, const GorchSampleCfg* cfgs,
+                          const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
+                          double* out_probs, GorchSampleDebug* out_debug, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = check_shape(dtype, B, V, row_stride, errOut);
+  if (rc) return rc;
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!logits || !cfgs || !uniforms || !out_ids) {
+    set_err(errOut, "gorch_cuda: null pointer argument");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  return launch_rows(c, logits, dtype, B, V, row_stride, cfgs, uniforms, out_ids, out_flags,
+                     out_probs, out_debug, 0, errOut);
+}
+
+int64_t gorch_cuda_sample_row(GorchCudaCtxRef ctx, const float* logits, int64_t n,
+                              float temperature, int64_t top_k, float top_p, int topp_mode,
+                              double uniform, uint32_t* out_flag, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return -1; }
+  GorchSampleCfg cfg;
+  cfg.temperature = temperature;
+  // the reference takes a Go int; anything outside (0, n) disables top-k (generate.go:157)
+  cfg.top_k = (top_k > 0 && top_k < n) ? static_cast<int32_t>(top_k) : 0;
+  cfg.top_p = top_p;
+  cfg.topp_mode = topp_mode;
+  int32_t id = -1;
+  uint32_t flag = 0;
+  int rc = host_run(c, logits, GORCH_CUDA_F32, 1, n, n, &cfg, &uniform, &id, &flag, 0, errOut);
+  if (rc) return -1;
+  if (out_flag) *out_flag = flag;
+  return id;
+}
+
+int gorch_cuda_argmax_host(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                           int64_t V, int64_t row_stride, int32_t* out_ids, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  return host_run(c, logits, dtype, B, V, row_stride, nullptr, nullptr, out_ids, nullptr, 1, errOut);
+}
+
+int gorch_cuda_argmax_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                          int64_t V, int64_t row_stride, int32_t* out_ids, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = check_shape(dtype, B, V, row_stride, errOut);
+  if (rc) return rc;
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!logits || !out_ids) { set_err(errOut, "gorch_cuda: null pointer argument"); return GORCH_CUDA_ERR_BAD_ARG; }
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  return launch_rows(c, logits, dtype, B, V, row_stride, nullptr, nullptr, out_ids, nullptr,
+                     nullptr, nullptr, 1, errOut);
+}
+
+}  // extern "C"

@@ -1,0 +1,317 @@
+"""Host-side mirror of the reference's sampling interface over libgorchcuda.so.
+
+Names and argument meaning follow the reference:
+  argmax(logits)                       model/generate.go:134-144
+  sample(logits, T, topK, topP)        model/generate.go:147-240 (mode A)
+  sampleLogits(..., rng)               model/qwen/generate.go:92-164 (mode B)
+  GenerateWithConfig / generateCached  model/generate.go:52-131
+  qwen.Generate                        model/qwen/generate.go:35-65
+with one difference the reference cannot express: the uniform is an argument
+(the reference calls rand.Float64() inside, generate.go:231).
+
+Everything here calls the CUDA library; there is no CPU path. A missing
+library or a machine without a B200-class GPU raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from .config import (CFG_DTYPE, DTYPE_BF16, DTYPE_F32, MODE_A, MODE_B, GenerateConfig,
+                     QwenGenerateConfig)
+
+DEBUG_DTYPE = np.dtype(
+    [("sum_exp", "<f8"), ("resum", "<f8"), ("edge_lo", "<f8"), ("edge_hi", "<f8"),
+     ("kept", "<i4"), ("max_scaled", "<f4"), ("threshold", "<f4"), ("path", "<i4")]
+)
+
+
+class GorchCudaError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"gorch_cuda error {code}: {message}")
+        self.code = code
+
+
+def _take_err(lib, err: C.c_void_p) -> str:
+    if not err.value:
+        return ""
+    msg = C.string_at(err.value).decode("utf-8", "replace")
+    lib.gorch_cuda_free_string(err)
+    return msg
+
+
+def _check(lib, rc: int, err: C.c_void_p) -> None:
+    if rc != 0:
+        raise GorchCudaError(rc, _take_err(lib, err))
+
+
+def _logits_arg(logits: np.ndarray):
+    x = np.ascontiguousarray(logits)
+    if x.dtype == np.uint16:
+        return x, DTYPE_BF16
+    if x.dtype != np.float32:
+        x = x.astype(np.float32)
+    return x, DTYPE_F32
+
+
+class CudaSampler:
+    """One device context (cf. metal.NewDevice, metal/metal.go:228-234): a
+    device, a stream and grow-only staging buffers."""
+
+    def __init__(self, device: int = 0):
+        self._lib = _lib.load()
+        err = C.c_void_p()
+        self._ctx = self._lib.gorch_cuda_create_ctx(int(device), C.byref(err))
+        if not self._ctx:
+            raise GorchCudaError(2, _take_err(self._lib, err))
+        self.device = int(device)
+
+    def release(self) -> None:
+        if getattr(self, "_ctx", None):
+            self._lib.gorch_cuda_release(self._ctx)
+            self._ctx = None
+
+    close = release
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.release()
+
+    # ---- plumbing
+    def sync(self) -> None:
+        err = C.c_void_p()
+        _check(self._lib, self._lib.gorch_cuda_sync(self._ctx, C.byref(err)), err)
+
+    def set_stream(self, stream_handle: int | None) -> None:
+        err = C.c_void_p()
+        _check(self._lib, self._lib.gorch_cuda_set_stream(self._ctx, stream_handle or None, C.byref(err)), err)
+
+    def set_timing(self, on: bool) -> None:
+        self._lib.gorch_cuda_set_timing(self._ctx, 1 if on else 0)
+
+    def counters(self) -> dict:
+        c = _lib.Counters()
+        self._lib.gorch_cuda_get_counters(self._ctx, C.byref(c))
+        return {name: getattr(c, name) for name, _ in c._fields_}
+
+    # ---- the sampling step, host memory in and out
+    def sample_batch(self, logits, cfgs, uniforms, want_flags: bool = True):
+        """[B,V] logits (float32, or uint16 bf16 bit patterns), per-row cfgs
+        (CFG_DTYPE) and uniforms -> (ids int32[B], flags uint32[B])."""
+        x, dtype = _logits_arg(logits)
+        if x.ndim != 2:
+            raise ValueError("logits must be [B,V]")
+        B, V = x.shape
+        cfgs = np.ascontiguousarray(cfgs, dtype=CFG_DTYPE)
+        uniforms = np.ascontiguousarray(uniforms, dtype=np.float64)
+        if cfgs.shape != (B,) or uniforms.shape != (B,):
+            raise ValueError("cfgs and uniforms must have one entry per row")
+        ids = np.empty(B, dtype=np.int32)
+        flags = np.zeros(B, dtype=np.uint32)
+        err = C.c_void_p()
+        rc = self._lib.gorch_cuda_sample_host(
+            self._ctx, x.ctypes.data, dtype, B, V, V, cfgs.ctypes.data, uniforms.ctypes.data,
+            ids.ctypes.data, flags.ctypes.data if want_flags else None, C.byref(err))
+        _check(self._lib, rc, err)
+        return ids, flags
+
+    def sample_host_ptrs(self, logits_ptr: int, dtype: int, B: int, V: int, row_stride: int,
+                         cfgs_ptr: int, uniforms_ptr: int, ids_ptr: int, flags_ptr: int | None):
+        """Raw-pointer form of sample_batch for callers that manage (pinned) host memory."""
+        err = C.c_void_p()
+        rc = self._lib.gorch_cuda_sample_host(self._ctx, logits_ptr, dtype, B, V, row_stride,
+                                              cfgs_ptr, uniforms_ptr, ids_ptr, flags_ptr,
+                                              C.byref(err))
+        _check(self._lib, rc, err)
+
+    def sample_dev_ptrs(self, logits_ptr: int, dtype: int, B: int, V: int, row_stride: int,
+                        cfgs_ptr: int, uniforms_ptr: int, ids_ptr: int, flags_ptr: int | None = None,
+                        probs_ptr: int | None = None, debug_ptr: int | None = None) -> None:
+        """Device pointers in and out; asynchronous on the context's stream."""
+        err = C.c_void_p()
+        rc = self._lib.gorch_cuda_sample_dev(self._ctx, logits_ptr, dtype, B, V, row_stride,
+                                             cfgs_ptr, uniforms_ptr, ids_ptr, flags_ptr,
+                                             probs_ptr, debug_ptr, C.byref(err))
+        _check(self._lib, rc, err)
+
+    # ---- device buffers (cf. metal Buffer, metal/metal.go:357-422)
+    def _buf(self, nbytes: int) -> int:
+        err = C.c_void_p()
+        b = self._lib.gorch_cuda_buffer_alloc(self._ctx, int(nbytes), C.byref(err))
+        if not b:
+            raise GorchCudaError(2, _take_err(self._lib, err))
+        return b
+
+    def _upload(self, buf: int, arr: np.ndarray) -> None:
+        err = C.c_void_p()
+        _check(self._lib, self._lib.gorch_cuda_buffer_upload(buf, 0, arr.ctypes.data, arr.nbytes, C.byref(err)), err)
+
+    def _download(self, buf: int, arr: np.ndarray) -> None:
+        err = C.c_void_p()
+        _check(self._lib, self._lib.gorch_cuda_buffer_download(buf, 0, arr.ctypes.data, arr.nbytes, C.byref(err)), err)
+
+    def sample_batch_debug(self, logits, cfgs, uniforms, want_probs: bool = True,
+                           pad_elems: int = 0):
+        """sample_batch through the device-pointer entry point, also returning the
+        dense final probabilities [B,V] (float64) and the per-row debug records.
+        `pad_elems` places the logits that many elements into their buffer, to
+        exercise rows that do not start on a 16-byte boundary."""
+        x, dtype = _logits_arg(logits)
+        B, V = x.shape
+        cfgs = np.ascontiguousarray(cfgs, dtype=CFG_DTYPE)
+        uniforms = np.ascontiguousarray(uniforms, dtype=np.float64)
+        ids = np.empty(B, dtype=np.int32)
+        flags = np.zeros(B, dtype=np.uint32)
+        dbg = np.zeros(B, dtype=DEBUG_DTYPE)
+        probs = np.empty((B, V), dtype=np.float64) if want_probs else None
+        pad_bytes = pad_elems * x.itemsize
+        staged = np.zeros(pad_bytes + x.nbytes, dtype=np.uint8)
+        staged[pad_bytes:] = x.view(np.uint8).reshape(-1)
+        bufs = []
+        try:
+            b_log = self._buf(staged.nbytes); bufs.append(b_log)
+            b_cfg = self._buf(cfgs.nbytes); bufs.append(b_cfg)
+            b_uni = self._buf(uniforms.nbytes); bufs.append(b_uni)
+            b_ids = self._buf(ids.nbytes); bufs.append(b_ids)
+            b_flg = self._buf(flags.nbytes); bufs.append(b_flg)
+            b_dbg = self._buf(dbg.nbytes); bufs.append(b_dbg)
+            b_prb = None
+            if want_probs:
+                b_prb = self._buf(probs.nbytes); bufs.append(b_prb)
+            self._upload(b_log, staged)
+            self._upload(b_cfg, cfgs)
+            self._upload(b_uni, uniforms)
+            ptr = self._lib.gorch_cuda_buffer_device_ptr
+            self.sample_dev_ptrs(ptr(b_log) + pad_bytes, dtype, B, V, V, ptr(b_cfg), ptr(b_uni),
+                                 ptr(b_ids), ptr(b_flg), ptr(b_prb) if want_probs else None,
+                                 ptr(b_dbg))
+            self.sync()
+            self._download(b_ids, ids)
+            self._download(b_flg, flags)
+            self._download(b_dbg, dbg)
+            if want_probs:
+                self._download(b_prb, probs)
+        finally:
+            for b in bufs:
+                self._lib.gorch_cuda_buffer_free(b)
+        return {"ids": ids, "flags": flags, "debug": dbg, "probs": probs}
+
+    def argmax_batch(self, logits) -> np.ndarray:
+        x, dtype = _logits_arg(logits)
+        B, V = x.shape
+        ids = np.empty(B, dtype=np.int32)
+        err = C.c_void_p()
+        rc = self._lib.gorch_cuda_argmax_host(self._ctx, x.ctypes.data, dtype, B, V, V,
+                                              ids.ctypes.data, C.byref(err))
+        _check(self._lib, rc, err)
+        return ids
+
+    def argmax_dev_ptrs(self, logits_ptr: int, dtype: int, B: int, V: int, row_stride: int,
+                        ids_ptr: int) -> None:
+        err = C.c_void_p()
+        rc = self._lib.gorch_cuda_argmax_dev(self._ctx, logits_ptr, dtype, B, V, row_stride,
+                                             ids_ptr, C.byref(err))
+        _check(self._lib, rc, err)
+
+    # ---- the reference's scalar call shapes
+    def argmax(self, logits) -> int:
+        """argmax(logits []float32) int  (model/generate.go:134)."""
+        x = np.ascontiguousarray(logits, dtype=np.float32).reshape(1, -1)
+        return int(self.argmax_batch(x)[0])
+
+    def sample(self, logits, temperature: float, top_k: int, top_p: float, u: float,
+               mode: int = MODE_A, return_flag: bool = False):
+        """sample(logits, temperature, topK, topP) int  (model/generate.go:147),
+        `u` standing in for rand.Float64()."""
+        x = np.ascontiguousarray(logits, dtype=np.float32).reshape(-1)
+        flag = C.c_uint32(0)
+        err = C.c_void_p()
+        tok = self._lib.gorch_cuda_sample_row(self._ctx, x.ctypes.data, x.size, float(temperature),
+                                              int(top_k), float(top_p), int(mode), float(u),
+                                              C.byref(flag), C.byref(err))
+        if tok < 0:
+            raise GorchCudaError(1, _take_err(self._lib, err))
+        return (int(tok), int(flag.value)) if return_flag else int(tok)
+
+    def sample_logits(self, logits, temperature, top_k, top_p, u, return_flag: bool = False):
+        """sampleLogits (model/qwen/generate.go:92): the true-nucleus flavour."""
+        return self.sample(logits, temperature, top_k, top_p, u, MODE_B, return_flag)
+
+    def next_token(self, last_logits, cfg, u: float) -> int:
+        """The branch at model/generate.go:75-79 / qwen/generate.go:49-53."""
+        if cfg.temperature == 0:
+            return self.argmax(last_logits)
+        return self.sample(last_logits, cfg.temperature, cfg.top_k, cfg.top_p, u, cfg.topp_mode)
+
+
+def generate_with_config(model, token_ids, cfg: GenerateConfig, uniforms, sampler) -> list:
+    """GenerateWithConfig (model/generate.go:52-90) and generateCached (:94-131).
+
+    `model` provides max_seq, vocab_size, forward(ids) -> [len, V] logits and,
+    for cfg.use_kv_cache, new_cache() / forward_cached(ids, cache) -> logits and
+    cache.len(). `uniforms` yields the values the reference would draw from
+    math/rand, one per sampled step. `sampler` is a CudaSampler."""
+    uni = iter(uniforms)
+    result = list(token_ids)
+    if cfg.use_kv_cache:
+        cache = model.new_cache()
+        if len(result) > model.max_seq:
+            result = result[len(result) - model.max_seq:]
+        logits = np.asarray(model.forward_cached(result, cache), dtype=np.float32)
+        last = logits.reshape(-1, model.vocab_size)[len(result) - 1]
+        for _ in range(cfg.max_new_tokens):
+            nxt = sampler.next_token(last, cfg, 0.0 if cfg.temperature == 0 else next(uni))
+            if cfg.stop_token >= 0 and nxt == cfg.stop_token:
+                break
+            result.append(nxt)
+            if cache.len() >= model.max_seq:
+                break
+            step = np.asarray(model.forward_cached([nxt], cache), dtype=np.float32)
+            last = step.reshape(-1)[: model.vocab_size]
+        return result
+    for _ in range(cfg.max_new_tokens):
+        inp = result
+        if len(inp) > model.max_seq:
+            inp = inp[len(inp) - model.max_seq:]
+        logits = np.asarray(model.forward(inp), dtype=np.float32).reshape(-1, model.vocab_size)
+        last = logits[len(inp) - 1]
+        nxt = sampler.next_token(last, cfg, 0.0 if cfg.temperature == 0 else next(uni))
+        if cfg.stop_token >= 0 and nxt == cfg.stop_token:
+            break
+        result.append(nxt)
+    return result
+
+
+def qwen_generate(model, prompt, cfg: QwenGenerateConfig, sampler, uniforms=None) -> list:
+    """qwen.Generate (model/qwen/generate.go:35-65). `model` provides
+    new_cache(), forward_cached(ids, cache) -> (1,V) logits, max_seq.
+    uniforms default to numpy's default_rng(cfg.seed) stream (the reference
+    seeds math/rand with cfg.Seed, :42; that generator is not reproduced)."""
+    if len(prompt) == 0:
+        raise ValueError("qwen: empty prompt")   # generate.go:36-38 panics
+    if uniforms is None:
+        rng = np.random.default_rng(cfg.seed)
+        uniforms = (float(rng.random()) for _ in iter(int, 1))
+    uni = iter(uniforms)
+    result = list(prompt)
+    cache = model.new_cache()
+    last = np.asarray(model.forward_cached(list(prompt), cache), dtype=np.float32).reshape(-1)
+    for _ in range(cfg.max_new_tokens):
+        nxt = sampler.next_token(last, cfg, 0.0 if cfg.temperature == 0 else next(uni))
+        if nxt in cfg.stop_tokens:
+            break
+        result.append(nxt)
+        if cache.len() >= model.max_seq:
+            break
+        last = np.asarray(model.forward_cached([nxt], cache), dtype=np.float32).reshape(-1)
+    return result

@@ -1,0 +1,164 @@
+/* gorch CUDA shim: the C ABI of libgorchcuda.so.
+ *
+ * A third backend package next to the reference's metal/ and accelerate/
+ * shims, for ONE path: the decode-time sampling step that
+ * model.GenerateWithConfig / generateCached (model/generate.go:71-79,
+ * :105-113) and qwen.Generate (model/qwen/generate.go:47-53) apply to LM-head
+ * logits. Conventions follow metal/shim.h: opaque void* handles
+ * (metal/shim.h:8-13), create/release pairs (:16-17, :230-231), NULL or a
+ * non-zero int on failure with a strdup'd message through char** errOut
+ * (:30-35) that the caller frees (:233-234), a blocking default with an
+ * explicit sync for the asynchronous forms (:209-228). Plain C, no C++ types.
+ *
+ * Threading: one stream per context; calls on one context are not
+ * concurrent (metal/shim.h:223-224). Contexts on different devices are
+ * independent.
+ */
+#ifndef GORCH_CUDA_SHIM_H
+#define GORCH_CUDA_SHIM_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* GorchCudaCtxRef;    /* device + stream + scratch; cf. MTLDeviceRef/MTLCommandQueueRef */
+typedef void* GorchCudaBufferRef; /* device allocation; cf. MTLBufferRef */
+
+/* Return codes (0 = success, like metal/shim.h:118-126). */
+#define GORCH_CUDA_OK 0
+#define GORCH_CUDA_ERR_BAD_ARG 1
+#define GORCH_CUDA_ERR_CUDA 2
+#define GORCH_CUDA_ERR_NCCL 3
+#define GORCH_CUDA_ERR_TIMEOUT 4
+#define GORCH_CUDA_ERR_LIMIT 5
+
+/* Element types of a logits tensor. bf16 rows are upcast in-kernel by
+ * bits << 16, the reference's bf16ToF32 (tensor.go:96-99). */
+#define GORCH_CUDA_F32 0
+#define GORCH_CUDA_BF16 1
+
+/* Which of the reference's two top-p routines a row follows. */
+#define GORCH_TOPP_MODE_A 0 /* model/generate.go:184-228 */
+#define GORCH_TOPP_MODE_B 1 /* model/qwen/generate.go:123-153 */
+
+/* Per-row flags written to out_flags. */
+#define GORCH_FLAG_BOUNDARY 0x001u     /* uniform within 1e-6 of an edge of the chosen CDF interval */
+#define GORCH_FLAG_FALLBACK 0x002u     /* walk fell through: id = V-1 (model/generate.go:239) */
+#define GORCH_FLAG_NONFINITE 0x004u    /* NaN/Inf poisoned the softmax; id = V-1 as upstream */
+#define GORCH_FLAG_TIE_CUT 0x008u      /* mode B cut separates equal probabilities */
+#define GORCH_FLAG_TIMEOUT 0x010u      /* a bounded device-side wait gave up */
+#define GORCH_FLAG_TOPP_EDGE 0x020u    /* top-p stop test decided within 1e-12 of its threshold */
+#define GORCH_FLAG_GENERAL_PATH 0x040u /* informational: row took the full-row path */
+#define GORCH_FLAG_INTERNAL 0x080u     /* an internal invariant failed; id = -1 or unreliable */
+#define GORCH_FLAG_BAD_CFG 0x100u      /* temperature negative, NaN or infinite; id = -1 */
+
+/* The sampling fields of GenerateConfig (model/generate.go:13-20; qwen:
+ * model/qwen/generate.go:13-20), one record per row. temperature 0 => greedy
+ * (generate.go:75); top_k <= 0 or >= V => off (:157); top_p <= 0 or >= 1 =>
+ * off (:184). */
+typedef struct {
+  float temperature;
+  int32_t top_k;
+  float top_p;
+  int32_t topp_mode;
+} GorchSampleCfg;
+
+/* Optional per-row diagnostics for parity checks. */
+typedef struct {
+  double sum_exp;   /* softmax denominator (generate.go:173-178) */
+  double resum;     /* top-p renormaliser (generate.go:221-227), 1 when inactive */
+  double edge_lo;   /* cumulative before the chosen token */
+  double edge_hi;   /* cumulative through the chosen token */
+  int32_t kept;     /* tokens with non-zero final probability */
+  float max_scaled; /* max of logits/T (generate.go:167-172) */
+  float threshold;  /* top-k threshold (generate.go:158); NaN when inactive */
+  int32_t path;     /* 0 greedy, 1 small-set path, 2 full-row path */
+} GorchSampleDebug;
+
+typedef struct {
+  uint64_t sample_launches; /* sampling kernel launches, cf. MetalDispatchCounts (ops.go:17-78) */
+  uint64_t argmax_launches;
+  uint64_t rows;
+  uint64_t h2d_bytes;       /* cf. metal.go:64-101 byte counters */
+  uint64_t d2h_bytes;
+  float last_kernel_ms;     /* device time of the last timed call (0 when timing is off) */
+} GorchCudaCounters;
+
+/* ---- lifecycle: replaces metal_create_device / metal_create_command_queue /
+ * metal_release / metal_free_string (metal/shim.h:16-17, 230-234) ---- */
+int gorch_cuda_device_count(int* count, char** errOut);
+GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut);
+void gorch_cuda_release(GorchCudaCtxRef ctx);
+void gorch_cuda_free_string(char* s);
+/* Block until all work queued on the context is done; cf. metal_sync_queue
+ * (metal/shim.h:228). */
+int gorch_cuda_sync(GorchCudaCtxRef ctx, char** errOut);
+/* Run the context's kernels on a caller-owned CUDA stream (cudaStream_t as
+ * void*); NULL restores the context's own stream. */
+int gorch_cuda_set_stream(GorchCudaCtxRef ctx, void* stream, char** errOut);
+/* Record device time of each call into counters.last_kernel_ms (adds a sync). */
+int gorch_cuda_set_timing(GorchCudaCtxRef ctx, int on);
+int gorch_cuda_get_counters(GorchCudaCtxRef ctx, GorchCudaCounters* out);
+
+/* ---- device buffers: replaces metal_create_shared_buffer /
+ * metal_buffer_contents / metal_release_buffer (metal/shim.h:21-28). CUDA
+ * memory is not host-visible, so contents move by upload/download. ---- */
+GorchCudaBufferRef gorch_cuda_buffer_alloc(GorchCudaCtxRef ctx, uint64_t bytes, char** errOut);
+void gorch_cuda_buffer_free(GorchCudaBufferRef buf);
+uint64_t gorch_cuda_buffer_length(GorchCudaBufferRef buf);
+void* gorch_cuda_buffer_device_ptr(GorchCudaBufferRef buf);
+int gorch_cuda_buffer_upload(GorchCudaBufferRef buf, uint64_t offset, const void* host,
+                             uint64_t bytes, char** errOut);
+int gorch_cuda_buffer_download(GorchCudaBufferRef buf, uint64_t offset, void* host,
+                               uint64_t bytes, char** errOut);
+
+/* ---- the sampling step ----
+ * Replaces the branch `if cfg.Temperature == 0 { argmax } else { sample }` at
+ * model/generate.go:75-79 and :109-113 (qwen: model/qwen/generate.go:49-53),
+ * i.e. argmax (generate.go:134-144), sample (:147-240), kthLargest (:243-260)
+ * and sampleLogits (qwen/generate.go:92-164), over a [B,V] batch of rows.
+ *
+ * logits      [B, row_stride] elements of `dtype`, row b at b*row_stride
+ * cfgs        [B] per-row configuration
+ * uniforms    [B] doubles in [0,1): the value the reference takes from
+ *             rand.Float64() (generate.go:231 / qwen/generate.go:155)
+ * out_ids     [B] sampled token ids
+ * out_flags   [B] GORCH_FLAG_* bits, or NULL
+ *
+ * Host form: all pointers are host memory; copies in and out happen inside
+ * the call, which blocks until the ids are written. */
+int gorch_cuda_sample_host(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                           int64_t V, int64_t row_stride, const GorchSampleCfg* cfgs,
+                           const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
+                           char** errOut);
+/* Device form: all pointers are device memory on the context's device; the
+ * launch is asynchronous on the context's stream (gorch_cuda_sync to wait).
+ * out_probs ([B,V] doubles: the filtered, renormalised distribution of
+ * generate.go:181/:227) and out_debug ([B]) may be NULL. */
+int gorch_cuda_sample_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                          int64_t V, int64_t row_stride, const GorchSampleCfg* cfgs,
+                          const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
+                          double* out_probs, GorchSampleDebug* out_debug, char** errOut);
+
+/* One row, the exact shape of the reference's calls: sample(logits,
+ * temperature, topK, topP) (generate.go:147) with the uniform passed in, and
+ * argmax when temperature == 0. Returns the token id, or -1 with *errOut set. */
+int64_t gorch_cuda_sample_row(GorchCudaCtxRef ctx, const float* logits, int64_t n,
+                              float temperature, int64_t top_k, float top_p, int topp_mode,
+                              double uniform, uint32_t* out_flag, char** errOut);
+
+/* Greedy fast path: argmax (generate.go:134-144; argmaxF32 qwen/generate.go:77-87;
+ * the inline loops at model/gpt2_loader.go:266-273 and model/qwen/voice.go:175)
+ * over every row; lowest index wins ties. */
+int gorch_cuda_argmax_host(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                           int64_t V, int64_t row_stride, int32_t* out_ids, char** errOut);
+int gorch_cuda_argmax_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                          int64_t V, int64_t row_stride, int32_t* out_ids, char** errOut);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* GORCH_CUDA_SHIM_H */

@@ -1,0 +1,197 @@
+"""ctypes front end for the CPU oracle (libgorch_oracle.so).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the
+benchmark's CPU-baseline leg. Nothing in the gorch_b200 package imports it.
+
+The library is the C++ restatement in gorch_sampling_oracle.cpp of the
+reference's model/generate.go:134-260 and model/qwen/generate.go:77-181.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libgorch_oracle.so")
+
+MODE_A = 0  # model/generate.go:184-228
+MODE_B = 1  # model/qwen/generate.go:123-153
+FAST_KTH = 1
+
+CFG_DTYPE = np.dtype(
+    [("temperature", "<f4"), ("top_k", "<i4"), ("top_p", "<f4"), ("topp_mode", "<i4")]
+)
+
+INFO_DTYPE = np.dtype(
+    [
+        ("kept", "<i8"),
+        ("sum_exp", "<f8"),
+        ("resum", "<f8"),
+        ("edge_lo", "<f8"),
+        ("edge_hi", "<f8"),
+        ("fallback", "<i4"),
+        ("cut_in_tie", "<i4"),
+        ("cut_cum", "<f8"),
+        ("max_scaled", "<f4"),
+        ("threshold", "<f4"),
+    ],
+    align=True,
+)
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the Makefile beside it; returns the .so path."""
+    src = os.path.join(_HERE, "gorch_sampling_oracle.cpp")
+    stale = (not os.path.exists(_LIB_PATH)) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
+    if force or stale:
+        subprocess.check_call(["make", "-C", _HERE, "-B", "libgorch_oracle.so"],
+                              stdout=subprocess.DEVNULL)
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(_LIB_PATH)
+        L.gorch_oracle_argmax_f32.restype = C.c_int64
+        L.gorch_oracle_argmax_f32.argtypes = [C.c_void_p, C.c_int64]
+        L.gorch_oracle_kth_largest_f32.restype = C.c_float
+        L.gorch_oracle_kth_largest_f32.argtypes = [C.c_void_p, C.c_int64, C.c_int64]
+        L.gorch_oracle_sample_f32.restype = C.c_int64
+        L.gorch_oracle_sample_f32.argtypes = [
+            C.c_void_p, C.c_int64, C.c_float, C.c_int64, C.c_float, C.c_int32,
+            C.c_double, C.c_void_p, C.c_void_p, C.c_int32,
+        ]
+        L.gorch_oracle_sample_batch.restype = None
+        L.gorch_oracle_sample_batch.argtypes = [
+            C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
+            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+        ]
+        L.gorch_oracle_topk_f32.restype = C.c_int32
+        L.gorch_oracle_topk_f32.argtypes = [
+            C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
+        ]
+        L.gorch_oracle_multinomial_f32.restype = None
+        L.gorch_oracle_multinomial_f32.argtypes = [
+            C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
+        ]
+        L.gorch_oracle_bf16_to_f32.restype = C.c_float
+        L.gorch_oracle_bf16_to_f32.argtypes = [C.c_uint16]
+        L.gorch_oracle_f32_to_bf16.restype = C.c_uint16
+        L.gorch_oracle_f32_to_bf16.argtypes = [C.c_float]
+        L.gorch_oracle_hw_threads.restype = C.c_int32
+        L.gorch_oracle_hw_threads.argtypes = []
+        _lib = L
+    return _lib
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def argmax(logits) -> int:
+    x = _f32(logits)
+    return int(lib().gorch_oracle_argmax_f32(x.ctypes.data, x.size))
+
+
+def kth_largest(data, k: int) -> float:
+    x = _f32(data)
+    return float(lib().gorch_oracle_kth_largest_f32(x.ctypes.data, x.size, int(k)))
+
+
+def sample(logits, temperature, top_k, top_p, u, mode=MODE_A, want_probs=False, flags=0):
+    """One row through sample (mode A) / sampleLogits (mode B).
+
+    Returns (id, info) or (id, info, probs)."""
+    x = _f32(logits)
+    info = np.zeros(1, dtype=INFO_DTYPE)
+    probs = np.empty(x.size, dtype=np.float64) if want_probs else None
+    tok = lib().gorch_oracle_sample_f32(
+        x.ctypes.data, x.size, float(temperature), int(top_k), float(top_p), int(mode),
+        float(u), probs.ctypes.data if want_probs else None, info.ctypes.data, int(flags),
+    )
+    if want_probs:
+        return int(tok), info[0], probs
+    return int(tok), info[0]
+
+
+def make_cfgs(B, temperature=1.0, top_k=0, top_p=0.0, mode=MODE_A) -> np.ndarray:
+    cfgs = np.zeros(B, dtype=CFG_DTYPE)
+    cfgs["temperature"] = temperature
+    cfgs["top_k"] = top_k
+    cfgs["top_p"] = top_p
+    cfgs["topp_mode"] = mode
+    return cfgs
+
+
+def sample_batch(logits, cfgs, uniforms, want_probs=False, want_info=True, flags=0, threads=1):
+    """A [B,V] batch. logits: float32, or uint16 holding bf16 bit patterns.
+
+    Returns dict(ids, probs|None, info|None)."""
+    x = np.ascontiguousarray(logits)
+    if x.dtype == np.uint16:
+        dtype = 1
+    else:
+        x = _f32(x)
+        dtype = 0
+    B, V = x.shape
+    cfgs = np.ascontiguousarray(cfgs, dtype=CFG_DTYPE)
+    uniforms = np.ascontiguousarray(uniforms, dtype=np.float64)
+    assert cfgs.shape == (B,) and uniforms.shape == (B,)
+    ids = np.empty(B, dtype=np.int64)
+    probs = np.empty((B, V), dtype=np.float64) if want_probs else None
+    info = np.zeros(B, dtype=INFO_DTYPE) if want_info else None
+    lib().gorch_oracle_sample_batch(
+        x.ctypes.data, dtype, B, V, V, cfgs.ctypes.data, uniforms.ctypes.data,
+        ids.ctypes.data, probs.ctypes.data if want_probs else None,
+        info.ctypes.data if want_info else None, int(flags), int(threads),
+    )
+    return {"ids": ids, "probs": probs, "info": info}
+
+
+def topk(x, k: int):
+    x = _f32(x)
+    B, V = x.shape
+    k = int(k)
+    values = np.empty((B, max(k, 0)), dtype=np.float32)
+    indices = np.empty((B, max(k, 0)), dtype=np.int64)
+    rc = lib().gorch_oracle_topk_f32(x.ctypes.data, B, V, k, values.ctypes.data,
+                                     indices.ctypes.data)
+    if rc != 0:
+        raise ValueError(f"TopK k={k} out of range [1, {V}]")  # index_ops.go:158-160
+    return values, indices
+
+
+def multinomial(probs, uniforms) -> np.ndarray:
+    p = _f32(probs)
+    B, V = p.shape
+    u = np.ascontiguousarray(uniforms, dtype=np.float64)
+    out = np.empty(B, dtype=np.int64)
+    lib().gorch_oracle_multinomial_f32(p.ctypes.data, B, V, u.ctypes.data, out.ctypes.data)
+    return out
+
+
+def f32_to_bf16_bits(a) -> np.ndarray:
+    """tensor.go:85-94 vectorised: float32 -> bf16 bit patterns (uint16), RNE."""
+    bits = _f32(a).view(np.uint32)
+    is_nan = (((bits >> 23) & 0xFF) == 0xFF) & ((bits & 0x7FFFFF) != 0)
+    rounding = np.uint32(0x7FFF) + ((bits >> 16) & np.uint32(1))
+    out = ((bits + rounding) >> 16).astype(np.uint16)
+    out_nan = ((bits >> 16) | np.uint32(0x40)).astype(np.uint16)
+    return np.where(is_nan, out_nan, out)
+
+
+def bf16_bits_to_f32(a) -> np.ndarray:
+    """tensor.go:96-99 vectorised."""
+    return (np.ascontiguousarray(a, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def hw_threads() -> int:
+    return int(lib().gorch_oracle_hw_threads())
