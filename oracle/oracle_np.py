@@ -74,7 +74,8 @@ def final_probs(logits, temperature, top_k, top_p, mode):
             resum = 0.0
             for v in q:
                 resum += float(v)
-            q = q / resum
+            with np.errstate(all="ignore"):
+                q = q / resum
         else:
             p64 = float(np.float32(top_p))
             order = sorted(range(n), key=lambda i: (-q[i], i))
