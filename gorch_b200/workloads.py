@@ -57,8 +57,19 @@ class Workload:
         return self.V * self.logits.dtype.itemsize + 16 + 8 + 4
 
 
+_SHARD = 0
+
+
+def set_shard(shard: int) -> None:
+    """Select an independent replica of every stream (key + 4096*shard); shard 0
+    is the canonical workload. Used to give each GPU of a weak-scaling run its
+    own rows."""
+    global _SHARD
+    _SHARD = int(shard)
+
+
 def _rng(c: int, stream: int) -> np.random.Generator:
-    return np.random.Generator(np.random.Philox(key=BASE_KEY + 16 * c + stream))
+    return np.random.Generator(np.random.Philox(key=BASE_KEY + 16 * c + stream + 4096 * _SHARD))
 
 
 def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
