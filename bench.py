@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="short run for ncu: no e2e leg, no CPU baseline, no clock hold")
     return ap.parse_args()
 
 
@@ -170,6 +172,8 @@ def reference_arm(args, rank, world):
 
 def main():
     args = parse()
+    if args.profile:
+        args.no_e2e = args.no_cpu_baseline = True
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -193,7 +197,8 @@ def main():
     B, V = w.B, w.V
     dt_code = DTYPE_BF16 if w.dtype == "bf16" else DTYPE_F32
     smp = sampling.CudaSampler(local_rank)
-    stream = torch.cuda.current_stream()
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
     smp.set_stream(stream.cuda_stream)
 
     # host (pinned) and device copies of the inputs
@@ -243,7 +248,7 @@ def main():
     kernel_ms = [a.elapsed_time(b) for a, b in evs]
     total_ms = float(sum(kernel_ms))          # device time of the K steps (flush writes excluded)
     # keep the load on for a moment if the timed region was too short for NVML to see it
-    t_end = time.perf_counter() + max(0.0, 0.6 - total_ms / 1e3)
+    t_end = time.perf_counter() + (0.0 if args.profile else max(0.0, 0.6 - total_ms / 1e3))
     while time.perf_counter() < t_end:
         for _ in range(20):
             step()

@@ -50,7 +50,7 @@ def load() -> C.CDLL:
         "gorch_cuda_release": (None, [p]),
         "gorch_cuda_free_string": (None, [p]),
         "gorch_cuda_sync": (i32, [p, err]),
-        "gorch_cuda_set_stream": (i32, [p, p, err]),
+        "gorch_cuda_set_stream": (i32, [p, p, i32, err]),
         "gorch_cuda_set_timing": (i32, [p, i32]),
         "gorch_cuda_get_counters": (i32, [p, C.POINTER(Counters)]),
         "gorch_cuda_buffer_alloc": (p, [p, C.c_uint64, err]),

@@ -280,10 +280,10 @@ int gorch_cuda_sync(GorchCudaCtxRef ctx, char** errOut) {
   return GORCH_CUDA_OK;
 }
 
-int gorch_cuda_set_stream(GorchCudaCtxRef ctx, void* stream, char** errOut) {
+int gorch_cuda_set_stream(GorchCudaCtxRef ctx, void* stream, int external, char** errOut) {
   Ctx* c = static_cast<Ctx*>(ctx);
   if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
-  c->stream = stream ? static_cast<cudaStream_t>(stream) : c->own_stream;
+  c->stream = external ? static_cast<cudaStream_t>(stream) : c->own_stream;
   return GORCH_CUDA_OK;
 }
 

@@ -93,8 +93,11 @@ class CudaSampler:
         _check(self._lib, self._lib.gorch_cuda_sync(self._ctx, C.byref(err)), err)
 
     def set_stream(self, stream_handle: int | None) -> None:
+        """Run on a caller-owned CUDA stream (its cudaStream_t as an int; 0 is the
+        legacy default stream); None goes back to the context's own stream."""
         err = C.c_void_p()
-        _check(self._lib, self._lib.gorch_cuda_set_stream(self._ctx, stream_handle or None, C.byref(err)), err)
+        ext = 0 if stream_handle is None else 1
+        _check(self._lib, self._lib.gorch_cuda_set_stream(self._ctx, stream_handle or None, ext, C.byref(err)), err)
 
     def set_timing(self, on: bool) -> None:
         self._lib.gorch_cuda_set_timing(self._ctx, 1 if on else 0)

@@ -95,9 +95,10 @@ void gorch_cuda_free_string(char* s);
 /* Block until all work queued on the context is done; cf. metal_sync_queue
  * (metal/shim.h:228). */
 int gorch_cuda_sync(GorchCudaCtxRef ctx, char** errOut);
-/* Run the context's kernels on a caller-owned CUDA stream (cudaStream_t as
- * void*); NULL restores the context's own stream. */
-int gorch_cuda_set_stream(GorchCudaCtxRef ctx, void* stream, char** errOut);
+/* external != 0: run the context's work on the caller-owned CUDA stream
+ * `stream` (a cudaStream_t as void*; NULL is the legacy default stream).
+ * external == 0: go back to the context's own stream. */
+int gorch_cuda_set_stream(GorchCudaCtxRef ctx, void* stream, int external, char** errOut);
 /* Record device time of each call into counters.last_kernel_ms (adds a sync). */
 int gorch_cuda_set_timing(GorchCudaCtxRef ctx, int on);
 int gorch_cuda_get_counters(GorchCudaCtxRef ctx, GorchCudaCounters* out);
