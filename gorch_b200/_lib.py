@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libgorchcud
 EXPORTS = [
     "gorch_cuda_device_count", "gorch_cuda_create_ctx", "gorch_cuda_release",
     "gorch_cuda_free_string", "gorch_cuda_sync", "gorch_cuda_set_stream",
-    "gorch_cuda_set_timing", "gorch_cuda_get_counters",
+    "gorch_cuda_set_timing", "gorch_cuda_get_counters", "gorch_cuda_set_kernel_variant",
     "gorch_cuda_buffer_alloc", "gorch_cuda_buffer_free", "gorch_cuda_buffer_length",
     "gorch_cuda_buffer_device_ptr", "gorch_cuda_buffer_upload", "gorch_cuda_buffer_download",
     "gorch_cuda_sample_host", "gorch_cuda_sample_dev", "gorch_cuda_sample_row",
@@ -53,6 +53,7 @@ def load() -> C.CDLL:
         "gorch_cuda_set_stream": (i32, [p, p, i32, err]),
         "gorch_cuda_set_timing": (i32, [p, i32]),
         "gorch_cuda_get_counters": (i32, [p, C.POINTER(Counters)]),
+        "gorch_cuda_set_kernel_variant": (i32, [p, i32, i32, err]),
         "gorch_cuda_buffer_alloc": (p, [p, C.c_uint64, err]),
         "gorch_cuda_buffer_free": (None, [p]),
         "gorch_cuda_buffer_length": (C.c_uint64, [p]),

@@ -16,9 +16,13 @@
 #include <new>
 
 #include "../../include/gorch_cuda_shim.h"
-#include "sample_kernel.cuh"
+#include "sample_cluster.cuh"
 
 namespace {
+
+// Largest slice kept in shared memory: 109 KB of dynamic shared memory per CTA
+// (two CTAs per SM) minus the two 16 KB work regions.
+constexpr int64_t kSliceCap = 109 * 1024 - gs::REGION_A - gs::REGION_B;
 
 struct Buffer {
   int device;
@@ -33,12 +37,15 @@ struct Scratch {  // grow-only device allocation
 
 struct Ctx {
   int device = 0;
+  int sm_count = 148;
   cudaStream_t own_stream = nullptr;
   cudaStream_t stream = nullptr;
   double* exp_table = nullptr;
   Scratch st_logits, st_cfgs, st_uniforms, st_ids, st_flags;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int timing = 0;
+  int variant = 0;        // 0: cluster kernel, 1: single-CTA kernel
+  int force_cluster = 0;  // 0: choose from the shape
   GorchCudaCounters counters{};
 };
 
@@ -127,13 +134,51 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
   a.exp_table = c->exp_table;
   a.row_offset = 0;
   if (c->timing) CUDA_TRY(cudaEventRecord(c->ev0, c->stream), errOut);
-  dim3 grid(static_cast<unsigned>(B)), block(gs::NT);
-  if (dtype == GORCH_CUDA_F32) {
-    gs::sample_rows_kernel<float><<<grid, block, gs::POOL_BYTES, c->stream>>>(a);
+  if (c->variant == 1) {
+    dim3 grid(static_cast<unsigned>(B)), block(gs::NT);
+    if (dtype == GORCH_CUDA_F32) {
+      gs::sample_rows_kernel<float><<<grid, block, gs::POOL_BYTES, c->stream>>>(a);
+    } else {
+      gs::sample_rows_kernel<uint16_t><<<grid, block, gs::POOL_BYTES, c->stream>>>(a);
+    }
+    CUDA_TRY(cudaGetLastError(), errOut);
   } else {
-    gs::sample_rows_kernel<uint16_t><<<grid, block, gs::POOL_BYTES, c->stream>>>(a);
+    // Cluster size: smallest power of two whose slice fits the shared-memory
+    // budget, raised for small batches so that the whole GPU has work.
+    const int vec = dtype == GORCH_CUDA_F32 ? 4 : 8;
+    const int64_t nvec_max = (V + 2 * (vec - 1)) / vec + 1;
+    int C = 1;
+    while (C < gs::CL_MAX && ((nvec_max + C - 1) / C) * 16 > kSliceCap) C *= 2;
+    while (C < gs::CL_MAX && B * C < 2 * c->sm_count && ((nvec_max + 2 * C - 1) / (2 * C)) >= 64) C *= 2;
+    if (c->force_cluster) C = c->force_cluster;
+    const int64_t need = ((nvec_max + C - 1) / C) * 16;
+    gs::ClusterArgs ca;
+    ca.k = a;
+    ca.resident_ok = need <= kSliceCap ? 1 : 0;
+    ca.slice_bytes = static_cast<int32_t>(ca.resident_ok && need > gs::MIN_SLICE_BYTES ? need : gs::MIN_SLICE_BYTES);
+    const size_t dyn = static_cast<size_t>(ca.slice_bytes) + gs::REGION_A + gs::REGION_B;
+    if (B * C > 0x7fffffffll) {
+      set_err(errOut, "gorch_cuda: batch too large for one launch");
+      return GORCH_CUDA_ERR_LIMIT;
+    }
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(static_cast<unsigned>(B * C));
+    lc.blockDim = dim3(gs::NT);
+    lc.dynamicSmemBytes = dyn;
+    lc.stream = c->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = static_cast<unsigned>(C);
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    lc.attrs = at;
+    lc.numAttrs = 1;
+    if (dtype == GORCH_CUDA_F32) {
+      CUDA_TRY(cudaLaunchKernelEx(&lc, gs::sample_cluster_kernel<float>, ca), errOut);
+    } else {
+      CUDA_TRY(cudaLaunchKernelEx(&lc, gs::sample_cluster_kernel<uint16_t>, ca), errOut);
+    }
   }
-  CUDA_TRY(cudaGetLastError(), errOut);
   if (force_greedy) c->counters.argmax_launches++; else c->counters.sample_launches++;
   c->counters.rows += static_cast<uint64_t>(B);
   if (c->timing) {
@@ -243,6 +288,7 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
     gorch_cuda_release(c);
     return nullptr;
   }
+  c->sm_count = prop.multiProcessorCount;
   if ((e = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking)) != cudaSuccess) return fail("cudaStreamCreate", e);
   c->stream = c->own_stream;
   if ((e = cudaEventCreate(&c->ev0)) != cudaSuccess) return fail("cudaEventCreate", e);
@@ -253,6 +299,8 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   if ((e = cudaMemcpy(c->exp_table, tab, sizeof tab, cudaMemcpyHostToDevice)) != cudaSuccess) return fail("cudaMemcpy(exp table)", e);
   if ((e = cudaFuncSetAttribute(gs::sample_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::POOL_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::sample_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::POOL_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::sample_cluster_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 109 * 1024)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::sample_cluster_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 109 * 1024)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   return c;
 }
 
@@ -291,6 +339,19 @@ int gorch_cuda_set_timing(GorchCudaCtxRef ctx, int on) {
   Ctx* c = static_cast<Ctx*>(ctx);
   if (!c) return GORCH_CUDA_ERR_BAD_ARG;
   c->timing = on ? 1 : 0;
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_set_kernel_variant(GorchCudaCtxRef ctx, int variant, int cluster_size, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if ((variant != 0 && variant != 1) ||
+      !(cluster_size == 0 || cluster_size == 1 || cluster_size == 2 || cluster_size == 4 || cluster_size == 8)) {
+    set_err(errOut, "gorch_cuda: variant must be 0 or 1, cluster_size 0, 1, 2, 4 or 8");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  c->variant = variant;
+  c->force_cluster = cluster_size;
   return GORCH_CUDA_OK;
 }
 

@@ -102,6 +102,11 @@ class CudaSampler:
     def set_timing(self, on: bool) -> None:
         self._lib.gorch_cuda_set_timing(self._ctx, 1 if on else 0)
 
+    def set_kernel_variant(self, variant: int = 0, cluster_size: int = 0) -> None:
+        """0: cluster kernel (default); 1: single-CTA kernel. cluster_size 0 = automatic."""
+        err = C.c_void_p()
+        _check(self._lib, self._lib.gorch_cuda_set_kernel_variant(self._ctx, int(variant), int(cluster_size), C.byref(err)), err)
+
     def counters(self) -> dict:
         c = _lib.Counters()
         self._lib.gorch_cuda_get_counters(self._ctx, C.byref(c))

@@ -102,6 +102,11 @@ int gorch_cuda_set_stream(GorchCudaCtxRef ctx, void* stream, int external, char*
 /* Record device time of each call into counters.last_kernel_ms (adds a sync). */
 int gorch_cuda_set_timing(GorchCudaCtxRef ctx, int on);
 int gorch_cuda_get_counters(GorchCudaCtxRef ctx, GorchCudaCounters* out);
+/* Which kernel serves the sampling calls. variant 0 (default): one thread-block
+ * cluster per row, slice resident in shared memory; variant 1: one CTA per row
+ * re-reading global memory (kept as an independent second implementation).
+ * cluster_size 0 picks the cluster size from the shape; 1, 2, 4, 8 force it. */
+int gorch_cuda_set_kernel_variant(GorchCudaCtxRef ctx, int variant, int cluster_size, char** errOut);
 
 /* ---- device buffers: replaces metal_create_shared_buffer /
  * metal_buffer_contents / metal_release_buffer (metal/shim.h:21-28). CUDA

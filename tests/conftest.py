@@ -19,10 +19,24 @@ def oracle():
     return orc
 
 
+# every GPU test runs against each kernel configuration: the cluster kernel with
+# its automatic cluster size and with forced sizes, and the single-CTA kernel
+VARIANTS = {"auto": (0, 0), "cluster1": (0, 1), "cluster2": (0, 2), "cluster4": (0, 4),
+            "cluster8": (0, 8), "single_cta": (1, 0)}
+
+
 @pytest.fixture(scope="session")
-def sampler():
+def _sampler_session():
     from gorch_b200 import build, sampling
     build.build()
     s = sampling.CudaSampler(0)
     yield s
     s.release()
+
+
+@pytest.fixture(params=list(VARIANTS))
+def sampler(request, _sampler_session):
+    variant, csize = VARIANTS[request.param]
+    _sampler_session.set_kernel_variant(variant, csize)
+    yield _sampler_session
+    _sampler_session.set_kernel_variant(0, 0)
