@@ -315,14 +315,17 @@ __global__ void __launch_bounds__(NT, 2) sample_cluster_kernel(ClusterArgs CA) {
     };
     uint4 raw_next = make_uint4(Neutral<T>::word, Neutral<T>::word, Neutral<T>::word, Neutral<T>::word);
     if (v0 + tid < v1) raw_next = load_masked(rv, v0 + tid);
+    // The decision to prune is taken from the atomic counter's return values: the
+    // thread that made the last append of a tile knows the exact count, and the
+    // barrier that ends the tile ORs the verdicts, so every thread sees the same.
+    int do_prune = 0;
     for (int base = v0; base < v1; base += NT) {            // uniform loop
       uint4 raw = raw_next;
       const int v = base + tid;
       raw_next = make_uint4(Neutral<T>::word, Neutral<T>::word, Neutral<T>::word, Neutral<T>::word);
       if (v + NT < v1) raw_next = load_masked(rv, v + NT);
-      int cnt = ctl.cand_count;
-      if (cnt + tile_elems > LCAP) {
-        cnt = prune(cnt);
+      if (do_prune) {
+        int cnt = prune(ctl.cand_count);
         if (cnt > LKEEP) { giveup = true; break; }          // ties at the threshold fill the buffer
       }
       float x[VEC];
@@ -334,17 +337,20 @@ __global__ void __launch_bounds__(NT, 2) sample_cluster_kernel(ClusterArgs CA) {
         nan_seen |= (x[c] != x[c]);
         any |= (x[c] >= thr);
       }
+      bool want = false;
       if (any && v < v1) {
         const int i0 = v * VEC - rv.shift;
 #pragma unroll
         for (int c = 0; c < VEC; c++) {
           int i = i0 + c;
           if (x[c] >= thr && i >= 0 && i < V) {
-            lc[atomicAdd(&ctl.cand_count, 1)] = make_uint2(__float_as_uint(x[c]), static_cast<uint32_t>(i));
+            int slot = atomicAdd(&ctl.cand_count, 1);
+            lc[slot] = make_uint2(__float_as_uint(x[c]), static_cast<uint32_t>(i));
+            want |= (slot + 1 + tile_elems > LCAP);
           }
         }
       }
-      __syncthreads();
+      do_prune = __syncthreads_or(want ? 1 : 0);
     }
     int n_loc = 0;
     if (!giveup) {

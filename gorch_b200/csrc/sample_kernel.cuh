@@ -473,6 +473,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(KernelArgs A) {
         __syncthreads();
         int ovf = ctl.overflow;
         int cnt = min(ctl.cand_count, CAND_CAP);
+        __syncthreads();   // everybody has read the counters before anyone appends again
         bool last_tile = (vbeg + tile_vecs >= rv.nvec);
         bool do_prune = ovf || (cnt > CAND_CAP / 2) || (last_tile && !ovf);
         if (!do_prune) { settled = true; break; }
