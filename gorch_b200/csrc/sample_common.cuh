@@ -39,6 +39,7 @@ struct RowDebug {  // optional per-row record for the parity tests
   float max_scaled; // max of logits/T
   float threshold;  // top-k threshold in logits/T units (NaN when inactive)
   int32_t path;     // 0 greedy, 1 small-set path, 2 full-row path
+  uint32_t cycles[8]; // SM clock ticks between the phases of the row, as seen by rank 0 / thread 0
 };
 
 // ---------------------------------------------------------------------------

@@ -51,6 +51,7 @@ struct KernelArgs {
   RowDebug* out_debug;     // [B] (may be null)
   const double* exp_table; // 256 doubles: 2^(j/256)
   int64_t row_offset;      // first row handled by this launch (for chunked launches)
+  const int32_t* worklist; // single-CTA kernel only: [0] = count, [1..] = rows to process (null: every row)
 };
 
 template <typename T> struct Elem;
@@ -325,8 +326,7 @@ __device__ __forceinline__ int bucket0(float d) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(NT, 2) sample_rows_kernel(KernelArgs A) {
-  extern __shared__ __align__(16) unsigned char pool[];
+__device__ void single_cta_row(const KernelArgs& A, const int64_t row_id, unsigned char* pool) {
   __shared__ Ctl ctl;
   __shared__ Cut cut;
   __shared__ double s_tab[256];
@@ -335,7 +335,6 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(KernelArgs A) {
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int64_t row_id = A.row_offset + blockIdx.x;
   const int V = A.V;
   const T* row = static_cast<const T*>(A.logits) + row_id * A.row_stride;
   RowView<T> rv;
@@ -371,6 +370,7 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(KernelArgs A) {
   RowDebug dbg;
   dbg.sum_exp = 0; dbg.resum = 1.0; dbg.edge_lo = 0; dbg.edge_hi = 0; dbg.kept = 0;
   dbg.max_scaled = 0; dbg.threshold = __int_as_float(0x7fc00000); dbg.path = 0;
+  for (int q = 0; q < 8; q++) dbg.cycles[q] = 0;
 
   // ------------------------------------------------------------------ greedy
   // generate.go:75-76 + 134-144: strict '>' from index 0. Lowest index wins
@@ -1078,6 +1078,21 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(KernelArgs A) {
     if (u - segbase / Re <= 1e-6) flags |= FLAG_BOUNDARY;
   }
   finish(id, flags, dbg);
+}
+
+// One CTA per row; with a work list, a fixed grid walks the listed rows.
+template <typename T>
+__global__ void __launch_bounds__(NT, 2) sample_rows_kernel(KernelArgs A) {
+  extern __shared__ __align__(16) unsigned char pool[];
+  if (A.worklist) {
+    const int n = A.worklist[0];
+    for (int w = blockIdx.x; w < n; w += gridDim.x) {
+      single_cta_row<T>(A, A.worklist[1 + w], pool);
+      __syncthreads();
+    }
+  } else {
+    single_cta_row<T>(A, A.row_offset + blockIdx.x, pool);
+  }
 }
 
 }  // namespace gs

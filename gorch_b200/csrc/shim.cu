@@ -41,6 +41,8 @@ struct Ctx {
   cudaStream_t own_stream = nullptr;
   cudaStream_t stream = nullptr;
   double* exp_table = nullptr;
+  double* eb_table = nullptr;
+  Scratch worklist;        // int32[1 + rows]: rows the cluster kernel leaves to the single-CTA kernel
   Scratch st_logits, st_cfgs, st_uniforms, st_ids, st_flags;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int timing = 0;
@@ -133,6 +135,7 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
   a.out_debug = reinterpret_cast<gs::RowDebug*>(out_debug);
   a.exp_table = c->exp_table;
   a.row_offset = 0;
+  a.worklist = nullptr;
   if (c->timing) CUDA_TRY(cudaEventRecord(c->ev0, c->stream), errOut);
   if (c->variant == 1) {
     dim3 grid(static_cast<unsigned>(B)), block(gs::NT);
@@ -152,31 +155,53 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
     while (C < gs::CL_MAX && B * C < 2 * c->sm_count && ((nvec_max + 2 * C - 1) / (2 * C)) >= 64) C *= 2;
     if (c->force_cluster) C = c->force_cluster;
     const int64_t need = ((nvec_max + C - 1) / C) * 16;
-    gs::ClusterArgs ca;
-    ca.k = a;
-    ca.resident_ok = need <= kSliceCap ? 1 : 0;
-    ca.slice_bytes = static_cast<int32_t>(ca.resident_ok && need > gs::MIN_SLICE_BYTES ? need : gs::MIN_SLICE_BYTES);
-    const size_t dyn = static_cast<size_t>(ca.slice_bytes) + gs::REGION_A + gs::REGION_B;
-    if (B * C > 0x7fffffffll) {
-      set_err(errOut, "gorch_cuda: batch too large for one launch");
-      return GORCH_CUDA_ERR_LIMIT;
-    }
-    cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3(static_cast<unsigned>(B * C));
-    lc.blockDim = dim3(gs::NT);
-    lc.dynamicSmemBytes = dyn;
-    lc.stream = c->stream;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = static_cast<unsigned>(C);
-    at[0].val.clusterDim.y = 1;
-    at[0].val.clusterDim.z = 1;
-    lc.attrs = at;
-    lc.numAttrs = 1;
-    if (dtype == GORCH_CUDA_F32) {
-      CUDA_TRY(cudaLaunchKernelEx(&lc, gs::sample_cluster_kernel<float>, ca), errOut);
+    if (need > kSliceCap || B * C > 0x7fffffffll) {
+      // rows too wide to keep in shared memory: the single-CTA kernel reads global memory
+      dim3 grid(static_cast<unsigned>(B)), block(gs::NT);
+      if (dtype == GORCH_CUDA_F32) {
+        gs::sample_rows_kernel<float><<<grid, block, gs::POOL_BYTES, c->stream>>>(a);
+      } else {
+        gs::sample_rows_kernel<uint16_t><<<grid, block, gs::POOL_BYTES, c->stream>>>(a);
+      }
+      CUDA_TRY(cudaGetLastError(), errOut);
     } else {
-      CUDA_TRY(cudaLaunchKernelEx(&lc, gs::sample_cluster_kernel<uint16_t>, ca), errOut);
+      int rc = ensure(c->worklist, (static_cast<size_t>(B) + 1) * sizeof(int32_t), errOut);
+      if (rc) return rc;
+      CUDA_TRY(cudaMemsetAsync(c->worklist.ptr, 0, sizeof(int32_t), c->stream), errOut);
+      gs::ClusterArgs ca;
+      ca.k = a;
+      ca.slice_bytes = static_cast<int32_t>(need > gs::MIN_SLICE_BYTES ? need : gs::MIN_SLICE_BYTES);
+      ca.eb_table = c->eb_table;
+      ca.worklist = static_cast<int32_t*>(c->worklist.ptr);
+      const size_t dyn = static_cast<size_t>(ca.slice_bytes) + gs::REGION_A + gs::REGION_B;
+      cudaLaunchConfig_t lc = {};
+      lc.gridDim = dim3(static_cast<unsigned>(B * C));
+      lc.blockDim = dim3(gs::NT);
+      lc.dynamicSmemBytes = dyn;
+      lc.stream = c->stream;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = static_cast<unsigned>(C);
+      at[0].val.clusterDim.y = 1;
+      at[0].val.clusterDim.z = 1;
+      lc.attrs = at;
+      lc.numAttrs = 1;
+      if (dtype == GORCH_CUDA_F32) {
+        CUDA_TRY(cudaLaunchKernelEx(&lc, gs::sample_cluster_kernel<float>, ca), errOut);
+      } else {
+        CUDA_TRY(cudaLaunchKernelEx(&lc, gs::sample_cluster_kernel<uint16_t>, ca), errOut);
+      }
+      // rows the cluster kernel handed over (rare): a fixed grid walks the list
+      gs::KernelArgs aw = a;
+      aw.worklist = ca.worklist;
+      const int64_t wg = B < 2 * c->sm_count ? B : 2 * c->sm_count;
+      dim3 grid(static_cast<unsigned>(wg)), block(gs::NT);
+      if (dtype == GORCH_CUDA_F32) {
+        gs::sample_rows_kernel<float><<<grid, block, gs::POOL_BYTES, c->stream>>>(aw);
+      } else {
+        gs::sample_rows_kernel<uint16_t><<<grid, block, gs::POOL_BYTES, c->stream>>>(aw);
+      }
+      CUDA_TRY(cudaGetLastError(), errOut);
     }
   }
   if (force_greedy) c->counters.argmax_launches++; else c->counters.sample_launches++;
@@ -297,6 +322,10 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   for (int j = 0; j < 256; j++) tab[j] = static_cast<double>(exp2l(static_cast<long double>(j) / 256.0L));
   if ((e = cudaMalloc(&c->exp_table, sizeof tab)) != cudaSuccess) return fail("cudaMalloc(exp table)", e);
   if ((e = cudaMemcpy(c->exp_table, tab, sizeof tab, cudaMemcpyHostToDevice)) != cudaSuccess) return fail("cudaMemcpy(exp table)", e);
+  static double ebt[gs::NB1];
+  for (int j = 0; j < gs::NB1; j++) ebt[j] = static_cast<double>(expl(-static_cast<long double>(j) / 32.0L));
+  if ((e = cudaMalloc(&c->eb_table, sizeof ebt)) != cudaSuccess) return fail("cudaMalloc(bucket table)", e);
+  if ((e = cudaMemcpy(c->eb_table, ebt, sizeof ebt, cudaMemcpyHostToDevice)) != cudaSuccess) return fail("cudaMemcpy(bucket table)", e);
   if ((e = cudaFuncSetAttribute(gs::sample_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::POOL_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::sample_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::POOL_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::sample_cluster_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 109 * 1024)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
@@ -313,6 +342,8 @@ void gorch_cuda_release(GorchCudaCtxRef ctx) {
     if (s->ptr) cudaFree(s->ptr);
   }
   if (c->exp_table) cudaFree(c->exp_table);
+  if (c->eb_table) cudaFree(c->eb_table);
+  if (c->worklist.ptr) cudaFree(c->worklist.ptr);
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
   if (c->own_stream) cudaStreamDestroy(c->own_stream);

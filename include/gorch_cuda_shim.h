@@ -75,6 +75,7 @@ typedef struct {
   float max_scaled; /* max of logits/T (generate.go:167-172) */
   float threshold;  /* top-k threshold (generate.go:158); NaN when inactive */
   int32_t path;     /* 0 greedy, 1 small-set path, 2 full-row path */
+  uint32_t cycles[8]; /* SM clock ticks per phase of the row (rank 0 of the cluster) */
 } GorchSampleDebug;
 
 typedef struct {
