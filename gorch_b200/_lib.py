@@ -24,7 +24,7 @@ EXPORTS = [
 
 class Counters(C.Structure):
     _fields_ = [
-        ("sample_launches", C.c_uint64), ("argmax_launches", C.c_uint64), ("rows", C.c_uint64),
+        ("sample_launches", C.c_uint64), ("kernel_launches", C.c_uint64), ("argmax_launches", C.c_uint64), ("rows", C.c_uint64),
         ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64), ("last_kernel_ms", C.c_float),
     ]
 

@@ -16,13 +16,17 @@
 #include <new>
 
 #include "../../include/gorch_cuda_shim.h"
-#include "sample_cluster.cuh"
+#include "sample_batch.cuh"
 
 namespace {
 
 // Largest slice kept in shared memory: 109 KB of dynamic shared memory per CTA
 // (two CTAs per SM) minus the two 16 KB work regions.
 constexpr int64_t kSliceCap = 109 * 1024 - gs::REGION_A - gs::REGION_B;
+
+// Batches of at least this many rows are sorted by kind and served by the narrow / wide
+// kernels; smaller ones use one cluster per row so that every SM still has work.
+constexpr int64_t kBatchModeRows = 128;
 
 struct Buffer {
   int device;
@@ -46,7 +50,7 @@ struct Ctx {
   Scratch st_logits, st_cfgs, st_uniforms, st_ids, st_flags;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int timing = 0;
-  int variant = 0;        // 0: cluster kernel, 1: single-CTA kernel
+  int variant = 0;        // 0: by batch size, 1: single-CTA kernel, 2: classify + narrow/wide kernels, 3: cluster kernel
   int force_cluster = 0;  // 0: choose from the shape
   GorchCudaCounters counters{};
 };
@@ -137,7 +141,42 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
   a.row_offset = 0;
   a.worklist = nullptr;
   if (c->timing) CUDA_TRY(cudaEventRecord(c->ev0, c->stream), errOut);
-  if (c->variant == 1) {
+  int klaunch = 1;
+  const bool batch_mode = c->variant == 2 || (c->variant == 0 && B >= kBatchModeRows);
+  if (batch_mode) {
+    // classify -> narrow (greedy / top-k) -> wide (top-k off) -> single-CTA (whatever is left)
+    const size_t ints = 16 + 3 * static_cast<size_t>(B) + 1;
+    int rc = ensure(c->worklist, ints * sizeof(int32_t), errOut);
+    if (rc) return rc;
+    int32_t* base = static_cast<int32_t*>(c->worklist.ptr);
+    gs::BatchArgs ba;
+    ba.k = a;
+    ba.eb_table = c->eb_table;
+    ba.hdr = base;
+    ba.list_narrow = base + 16;
+    ba.list_wide = base + 16 + B;
+    ba.list_single = base + 16 + 2 * B;
+    ba.B = B;
+    CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
+    CUDA_TRY(cudaMemsetAsync(ba.list_single, 0, sizeof(int32_t), c->stream), errOut);
+    gs::classify_rows_kernel<<<static_cast<unsigned>((B + 255) / 256), 256, 0, c->stream>>>(ba);
+    const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
+    const unsigned gw = static_cast<unsigned>(B < c->sm_count ? B : c->sm_count);
+    const unsigned gsgl = static_cast<unsigned>(B < 2 * c->sm_count ? B : 2 * c->sm_count);
+    gs::KernelArgs aw = a;
+    aw.worklist = ba.list_single;
+    if (dtype == GORCH_CUDA_F32) {
+      gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
+      if (!force_greedy) gs::wide_rows_kernel<float><<<gw, gs::W_NT, gs::W2_DYN_BYTES, c->stream>>>(ba);
+      if (!force_greedy) gs::sample_rows_kernel<float><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
+    } else {
+      gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
+      if (!force_greedy) gs::wide_rows_kernel<uint16_t><<<gw, gs::W_NT, gs::W2_DYN_BYTES, c->stream>>>(ba);
+      if (!force_greedy) gs::sample_rows_kernel<uint16_t><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
+    }
+    CUDA_TRY(cudaGetLastError(), errOut);
+    klaunch = force_greedy ? 2 : 4;
+  } else if (c->variant == 1) {
     dim3 grid(static_cast<unsigned>(B)), block(gs::NT);
     if (dtype == GORCH_CUDA_F32) {
       gs::sample_rows_kernel<float><<<grid, block, gs::POOL_BYTES, c->stream>>>(a);
@@ -202,8 +241,10 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
         gs::sample_rows_kernel<uint16_t><<<grid, block, gs::POOL_BYTES, c->stream>>>(aw);
       }
       CUDA_TRY(cudaGetLastError(), errOut);
+      klaunch = 2;
     }
   }
+  c->counters.kernel_launches += static_cast<uint64_t>(klaunch);
   if (force_greedy) c->counters.argmax_launches++; else c->counters.sample_launches++;
   c->counters.rows += static_cast<uint64_t>(B);
   if (c->timing) {
@@ -330,6 +371,10 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   if ((e = cudaFuncSetAttribute(gs::sample_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::POOL_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::sample_cluster_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 109 * 1024)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::sample_cluster_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 109 * 1024)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::narrow_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::narrow_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::W2_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::W2_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   return c;
 }
 
@@ -376,9 +421,9 @@ int gorch_cuda_set_timing(GorchCudaCtxRef ctx, int on) {
 int gorch_cuda_set_kernel_variant(GorchCudaCtxRef ctx, int variant, int cluster_size, char** errOut) {
   Ctx* c = static_cast<Ctx*>(ctx);
   if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
-  if ((variant != 0 && variant != 1) ||
+  if ((variant < 0 || variant > 3) ||
       !(cluster_size == 0 || cluster_size == 1 || cluster_size == 2 || cluster_size == 4 || cluster_size == 8)) {
-    set_err(errOut, "gorch_cuda: variant must be 0 or 1, cluster_size 0, 1, 2, 4 or 8");
+    set_err(errOut, "gorch_cuda: variant must be 0..3, cluster_size 0, 1, 2, 4 or 8");
     return GORCH_CUDA_ERR_BAD_ARG;
   }
   c->variant = variant;

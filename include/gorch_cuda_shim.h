@@ -79,7 +79,8 @@ typedef struct {
 } GorchSampleDebug;
 
 typedef struct {
-  uint64_t sample_launches; /* sampling kernel launches, cf. MetalDispatchCounts (ops.go:17-78) */
+  uint64_t sample_launches; /* sampling calls dispatched, cf. MetalDispatchCounts (ops.go:17-78) */
+  uint64_t kernel_launches; /* CUDA kernels launched by those calls */
   uint64_t argmax_launches;
   uint64_t rows;
   uint64_t h2d_bytes;       /* cf. metal.go:64-101 byte counters */
@@ -103,10 +104,12 @@ int gorch_cuda_set_stream(GorchCudaCtxRef ctx, void* stream, int external, char*
 /* Record device time of each call into counters.last_kernel_ms (adds a sync). */
 int gorch_cuda_set_timing(GorchCudaCtxRef ctx, int on);
 int gorch_cuda_get_counters(GorchCudaCtxRef ctx, GorchCudaCounters* out);
-/* Which kernel serves the sampling calls. variant 0 (default): one thread-block
- * cluster per row, slice resident in shared memory; variant 1: one CTA per row
- * re-reading global memory (kept as an independent second implementation).
- * cluster_size 0 picks the cluster size from the shape; 1, 2, 4, 8 force it. */
+/* Which kernels serve the sampling calls. variant 0 (default): by batch size
+ * (large batches: rows sorted by kind, then the narrow and wide kernels; small
+ * ones: one thread-block cluster per row); 1: one CTA per row re-reading global
+ * memory (an independent second implementation); 2: force the large-batch
+ * kernels; 3: force the cluster kernel. cluster_size 0 picks the cluster size
+ * from the shape; 1, 2, 4, 8 force it. */
 int gorch_cuda_set_kernel_variant(GorchCudaCtxRef ctx, int variant, int cluster_size, char** errOut);
 
 /* ---- device buffers: replaces metal_create_shared_buffer /

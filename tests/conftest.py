@@ -21,8 +21,8 @@ def oracle():
 
 # every GPU test runs against each kernel configuration: the cluster kernel with
 # its automatic cluster size and with forced sizes, and the single-CTA kernel
-VARIANTS = {"auto": (0, 0), "cluster1": (0, 1), "cluster2": (0, 2), "cluster4": (0, 4),
-            "cluster8": (0, 8), "single_cta": (1, 0)}
+VARIANTS = {"auto": (0, 0), "batch": (2, 0), "cluster1": (3, 1), "cluster2": (3, 2), "cluster4": (3, 4),
+            "cluster8": (3, 8), "single_cta": (1, 0)}
 
 
 @pytest.fixture(scope="session")
