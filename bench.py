@@ -235,7 +235,7 @@ def main():
     clocks.start()
     K = args.steps
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
-    launches0 = smp.counters()["sample_launches"]
+    launches0 = smp.counters()["kernel_launches"]
     barrier()
     for a, b in evs:
         if flush is not None:
@@ -244,7 +244,7 @@ def main():
         step()
         b.record(stream)
     barrier()
-    launches = smp.counters()["sample_launches"] - launches0
+    launches = smp.counters()["kernel_launches"] - launches0
     kernel_ms = [a.elapsed_time(b) for a, b in evs]
     total_ms = float(sum(kernel_ms))          # device time of the K steps (flush writes excluded)
     # keep the load on for a moment if the timed region was too short for NVML to see it
@@ -293,7 +293,8 @@ def main():
             "logits_gbs_per_gpu": achieved,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": measured_traffic(w), "peak_source": peak_kind,
-                         "kernel": "sample_rows_kernel", "algorithmic_bytes_per_launch": alg_bytes},
+                         "kernel": dominant_kernel(w), "algorithmic_bytes_per_launch": alg_bytes,
+                         "timed": "whole step (every kernel of the call), CUDA events on the launching stream"},
             "clocks": clk, "gpu_launches": int(launches),
         }
         if e2e_ms_max > 0:
@@ -313,6 +314,15 @@ def main():
     if world > 1:
         dist.destroy_process_group()
     smp.release()
+
+
+def dominant_kernel(w):
+    """The kernel that does the streaming for this workload (see profiles/)."""
+    if w.B < 384:
+        return "sample_cluster_kernel"
+    if int(w.cfgs["top_k"][0]) > 0 or float(w.cfgs["temperature"][0]) == 0.0:
+        return "narrow_rows_kernel"
+    return "wide_rows_kernel"
 
 
 def measured_traffic(w):

@@ -26,7 +26,7 @@ constexpr int64_t kSliceCap = 109 * 1024 - gs::REGION_A - gs::REGION_B;
 
 // Batches of at least this many rows are sorted by kind and served by the narrow / wide
 // kernels; smaller ones use one cluster per row so that every SM still has work.
-constexpr int64_t kBatchModeRows = 128;
+constexpr int64_t kBatchModeRows = 384;
 
 struct Buffer {
   int device;
