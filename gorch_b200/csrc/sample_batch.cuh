@@ -533,30 +533,7 @@ __device__ __forceinline__ uint4 mask_edges(const RowView<T>& rv, int v, uint4 r
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// ---- bulk asynchronous copies global -> shared (TMA, no tensor map) with an mbarrier per stage
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_addr(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, unsigned long long* bar,
-                                          unsigned long long policy) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_addr(bar)), "r"(bytes) : "memory");
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-               :: "r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)), "l"(policy) : "memory");
-}
-// Bounded wait for a phase of the barrier: false when it has not completed after about two
-// seconds of SM clock. Each attempt may suspend the thread for up to ~20 us.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity) {
-  const uint32_t a = smem_addr(bar);
-  const long long start = clock64();
-  for (;;) {
-    uint32_t done;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(done) : "r"(a), "r"(parity), "r"(20000u) : "memory");
-    if (done) return true;
-    if (clock64() - start > 4000000000ll) return false;
-  }
-}
 
 #ifndef GS_W_TILE_VECS
 #define GS_W_TILE_VECS 2048
@@ -571,59 +548,44 @@ constexpr int W2_OFF_EB = W2_OFF_ZONE + W_ZCAP * 8;
 constexpr int W2_OFF_PART = W2_OFF_EB + NB1 * 8;
 constexpr int W2_DYN_BYTES = W2_OFF_PART + W_MAX_TILES * W_NW * 8;
 
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_addr(bar)) : "memory");
-}
-
-// Ring of W_NST tiles fed by bulk copies. Every warp consumes every tile (its own 64-vector
-// piece of it): it waits on the tile's "full" barrier, and its lane 0 arrives on the tile's
-// "empty" barrier when the warp is done. Warp 0 is also the producer: before it starts tile t
-// it waits until every warp has released tile t-1 and refills that stage with tile t-1+W_NST.
-// No block-wide barrier is involved, so warps drift up to W_NST-1 tiles apart.
+// Thread-private asynchronous prefetch through shared memory. A tile is W_TILE_VECS vectors; warp w
+// owns vectors [64w, 64w+64) of every tile and lane l of it the two vectors 64w+l and 64w+32+l. Each
+// thread copies exactly the vectors it will read (cp.async, 16 bytes each, through L2 like an
+// ordinary load) W_NST-1 tiles ahead into its own slots of a W_NST-deep ring and waits for its own
+// copy groups: no barrier of any kind inside a pass, and the row is re-read from L2 by later passes.
 struct WRing {
   uint4* base;
-  unsigned long long* full;
-  unsigned long long* empty;
   const uint4* src;        // vector 0 of the row
   int nvec, ntiles;
-  uint32_t fpar, epar;     // next parity to wait for, one bit per stage
   unsigned long long pol;
-  bool ok;
 };
-__device__ __forceinline__ void wring_issue(const WRing& r, int t) {
-  const int nvt = min(W_TILE_VECS, r.nvec - t * W_TILE_VECS);
-  bulk_load(r.base + (t % W_NST) * W_TILE_VECS, r.src + static_cast<size_t>(t) * W_TILE_VECS,
-            static_cast<uint32_t>(nvt) * 16u, &r.full[t % W_NST], r.pol);
+__device__ __forceinline__ void cp_async16(uint32_t dst_s, const void* src, unsigned long long pol) {
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" :: "r"(dst_s), "l"(src), "l"(pol) : "memory");
 }
-__device__ __forceinline__ void wring_begin(WRing& r, int tid) {
-  if (tid == 0) for (int t = 0; t < min(W_NST, r.ntiles); t++) wring_issue(r, t);
-}
-// Returns the tile's shared-memory address once it has landed; sets r.ok = false on a timeout.
-__device__ __forceinline__ const uint4* wring_acquire(WRing& r, int t, int warp, int lane) {
-  if (warp == 0 && t >= 1) {
-    const int ps = (t - 1) % W_NST;
-    if (!mbar_wait(&r.empty[ps], (r.epar >> ps) & 1u)) r.ok = false;
-    r.epar ^= (1u << ps);
-    if (lane == 0 && t - 1 + W_NST < r.ntiles) wring_issue(r, t - 1 + W_NST);
-    __syncwarp();
+__device__ __forceinline__ void wring_issue(const WRing& r, int t, int warp, int lane) {
+  if (t < r.ntiles) {
+    const int j = warp * (W_TILE_VECS / W_NW) + lane;
+    const int g = t * W_TILE_VECS + j;
+    const uint32_t d = smem_addr(r.base + (t % W_NST) * W_TILE_VECS + j);
+    if (g < r.nvec) cp_async16(d, r.src + g, r.pol);
+    if (g + 32 < r.nvec) cp_async16(d + 512u, r.src + g + 32, r.pol);
   }
-  const int st = t % W_NST;
-  if (!mbar_wait(&r.full[st], (r.fpar >> st) & 1u)) r.ok = false;
-  r.fpar ^= (1u << st);
-  return r.base + st * W_TILE_VECS;
+  asm volatile("cp.async.commit_group;" ::: "memory");   // one group per tile, empty or not
 }
-__device__ __forceinline__ void wring_release(WRing& r, int t, int lane) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(&r.empty[t % W_NST]);      // tiles are only read by the warps: no proxy fence needed
+__device__ __forceinline__ void wring_begin(const WRing& r, int tid) {
+#pragma unroll
+  for (int t = 0; t < W_NST - 1; t++) wring_issue(r, t, tid >> 5, tid & 31);
 }
-// After the last tile: warp 0 collects the last tile's release so that every phase of the
-// "empty" barriers has been observed exactly once.
-__device__ __forceinline__ void wring_end(WRing& r, int warp) {
-  if (warp == 0 && r.ntiles >= 1) {
-    const int ps = (r.ntiles - 1) % W_NST;
-    if (!mbar_wait(&r.empty[ps], (r.epar >> ps) & 1u)) r.ok = false;
-    r.epar ^= (1u << ps);
-  }
+// Issues tile t+W_NST-1 into the slot read one iteration ago and returns tile t once this
+// thread's copies of it have landed.
+__device__ __forceinline__ const uint4* wring_acquire(const WRing& r, int t, int warp, int lane) {
+  wring_issue(r, t + W_NST - 1, warp, lane);
+  asm volatile("cp.async.wait_group %0;" :: "n"(W_NST - 1) : "memory");
+  return r.base + (t % W_NST) * W_TILE_VECS;
+}
+__device__ __forceinline__ void wring_release(const WRing&, int, int) {}
+__device__ __forceinline__ void wring_end(const WRing&, int) {
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 // Shared-memory loads by 32-bit shared address (the pointers below travel through structs and
 // function arguments, where the compiler would otherwise fall back to generic loads).
@@ -709,11 +671,11 @@ __device__ __forceinline__ void load8_checked(const uint4* tile, int nvt, int t,
 
 // pass 1: max, min, NaN flag over the row's logits
 template <typename T>
-__device__ __noinline__ void wide_pass1(WRing& r_io, const RowView<T>& rv_in, int tid, float& xmax, float& xmin, bool& nan_seen) {
+__device__ __noinline__ void wide_pass1(const WRing& r_io, const RowView<T>& rv_in, int tid, float& xmax, float& xmin, bool& nan_seen) {
   constexpr int VEC = Elem<T>::VEC;
   constexpr int STEPS = (W_TILE_VECS / W_NW) / (32 * (8 / VEC));
   const int warp = tid >> 5, lane = tid & 31;
-  WRing r = r_io;                      // registers, not memory, inside the loop
+  const WRing r = r_io;                // registers, not memory, inside the loop
   const RowView<T> rv = rv_in;
   float vmax = -INFINITY, vmin = INFINITY;
   bool nan = false;
@@ -746,18 +708,17 @@ __device__ __noinline__ void wide_pass1(WRing& r_io, const RowView<T>& rv_in, in
     wring_release(r, t, lane);
   }
   wring_end(r, warp);
-  r_io.fpar = r.fpar; r_io.epar = r.epar; r_io.ok = r.ok;
   xmax = vmax; xmin = vmin; nan_seen = nan;
 }
 
 // pass 2: count histogram over the 1/128 buckets of d (logits outside the row are not counted)
 template <typename T>
-__device__ __noinline__ void wide_pass2(WRing& r_io, const RowView<T>& rv_in, int tid, uint32_t* hist, float m, float Tm) {
+__device__ __noinline__ void wide_pass2(const WRing& r_io, const RowView<T>& rv_in, int tid, uint32_t* hist, float m, float Tm) {
   constexpr int VEC = Elem<T>::VEC;
   constexpr int STEPS = (W_TILE_VECS / W_NW) / (32 * (8 / VEC));
   const int warp = tid >> 5, lane = tid & 31;
   const bool t_is_one = (Tm == 1.0f);
-  WRing r = r_io;
+  const WRing r = r_io;
   const RowView<T> rv = rv_in;
   wring_begin(r, tid);
   for (int t = 0; t < r.ntiles; t++) {
@@ -793,7 +754,6 @@ __device__ __noinline__ void wide_pass2(WRing& r_io, const RowView<T>& rv_in, in
     wring_release(r, t, lane);
   }
   wring_end(r, warp);
-  r_io.fpar = r.fpar; r_io.epar = r.epar; r_io.ok = r.ok;
 }
 
 // pass 3: exponentials. part[t*W_NW + warp] receives the certainly-kept mass of the warp's
@@ -801,14 +761,14 @@ __device__ __noinline__ void wide_pass2(WRing& r_io, const RowView<T>& rv_in, in
 // FAST: every logit of the row has d > -31.9 (bucket-table exponential, no range check);
 // TONE: temperature 1; CUT: a top-p cut is active (dA/dB classify the logits).
 template <typename T, bool FAST, bool TONE, bool CUT>
-__device__ __noinline__ void wide_pass3(WRing& r_io, const RowView<T>& rv_in, int tid, float m, float Tm, float dA, float dB,
+__device__ __noinline__ void wide_pass3(const WRing& r_io, const RowView<T>& rv_in, int tid, float m, float Tm, float dA, float dB,
                                         const double* ebs, const double* s_tab, double* part, uint2* zl, int* zcnt,
                                         double& Ksum, double& Dsum, double& Zsum) {
   constexpr int VEC = Elem<T>::VEC;
   constexpr int EPI = 8 / VEC;
   constexpr int STEPS = (W_TILE_VECS / W_NW) / (32 * EPI);
   const int warp = tid >> 5, lane = tid & 31;
-  WRing r = r_io;
+  const WRing r = r_io;
   const RowView<T> rv = rv_in;
   const uint32_t eb_s = smem_addr(ebs);
   double dsum = 0.0, zsum = 0.0, ksum = 0.0;
@@ -871,25 +831,21 @@ __device__ __noinline__ void wide_pass3(WRing& r_io, const RowView<T>& rv_in, in
     if (lane == 0) { part[t * W_NW + warp] = kw; ksum += kw; }
   }
   wring_end(r, warp);
-  r_io.fpar = r.fpar; r_io.epar = r.epar; r_io.ok = r.ok;
   Ksum = ksum; Dsum = dsum; Zsum = zsum;
 }
 
 struct WideShared {
   bu::Scratch sc;
   double tab[256];
-  unsigned long long full[W_NST];
-  unsigned long long empty[W_NST];
   double bcd[4];
   int bc[4];
   int cnt;
   int row;
-  int abort_flag;
 };
 
 template <typename T>
 __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned char* dyn, WideShared& sh,
-                         uint32_t& fpar, uint32_t& epar, unsigned long long pol_keep, unsigned long long pol_drop) {
+                         unsigned long long pol_keep, unsigned long long pol_drop) {
   const KernelArgs& A = BA.k;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int V = A.V;
@@ -944,26 +900,14 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
   }
 
   WRing ring_;
-  ring_.base = ring; ring_.full = sh.full; ring_.empty = sh.empty; ring_.src = rv.vbase;
-  ring_.nvec = rv.nvec; ring_.ntiles = ntiles; ring_.fpar = fpar; ring_.epar = epar; ring_.ok = true;
-  // a copy that did not land in time: flag the row, leave it, keep the barrier bookkeeping
-  auto pass_failed = [&]() -> bool {
-    fpar = ring_.fpar; epar = ring_.epar;
-    const int bad = __syncthreads_or(ring_.ok ? 0 : 1);
-    if (bad) {
-      dbg.sum_exp = QNAN;
-      fill_probs_row(QNAN);
-      write_row(-1, flags | FLAG_TIMEOUT);
-    }
-    return bad != 0;
-  };
+  ring_.base = ring; ring_.src = rv.vbase; ring_.nvec = rv.nvec; ring_.ntiles = ntiles;
 
   // ---- pass 1: max, min, NaN (from HBM; L2 is asked to keep the row)
   float xmax = -INFINITY, xmin = INFINITY;
   bool nan_seen = false;
   ring_.pol = pol_keep;
   wide_pass1<T>(ring_, rv, tid, xmax, xmin, nan_seen);
-  if (pass_failed()) return;
+  __syncthreads();
   const int anynan = bu::max_i<W_NW>(nan_seen ? 1 : 0, sc, tid);
   xmax = okey_to_float(static_cast<uint32_t>(bu::max_u64<W_NW>(static_cast<unsigned long long>(okey(xmax)), sc, tid)));
   xmin = okey_to_float(static_cast<uint32_t>(bu::min_u64<W_NW>(static_cast<unsigned long long>(okey(xmin)), sc, tid)));
@@ -988,7 +932,7 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     __syncthreads();
     ring_.pol = pol_keep;
     wide_pass2<T>(ring_, rv, tid, hist, m, Tm);
-    if (pass_failed()) return;
+    __syncthreads();
     constexpr int PER = W_NB / W_NT;                         // 4 buckets per thread
     double lo_inc[PER], hi_inc[PER];
     int cb[PER];
@@ -1055,7 +999,7 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     else         { if (t_is_one) GS_P3(false, true, false); else GS_P3(false, false, false); }
   }
 #undef GS_P3
-  if (pass_failed()) return;
+  __syncthreads();
   if (lane != 0) Ksum = 0.0;                                 // kept mass is already warp-reduced into lane 0
   double Ktot = Ksum, Dtot = Dsum, Ztot = Zsum;
   bu::sum_d3<W_NW>(Ktot, Dtot, Ztot, sc, tid);
@@ -1323,15 +1267,9 @@ __global__ void __launch_bounds__(W_NT, 1) wide_rows_kernel(BatchArgs BA) {
   extern __shared__ __align__(128) unsigned char dyn[];
   __shared__ WideShared sh;
   if (threadIdx.x < 256) sh.tab[threadIdx.x] = BA.k.exp_table[threadIdx.x];
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < W_NST; s++) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], W_NW); }
-    sh.abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
   unsigned long long pol_keep, pol_drop;
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_keep));
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol_drop));
-  uint32_t fpar = 0, epar = 0;
   const int n = BA.hdr[1];
   for (;;) {
     __syncthreads();
@@ -1342,7 +1280,7 @@ __global__ void __launch_bounds__(W_NT, 1) wide_rows_kernel(BatchArgs BA) {
     __syncthreads();
     const int row = sh.row;
     if (row < 0) break;
-    wide_row<T>(BA, row, dyn, sh, fpar, epar, pol_keep, pol_drop);
+    wide_row<T>(BA, row, dyn, sh, pol_keep, pol_drop);
   }
 }
 
