@@ -17,7 +17,7 @@ EXPORTS = [
     "gorch_cuda_set_timing", "gorch_cuda_get_counters", "gorch_cuda_set_kernel_variant",
     "gorch_cuda_buffer_alloc", "gorch_cuda_buffer_free", "gorch_cuda_buffer_length",
     "gorch_cuda_buffer_device_ptr", "gorch_cuda_buffer_upload", "gorch_cuda_buffer_download",
-    "gorch_cuda_sample_host", "gorch_cuda_sample_dev", "gorch_cuda_sample_row",
+    "gorch_cuda_sample_host", "gorch_cuda_sample_dev", "gorch_cuda_sample_dev_static", "gorch_cuda_sample_row",
     "gorch_cuda_argmax_host", "gorch_cuda_argmax_dev",
 ]
 
@@ -62,6 +62,7 @@ def load() -> C.CDLL:
         "gorch_cuda_buffer_download": (i32, [p, C.c_uint64, p, C.c_uint64, err]),
         "gorch_cuda_sample_host": (i32, [p, p, i32, i64, i64, i64, p, p, p, p, err]),
         "gorch_cuda_sample_dev": (i32, [p, p, i32, i64, i64, i64, p, p, p, p, p, p, err]),
+        "gorch_cuda_sample_dev_static": (i32, [p, p, i32, i64, i64, i64, p, p, p, p, err]),
         "gorch_cuda_sample_row": (i64, [p, p, i64, f32, i64, f32, i32, f64, C.POINTER(C.c_uint32), err]),
         "gorch_cuda_argmax_host": (i32, [p, p, i32, i64, i64, i64, p, err]),
         "gorch_cuda_argmax_dev": (i32, [p, p, i32, i64, i64, i64, p, err]),

@@ -1264,7 +1264,7 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
 
 template <typename T>
 __global__ void __launch_bounds__(W_NT, 1) wide_rows_kernel(BatchArgs BA) {
-  extern __shared__ __align__(128) unsigned char dyn[];
+  extern __shared__ __align__(16) unsigned char dyn[];
   __shared__ WideShared sh;
   if (threadIdx.x < 256) sh.tab[threadIdx.x] = BA.k.exp_table[threadIdx.x];
   unsigned long long pol_keep, pol_drop;

@@ -55,6 +55,18 @@ struct Ctx {
   GorchCudaCounters counters{};
 };
 
+// Work lists for gorch_cuda_sample_dev_static: fixed storage inside the loaded module, so the
+// entry point never allocates. Every GPU that loads the library holds one copy (about 48 KB)
+// until the process exits. In host code this name is only a handle for cudaGetSymbolAddress;
+// the device address is looked up once per device (static_lists_ptr) and passed to the kernels.
+constexpr int64_t kStaticMaxRows = 4096;
+static __device__ __align__(256) int32_t g_static_worklists[16 + 3 * kStaticMaxRows + 1];
+constexpr int kMaxDevices = 64;
+int32_t* g_static_ptr[kMaxDevices] = {};
+
+// Device address of g_static_worklists on the CURRENT device (looked up on first use there).
+int static_lists_ptr(int device, int32_t** out, char** errOut);
+
 void set_err(char** errOut, const char* fmt, ...) {
   if (!errOut) return;
   char buf[512];
@@ -73,6 +85,20 @@ void set_err(char** errOut, const char* fmt, ...) {
       return GORCH_CUDA_ERR_CUDA;                                                \
     }                                                                            \
   } while (0)
+
+int static_lists_ptr(int device, int32_t** out, char** errOut) {
+  if (device < 0 || device >= kMaxDevices) {
+    set_err(errOut, "gorch_cuda: device index %d beyond the static table", device);
+    return GORCH_CUDA_ERR_LIMIT;
+  }
+  if (!g_static_ptr[device]) {
+    void* p = nullptr;
+    CUDA_TRY(cudaGetSymbolAddress(&p, g_static_worklists), errOut);
+    g_static_ptr[device] = static_cast<int32_t*>(p);
+  }
+  *out = g_static_ptr[device];
+  return GORCH_CUDA_OK;
+}
 
 int ensure(Scratch& s, size_t bytes, char** errOut) {
   if (bytes <= s.cap) return GORCH_CUDA_OK;
@@ -559,6 +585,76 @@ int gorch_cuda_argmax_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, in
   CUDA_TRY(cudaSetDevice(c->device), errOut);
   return launch_rows(c, logits, dtype, B, V, row_stride, nullptr, nullptr, out_ids, nullptr,
                      nullptr, nullptr, 1, errOut);
+}
+
+int gorch_cuda_sample_dev_static(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                                 int64_t V, int64_t row_stride, const GorchSampleCfg* cfgs,
+                                 const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
+                                 char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = check_shape(dtype, B, V, row_stride, errOut);
+  if (rc) return rc;
+  if (B == 0) return GORCH_CUDA_OK;
+  if (B > kStaticMaxRows) {
+    set_err(errOut, "gorch_cuda: gorch_cuda_sample_dev_static serves at most %lld rows per call, got %lld",
+            (long long)kStaticMaxRows, (long long)B);
+    return GORCH_CUDA_ERR_LIMIT;
+  }
+  if (!logits || !cfgs || !uniforms || !out_ids) {
+    set_err(errOut, "gorch_cuda: null pointer argument");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  if ((reinterpret_cast<uintptr_t>(logits) % elem_size(dtype)) != 0) {
+    set_err(errOut, "gorch_cuda: logits pointer not aligned to its element size");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  int32_t* base = nullptr;
+  if ((rc = static_lists_ptr(c->device, &base, errOut))) return rc;   // first call per device: symbol lookup
+  gs::BatchArgs ba;
+  ba.k.logits = logits;
+  ba.k.row_stride = row_stride;
+  ba.k.V = static_cast<int32_t>(V);
+  ba.k.force_greedy = 0;
+  ba.k.cfgs = reinterpret_cast<const gs::RowCfg*>(cfgs);
+  ba.k.uniforms = uniforms;
+  ba.k.out_ids = out_ids;
+  ba.k.out_flags = out_flags;
+  ba.k.out_probs = nullptr;
+  ba.k.out_debug = nullptr;
+  ba.k.exp_table = c->exp_table;
+  ba.k.row_offset = 0;
+  ba.k.worklist = nullptr;
+  ba.eb_table = c->eb_table;
+  ba.hdr = base;
+  ba.list_narrow = base + 16;
+  ba.list_wide = base + 16 + B;
+  ba.list_single = base + 16 + 2 * B;
+  ba.B = B;
+  // the lists keep the previous call's contents: the counters and cursors must start at zero
+  CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
+  CUDA_TRY(cudaMemsetAsync(ba.list_single, 0, sizeof(int32_t), c->stream), errOut);
+  gs::classify_rows_kernel<<<static_cast<unsigned>((B + 255) / 256), 256, 0, c->stream>>>(ba);
+  const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
+  const unsigned gw = static_cast<unsigned>(B < c->sm_count ? B : c->sm_count);
+  const unsigned gsgl = static_cast<unsigned>(B < 2 * c->sm_count ? B : 2 * c->sm_count);
+  gs::KernelArgs aw = ba.k;
+  aw.worklist = ba.list_single;
+  if (dtype == GORCH_CUDA_F32) {
+    gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
+    gs::wide_rows_kernel<float><<<gw, gs::W_NT, gs::W2_DYN_BYTES, c->stream>>>(ba);
+    gs::sample_rows_kernel<float><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
+  } else {
+    gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
+    gs::wide_rows_kernel<uint16_t><<<gw, gs::W_NT, gs::W2_DYN_BYTES, c->stream>>>(ba);
+    gs::sample_rows_kernel<uint16_t><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
+  }
+  CUDA_TRY(cudaGetLastError(), errOut);
+  c->counters.kernel_launches += 4;
+  c->counters.sample_launches++;
+  c->counters.rows += static_cast<uint64_t>(B);
+  return GORCH_CUDA_OK;
 }
 
 }  // extern "C"

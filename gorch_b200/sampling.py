@@ -215,6 +215,15 @@ class CudaSampler:
                 self._lib.gorch_cuda_buffer_free(b)
         return {"ids": ids, "flags": flags, "debug": dbg, "probs": probs}
 
+    def sample_dev_static_ptrs(self, logits_ptr: int, dtype: int, B: int, V: int, row_stride: int,
+                               cfgs_ptr: int, uniforms_ptr: int, ids_ptr: int, flags_ptr: int | None = None) -> None:
+        """gorch_cuda_sample_dev_static: device pointers in and out, no device allocation inside
+        (row work lists in a fixed array of the library image; at most 4096 rows per call)."""
+        err = C.c_void_p()
+        rc = self._lib.gorch_cuda_sample_dev_static(self._ctx, logits_ptr, dtype, B, V, row_stride,
+                                                    cfgs_ptr, uniforms_ptr, ids_ptr, flags_ptr, C.byref(err))
+        _check(self._lib, rc, err)
+
     def argmax_batch(self, logits) -> np.ndarray:
         x, dtype = _logits_arg(logits)
         B, V = x.shape

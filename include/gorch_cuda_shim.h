@@ -152,6 +152,26 @@ int gorch_cuda_sample_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, in
                           const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
                           double* out_probs, GorchSampleDebug* out_debug, char** errOut);
 
+/* No counterpart in the reference. Same work and same results as gorch_cuda_sample_dev
+ * (without the optional probability / diagnostic outputs), for callers that must not
+ * trigger a device allocation: a decode loop that is being recorded into a CUDA stream
+ * capture, where cudaMalloc is not permitted, or a serving process whose memory budget is
+ * fixed up front and that treats any later cudaMalloc (which also synchronises the device)
+ * as a fault. The row work lists that the other entry point keeps in a grow-only
+ * cudaMalloc'd buffer live here in a fixed array inside the library image: about 48 KB of
+ * device memory on every GPU that loads the library, held until the process exits.
+ *   - at most 4096 rows per call; more is refused with GORCH_CUDA_ERR_LIMIT;
+ *   - the first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call before starting a stream capture;
+ *   - all calls on a device share the one array: two calls whose kernels overlap on the
+ *     GPU (different streams or contexts) race on it. Calls on one stream are safe: the
+ *     counters are cleared at the start of every call;
+ *   - neither this function nor anything it calls uses cudaMalloc or cudaFree. */
+int gorch_cuda_sample_dev_static(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                                 int64_t V, int64_t row_stride, const GorchSampleCfg* cfgs,
+                                 const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
+                                 char** errOut);
+
 /* One row, the exact shape of the reference's calls: sample(logits,
  * temperature, topK, topP) (generate.go:147) with the uniform passed in, and
  * argmax when temperature == 0. Returns the token id, or -1 with *errOut set. */
