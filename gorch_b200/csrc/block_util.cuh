@@ -1,4 +1,4 @@
-// Block-wide reductions and scans for CTAs of NWARPS warps (sm_100a).
+// Block-wide reductions and scans for CTAs of NWARPS <= 32 warps (sm_100a).
 #pragma once
 
 #include "sample_common.cuh"
@@ -15,16 +15,16 @@ struct Scratch {
   int i1[32];
 };
 
+// Second level of every reduction below: each warp reads the NWARPS per-warp partials (one per
+// lane) and reduces them with shuffles, so a reduction costs one shared load per thread and
+// every thread ends with the same bits.
 template <int NWARPS>
 __device__ __forceinline__ double sum_d(double v, Scratch& s, int tid) {
   v = warp_sum_d(v);
   __syncthreads();
   if ((tid & 31) == 0) s.d0[tid >> 5] = v;
   __syncthreads();
-  double t = 0.0;
-#pragma unroll
-  for (int w = 0; w < NWARPS; w++) t += s.d0[w];
-  return t;
+  return warp_sum_d(((tid & 31) < NWARPS) ? s.d0[tid & 31] : 0.0);
 }
 
 // Three sums with one pair of barriers.
@@ -34,10 +34,10 @@ __device__ __forceinline__ void sum_d3(double& a, double& b, double& c, Scratch&
   __syncthreads();
   if ((tid & 31) == 0) { s.d0[tid >> 5] = a; s.d1[tid >> 5] = b; s.u[tid >> 5] = static_cast<unsigned long long>(__double_as_longlong(c)); }
   __syncthreads();
-  double ta = 0.0, tb = 0.0, tc = 0.0;
-#pragma unroll
-  for (int w = 0; w < NWARPS; w++) { ta += s.d0[w]; tb += s.d1[w]; tc += __longlong_as_double(static_cast<long long>(s.u[w])); }
-  a = ta; b = tb; c = tc;
+  const int l = tid & 31;
+  a = warp_sum_d((l < NWARPS) ? s.d0[l] : 0.0);
+  b = warp_sum_d((l < NWARPS) ? s.d1[l] : 0.0);
+  c = warp_sum_d((l < NWARPS) ? __longlong_as_double(static_cast<long long>(s.u[l])) : 0.0);
 }
 
 template <int NWARPS>
@@ -46,10 +46,7 @@ __device__ __forceinline__ int sum_i(int v, Scratch& s, int tid) {
   __syncthreads();
   if ((tid & 31) == 0) s.i0[tid >> 5] = v;
   __syncthreads();
-  int t = 0;
-#pragma unroll
-  for (int w = 0; w < NWARPS; w++) t += s.i0[w];
-  return t;
+  return __reduce_add_sync(FULL, ((tid & 31) < NWARPS) ? s.i0[tid & 31] : 0);
 }
 
 template <int NWARPS>
@@ -58,10 +55,7 @@ __device__ __forceinline__ int min_i(int v, Scratch& s, int tid) {
   __syncthreads();
   if ((tid & 31) == 0) s.i0[tid >> 5] = v;
   __syncthreads();
-  int t = s.i0[0];
-#pragma unroll
-  for (int w = 1; w < NWARPS; w++) t = min(t, s.i0[w]);
-  return t;
+  return __reduce_min_sync(FULL, s.i0[(tid & 31) < NWARPS ? (tid & 31) : 0]);
 }
 
 template <int NWARPS>
@@ -70,10 +64,7 @@ __device__ __forceinline__ int max_i(int v, Scratch& s, int tid) {
   __syncthreads();
   if ((tid & 31) == 0) s.i0[tid >> 5] = v;
   __syncthreads();
-  int t = s.i0[0];
-#pragma unroll
-  for (int w = 1; w < NWARPS; w++) t = max(t, s.i0[w]);
-  return t;
+  return __reduce_max_sync(FULL, s.i0[(tid & 31) < NWARPS ? (tid & 31) : 0]);
 }
 
 // Two minima with one pair of barriers.
@@ -84,26 +75,26 @@ __device__ __forceinline__ void min_i2(int& a, int& b, Scratch& s, int tid) {
   __syncthreads();
   if ((tid & 31) == 0) { s.i0[tid >> 5] = a; s.i1[tid >> 5] = b; }
   __syncthreads();
-  int ta = s.i0[0], tb = s.i1[0];
-#pragma unroll
-  for (int w = 1; w < NWARPS; w++) { ta = min(ta, s.i0[w]); tb = min(tb, s.i1[w]); }
-  a = ta; b = tb;
+  const int l = (tid & 31) < NWARPS ? (tid & 31) : 0;
+  a = __reduce_min_sync(FULL, s.i0[l]);
+  b = __reduce_min_sync(FULL, s.i1[l]);
 }
 
-template <int NWARPS>
-__device__ __forceinline__ unsigned long long max_u64(unsigned long long v, Scratch& s, int tid) {
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    unsigned long long t = __shfl_xor_sync(FULL, v, o);
+    const unsigned long long t = __shfl_xor_sync(FULL, v, o);
     v = t > v ? t : v;
   }
+  return v;
+}
+template <int NWARPS>
+__device__ __forceinline__ unsigned long long max_u64(unsigned long long v, Scratch& s, int tid) {
+  v = warp_max_u64(v);
   __syncthreads();
   if ((tid & 31) == 0) s.u[tid >> 5] = v;
   __syncthreads();
-  unsigned long long t = s.u[0];
-#pragma unroll
-  for (int w = 1; w < NWARPS; w++) t = s.u[w] > t ? s.u[w] : t;
-  return t;
+  return warp_max_u64(s.u[(tid & 31) < NWARPS ? (tid & 31) : 0]);
 }
 template <int NWARPS>
 __device__ __forceinline__ unsigned long long min_u64(unsigned long long v, Scratch& s, int tid) {
@@ -118,14 +109,10 @@ __device__ __forceinline__ double scan_excl_d(double v, double& total, Scratch& 
   __syncthreads();
   if (lane == 31) s.d0[w] = incl;
   __syncthreads();
-  double base = 0.0, tot = 0.0;
-#pragma unroll
-  for (int j = 0; j < NWARPS; j++) {
-    const double x = s.d0[j];
-    if (j < w) base += x;
-    tot += x;
-  }
-  total = tot;
+  const double wv = (lane < NWARPS) ? s.d0[lane] : 0.0;
+  const double wi = warp_scan_incl_d(wv, lane);
+  total = __shfl_sync(FULL, wi, NWARPS - 1);
+  const double base = __shfl_sync(FULL, wi - wv, w);
   return base + incl - v;
 }
 
@@ -138,14 +125,11 @@ __device__ __forceinline__ void scan_excl_d2(double a, double b, double& ea, dou
   __syncthreads();
   if (lane == 31) { s.d0[w] = ia; s.d1[w] = ib; }
   __syncthreads();
-  double ba = 0, bb = 0, sa = 0, sb = 0;
-#pragma unroll
-  for (int j = 0; j < NWARPS; j++) {
-    const double va = s.d0[j], vb = s.d1[j];
-    if (j < w) { ba += va; bb += vb; }
-    sa += va; sb += vb;
-  }
-  ea = ba + ia - a; eb = bb + ib - b; ta = sa; tb = sb;
+  const double wa = (lane < NWARPS) ? s.d0[lane] : 0.0, wb = (lane < NWARPS) ? s.d1[lane] : 0.0;
+  const double sa = warp_scan_incl_d(wa, lane), sb = warp_scan_incl_d(wb, lane);
+  ta = __shfl_sync(FULL, sa, NWARPS - 1); tb = __shfl_sync(FULL, sb, NWARPS - 1);
+  ea = __shfl_sync(FULL, sa - wa, w) + ia - a;
+  eb = __shfl_sync(FULL, sb - wb, w) + ib - b;
 }
 
 // k-th largest (with multiplicity) of the float bit patterns list[j].x, j < n, by

@@ -1,0 +1,805 @@
+// wide_rows_kernel: rows whose softmax runs over the whole vocabulary (top-k off).
+//
+// 1024 threads, one persistent CTA per SM, one row at a time per CTA. Warp w owns one
+// contiguous span of the row (1/32 of it, rounded up to whole steps); in a step every lane
+// handles eight logits (two 16-byte vectors of f32, one of bf16), loaded straight into
+// registers one or two steps ahead of their use. Nothing is shared between threads inside a
+// pass, so a pass contains no barrier; the loads go through L2 (cache hints: keep in pass 1,
+// evict first in pass 3), where the later passes find the row again.
+//
+//   sample                     the first step of every warp: an upper estimate (anchor) of the
+//                              row's maximum and its range
+//   pass 1 (HBM)               max, min, NaN; with an active top-p cut also the count histogram
+//                              over 4096 linear buckets of s - anchor, whose width is the power
+//                              of two that covers the estimated range
+//   bracket                    count-based lower/upper mass bounds bracket the cut to a zone of
+//                              buckets (a maximum above the anchor: pass 2 recounts exactly)
+//   pass 3 (L2)                exponentials. Mass of d >= dA (certainly kept) per piece of
+//                              four steps, zone logits (dB <= d < dA) into an exact list
+//   tail                       weighted selection inside the zone, prefix over the pieces,
+//                              rescan of the one piece that holds the drawn token
+//
+// Row semantics: model/generate.go:147-240 (mode A), model/qwen/generate.go:92-153 (mode B).
+#pragma once
+
+#include "sample_batch.cuh"
+
+namespace gs {
+
+#ifndef GS_W_NT
+#define GS_W_NT 512
+#endif
+constexpr int W_NT = GS_W_NT;           // threads per CTA
+constexpr int W_CTAS = 1024 / W_NT;     // CTAs per SM
+constexpr int W_NSUB = W_NT;            // sub-buckets of one weighted-selection round
+constexpr int W_NW = W_NT / 32;
+constexpr int W_NB = 4096;              // histogram buckets
+constexpr int W_ZCAP = 2048;            // exact zone list capacity
+constexpr int W_G = 4;                  // steps per piece (power of two)
+constexpr int W_MAX_STEPS = 64;         // steps per warp and pass; longer rows go to the single-CTA kernel
+constexpr int W_MAX_PPW = W_MAX_STEPS / W_G;
+constexpr int W_MAX_PIECES = W_NW * W_MAX_PPW;                 // 512
+constexpr int W_EB_REP = 16;            // copies of a table entry in the conflict-free layout
+constexpr int W_EB_REP_ENTRIES = 128;   // entries of that layout: d > -(128-1)/32
+constexpr int W_OFF_HIST = 0;
+constexpr int W_OFF_ZONE = W_OFF_HIST + W_NB * 4;
+constexpr int W_OFF_EB = W_OFF_ZONE + W_ZCAP * 8;              // 1024 entries, or 128 entries x 16 copies
+constexpr int W_OFF_PART = W_OFF_EB + W_EB_REP * W_EB_REP_ENTRIES * 8;
+constexpr int W_DYN_BYTES = W_OFF_PART + W_MAX_PIECES * 8;     // 52 KB
+static_assert(W_EB_REP * W_EB_REP_ENTRIES >= NB1, "either layout fits");
+static_assert(W_MAX_PIECES <= W_NT && W_G * 64 <= W_NT && W_NSUB * 12 <= W_NB * 4, "piece prefix and sub-bucket arrays");
+
+// Histogram buckets of width 1/scale (scale a power of two): bucket = round(-d * scale),
+// clamped to W_NB - 1. Multiplying by a power of two is exact, so the bucket edges are exact.
+__device__ __forceinline__ int bucket_w(float d, float scale, float dclamp) {
+  const float f = fmaf(fmaxf(d, dclamp), -scale, 8388608.0f);
+  return __float_as_int(f) & 0x1fff;
+}
+// smallest d whose bucket is <= bmax (the edge is a tie that rounds to even)
+__device__ __forceinline__ float bucket_floor_w(int bmax, float scale, float dclamp) {
+  if (bmax >= W_NB - 1) return -INFINITY;
+  if (bmax < 0) return INFINITY;
+  const float t = -(static_cast<float>(2 * bmax + 1) * (0.5f / scale));
+  return (bucket_w(t, scale, dclamp) <= bmax) ? t : __uint_as_float(__float_as_uint(t) - 1u);
+}
+
+__device__ __forceinline__ uint4 ldg_hint(const uint4* p, unsigned long long pol) {
+  uint4 v;
+  asm volatile("ld.global.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol));
+  return v;
+}
+__device__ __forceinline__ double lds_f64(uint32_t addr) {
+  double v;
+  asm("ld.shared.f64 %0, [%1];" : "=d"(v) : "r"(addr));
+  return v;
+}
+// exp(d) for -31.9 < d <= 0 from the table E[b] = exp(-b/32) in shared memory: d = -b/32 + dl with
+// |dl| <= 1/64 exactly (f32), exp = E[b] * (1 + w), w = dl + dl^2/2 + ... + dl^5/120 in f32. The one
+// rounding of w (at most 2^-31 relative to the result, unbiased) is the error that matters.
+// The bits of f are 0x4B000000 + b, so bits * eb_mul + eb_bias is the address of E[b] (mod 2^32)
+// with eb_mul = 8 and eb_bias = table - 0x4B000000 * 8 for the plain table. In the conflict-free
+// layout (rows whose d stay above -(W_EB_REP_ENTRIES-1)/32) entry b has sixteen copies 8 bytes
+// apart and lane l reads copy l mod 16, its own pair of banks: eb_mul = 128, eb_bias = table +
+// 8 (l mod 16) - 0x4B000000 * 128.
+__device__ __forceinline__ double exp_fast_s(float d, uint32_t eb_mul, uint32_t eb_bias) {
+  const float f = fmaf(d, -32.0f, 8388608.0f);
+  const float dl = fmaf(f - 8388608.0f, 0.03125f, d);
+  float t = fmaf(dl, 8.3333338e-3f, 4.1666668e-2f);
+  t = fmaf(t, dl, 1.6666667e-1f);
+  t = fmaf(t, dl, 0.5f);
+  const float w = fmaf(t, dl * dl, dl);
+  const double E = lds_f64(__float_as_uint(f) * eb_mul + eb_bias);
+  return fma(E, static_cast<double>(w), E);
+}
+constexpr double W_EXP_REL_ERR = 6e-10;   // bound of exp_fast_s against the exact exponential
+
+// What one thread needs to stream its warp's span of a row.
+struct WSpan {
+  const uint4* lane_src;   // this lane's first vector: row vector (first + lane)
+  int first;               // first vector of the warp's span
+  int rel;                 // vectors from lane_src to the row's end (<= 0: none)
+  int nst;                 // steps this warp runs
+  int omax;                // largest valid vector offset from lane_src
+  int clean_lo, clean_hi;  // steps [clean_lo, clean_hi) hold no logit outside the row (warp-uniform)
+};
+
+// The lane's vectors of step st. A vector past the row's end is replaced by the lane's last one
+// (or the row's first when the lane has none): always a valid address, and such vectors are
+// masked by the caller from their true index.
+template <typename T>
+__device__ __forceinline__ void w_load(const WSpan& sp, int st, unsigned long long pol, uint4& ra, uint4& rb) {
+  constexpr int EPI = 8 / Elem<T>::VEC, SV = 32 * EPI;
+  const int o = st * SV;
+  ra = ldg_hint(sp.lane_src + min(o, sp.omax), pol);
+  if (EPI == 2) rb = ldg_hint(sp.lane_src + min(o + 32, sp.omax), pol);
+  else rb = ra;
+}
+
+// Steps [st0, st1) of one pass; qa/qb hold the vectors of steps st0 .. st0+D-1 on entry and of
+// st1 .. st1+D-1 on exit (D steps of register prefetch). CLEAN runs hold no logit outside the
+// row and skip all masking; the others (a warp's step that holds the row's first or last vector,
+// or vectors past the end) give every logit outside the row the value -Inf and a clear bit in
+// `valid`. body(x, valid, st, gv): eight logits of this lane, validity bits, step, the lane's
+// first vector.
+template <typename T, int D, bool CLEAN, typename F>
+__device__ __forceinline__ void wide_steps(const WSpan& sp, const RowView<T>& rv, unsigned long long pol, int lane,
+                                           int st0, int st1, uint4 (&qa)[D], uint4 (&qb)[D], F&& body) {
+  constexpr int VEC = Elem<T>::VEC, EPI = 8 / VEC, SV = 32 * EPI;
+#pragma unroll 1
+  for (int st = st0; st < st1; st++) {
+    uint4 na, nb;
+    w_load<T>(sp, st + D, pol, na, nb);
+    float x[8];
+    if (EPI == 2) { Elem<T>::unpack(qa[0], x); Elem<T>::unpack(qb[0], x + 4 * (EPI - 1)); }
+    else Elem<T>::unpack(qa[0], x);
+#pragma unroll
+    for (int k = 0; k + 1 < D; k++) { qa[k] = qa[k + 1]; qb[k] = qb[k + 1]; }
+    qa[D - 1] = na; qb[D - 1] = nb;
+    const int gv = sp.first + st * SV + lane;
+    uint32_t valid = 0xffu;
+    if (!CLEAN) {
+      valid = 0u;
+#pragma unroll
+      for (int h = 0; h < EPI; h++) {
+        const int g = gv + 32 * h;
+        const int i0 = g * VEC - rv.shift;
+#pragma unroll
+        for (int c = 0; c < VEC; c++) {
+          const int i = i0 + c;
+          if (g < rv.nvec && i >= 0 && i < rv.V) valid |= 1u << (h * VEC + c);
+          else x[h * VEC + c] = -INFINITY;
+        }
+      }
+    }
+    body(x, valid, st, gv);
+  }
+}
+// One pass over the warp's span with D steps of prefetch: runs of clean and other steps, in order.
+#define GS_WIDE_STREAM(T, D, sp, rv, pol, lane, BODY)                                           \
+  do {                                                                                          \
+    uint4 qa_[D], qb_[D];                                                                       \
+    _Pragma("unroll") for (int s_ = 0; s_ < D; s_++) w_load<T>(sp, s_, pol, qa_[s_], qb_[s_]);  \
+    if (sp.clean_lo > 0) wide_steps<T, D, false>(sp, rv, pol, lane, 0, sp.clean_lo, qa_, qb_, BODY(false)); \
+    wide_steps<T, D, true>(sp, rv, pol, lane, sp.clean_lo, sp.clean_hi, qa_, qb_, BODY(true));  \
+    if (sp.clean_hi < sp.nst) wide_steps<T, D, false>(sp, rv, pol, lane, sp.clean_hi, sp.nst, qa_, qb_, BODY(false)); \
+  } while (0)
+
+// pass 1: max, min, NaN flag over the row's logits. With HIST it also counts the logits into the
+// histogram of q = s - anchor (an upper estimate of the row's maximum taken from a sample), so that
+// rows whose maximum stays below the anchor need no second pass for their histogram.
+template <typename T, bool HIST, bool TONE>
+__device__ __noinline__ void wide_pass1(const WSpan& sp_in, const RowView<T>& rv_in, unsigned long long pol, int lane,
+                                        uint32_t hist_bias, float anchor, float Tm, float scale, float dclamp,
+                                        float& xmax, float& xmin, bool& nan_seen) {
+  const WSpan sp = sp_in;                // registers, not memory, inside the loop
+  const RowView<T> rv = rv_in;
+  float vmax = -INFINITY, vmin = INFINITY;
+  uint32_t amax = 0u;                    // largest |bits|: above 0x7f800000 means a NaN
+#define GS_BODY1(CL) [&](const float* x, uint32_t valid, int, int) {                             \
+    _Pragma("unroll") for (int c = 0; c < 8; c++) {                                              \
+      vmax = fmaxf(vmax, x[c]);                                                                  \
+      vmin = fminf(vmin, (CL || ((valid >> c) & 1u)) ? x[c] : INFINITY);                         \
+      amax = max(amax, __float_as_uint(x[c]) & 0x7fffffffu);                                     \
+      if (HIST) {                                                                                \
+        const float s = TONE ? x[c] : __fdiv_rn(x[c], Tm);                                       \
+        /* NaN and anything above the anchor land in bucket 0 or W_NB-1: such rows are redone */ \
+        const float f = fmaf(fminf(fmaxf(s - anchor, dclamp), 0.0f), -scale, 8388608.0f);        \
+        const uint32_t a = __float_as_uint(f) * 4u + hist_bias;                                  \
+        if (CL || ((valid >> c) & 1u)) asm volatile("red.shared.add.u32 [%0], 1;" :: "r"(a) : "memory"); \
+      }                                                                                          \
+    } }
+  GS_WIDE_STREAM(T, 2, sp, rv, pol, lane, GS_BODY1);
+#undef GS_BODY1
+  xmax = vmax; xmin = vmin; nan_seen = amax > 0x7f800000u;
+}
+
+// pass 2: count histogram of d (logits outside the row are not counted).
+// hist_bias = shared address of the histogram - 0x4B000000 * 4 (mod 2^32): see exp_fast_s.
+template <typename T, bool TONE>
+__device__ __noinline__ void wide_pass2(const WSpan& sp_in, const RowView<T>& rv_in, unsigned long long pol, int lane,
+                                        uint32_t hist_bias, float m, float Tm, float scale, float dclamp) {
+  const WSpan sp = sp_in;
+  const RowView<T> rv = rv_in;
+#define GS_BODY2(CL) [&](const float* x, uint32_t valid, int, int) {                             \
+    _Pragma("unroll") for (int c = 0; c < 8; c++) {                                              \
+      const float s = TONE ? x[c] : __fdiv_rn(x[c], Tm);                                         \
+      const float f = fmaf(fmaxf(s - m, dclamp), -scale, 8388608.0f);                            \
+      const uint32_t a = __float_as_uint(f) * 4u + hist_bias;                                    \
+      if (CL || ((valid >> c) & 1u)) asm volatile("red.shared.add.u32 [%0], 1;" :: "r"(a) : "memory"); \
+    } }
+  GS_WIDE_STREAM(T, 1, sp, rv, pol, lane, GS_BODY2);
+#undef GS_BODY2
+}
+
+// pass 3: exponentials. part[warp * ppw + piece] receives the certainly-kept mass (d >= dA) of
+// each piece of W_G steps; zone logits (dB <= d < dA) go to the list zl. The lane-private sum of
+// all mass comes back in Ssum, the kept mass of the warp's pieces in lane 0's Ksum.
+// FAST: every logit of the row has d > -31.9 (bucket-table exponential, no range check);
+// TONE: temperature 1; CUT: a top-p cut is active.
+template <typename T, bool FAST, bool TONE, bool CUT>
+__device__ __noinline__ void wide_pass3(const WSpan& sp_in, const RowView<T>& rv_in, unsigned long long pol, int lane, int warp,
+                                        float m, float Tm, float dA, float dB, uint32_t eb_mul, uint32_t eb_bias, const double* s_tab,
+                                        double* part, int ppw, uint2* zl, int* zcnt, double& Ssum, double& Ksum) {
+  constexpr int VEC = Elem<T>::VEC;
+  const WSpan sp = sp_in;
+  const RowView<T> rv = rv_in;
+  // |d - dmid| <= dhalf is a superset of the zone dB <= d < dA (infinite ends are clamped)
+  const float dAc = fminf(dA, 3.0e38f), dBc = fmaxf(dB, -3.0e38f);
+  const float dmid = 0.5f * dAc + 0.5f * dBc;
+  const float dhalf = (0.5f * dAc - 0.5f * dBc) * 1.000001f + 1e-30f;
+  const bool none_kept = CUT && (dA == INFINITY);
+  const float dfloor = (eb_mul == 8u) ? -31.9f : -(W_EB_REP_ENTRIES - 1.5f) / 32.0f;   // keeps masked logits inside the table
+  double t0 = 0.0, t1 = 0.0, sub = 0.0;
+  double stot = 0.0, ksum = 0.0;
+#define GS_BODY3(CL) [&](const float* x, uint32_t valid, int st, int gv) {                       \
+    float nearest = INFINITY;                                                                    \
+    _Pragma("unroll") for (int c = 0; c < 8; c++) {                                              \
+      const float s = TONE ? x[c] : __fdiv_rn(x[c], Tm);                                         \
+      const float d = s - m;                                                                     \
+      double e;                                                                                  \
+      if (FAST) {                                                                                \
+        e = exp_fast_s(CL ? d : fmaxf(d, dfloor), eb_mul, eb_bias);                                      \
+        if (!CL) e = __hiloint2double(((valid >> c) & 1u) ? __double2hiint(e) : 0, ((valid >> c) & 1u) ? __double2loint(e) : 0); \
+      } else {                                                                                   \
+        e = exp_safe(d, s_tab);                              /* exp_safe(-Inf) is exactly 0 */   \
+      }                                                                                          \
+      if (c & 1) t1 += e; else t0 += e;                                                          \
+      if (CUT) {                                                                                 \
+        sub = fma(e, __hiloint2double((d < dA) ? 0x3ff00000 : 0, 0), sub);                       \
+        nearest = fminf(nearest, fabsf(d - dmid));                                               \
+      }                                                                                          \
+    }                                                                                            \
+    if (CUT && nearest <= dhalf) {                           /* rare: a logit of this lane near the zone */ \
+      _Pragma("unroll") for (int c = 0; c < 8; c++) {                                            \
+        const float s = TONE ? x[c] : __fdiv_rn(x[c], Tm);                                       \
+        const float d = s - m;                                                                   \
+        if ((CL || ((valid >> c) & 1u)) && d < dA && d >= dB) {                                  \
+          const int i = (gv + 32 * (c / VEC)) * VEC - rv.shift + (c % VEC);                      \
+          const int slot = atomicAdd(zcnt, 1);                                                   \
+          if (slot < W_ZCAP) zl[slot] = make_uint2(__float_as_uint(d), static_cast<uint32_t>(i)); \
+        }                                                                                        \
+      }                                                                                          \
+    }                                                                                            \
+    if ((st & (W_G - 1)) == W_G - 1 || st == sp.nst - 1) {   /* end of a piece */                \
+      const double tot = t0 + t1;                                                                \
+      /* With dA = +Inf nothing is certainly kept (exactly 0); otherwise the subtraction's */    \
+      /* rounding is far below the row maximum's own mass. */                                    \
+      double kw = none_kept ? 0.0 : tot - sub;                                                   \
+      kw = warp_sum_d(kw);                                                                       \
+      stot += tot;                                                                               \
+      if (lane == 0) { part[warp * ppw + (st / W_G)] = kw; ksum += kw; }                         \
+      t0 = t1 = 0.0; sub = 0.0;                                                                  \
+    } }
+  GS_WIDE_STREAM(T, 1, sp, rv, pol, lane, GS_BODY3);
+#undef GS_BODY3
+  Ssum = stot; Ksum = ksum;
+}
+
+struct WideShared {
+  bu::Scratch sc;
+  double tab[256];
+  double bcd[4];
+  int bc[4];
+  int cnt;
+  int row;
+};
+
+template <typename T>
+__device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned char* dyn, WideShared& sh,
+                         unsigned long long pol_keep, unsigned long long pol_drop) {
+  const KernelArgs& A = BA.k;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int V = A.V;
+  constexpr int VEC = Elem<T>::VEC;
+  constexpr int SV = 32 * (8 / VEC);                         // vectors of one warp-step
+  constexpr int PV = W_G * SV;                               // vectors of one piece
+  const T* row = static_cast<const T*>(A.logits) + row_id * A.row_stride;
+  RowView<T> rv;
+  rv.init(row, V);
+  bu::Scratch& sc = sh.sc;
+  const double* s_tab = sh.tab;
+  uint32_t* hist = reinterpret_cast<uint32_t*>(dyn + W_OFF_HIST);
+  uint2* zl = reinterpret_cast<uint2*>(dyn + W_OFF_ZONE);
+  unsigned long long* zk = reinterpret_cast<unsigned long long*>(dyn + W_OFF_ZONE);
+  double* ebs = reinterpret_cast<double*>(dyn + W_OFF_EB);
+  double* part = reinterpret_cast<double*>(dyn + W_OFF_PART);   // [warp][piece] kept mass, row order
+  const double QNAN = __longlong_as_double(0x7ff8000000000000ll);
+
+  const RowCfg cfg = A.cfgs[row_id];
+  const float Tm = cfg.temperature;
+  const bool topp_on = (cfg.top_p > 0.0f && cfg.top_p < 1.0f);
+  const int mode = cfg.topp_mode;
+  const double u = A.uniforms[row_id];
+  const double plim = (mode == 0) ? static_cast<double>(cfg.top_p) * 1.5 : static_cast<double>(cfg.top_p);
+  // mode A prunes only while the mass exceeds 1.5p; the mass starts at 1 up to ~1e-11 of rounding
+  // and 1.5*float(p) is never that close to 1
+  const bool cut_on = topp_on && !(mode == 0 && plim >= 1.0);
+  const bool t_is_one = (Tm == 1.0f);
+  uint32_t flags = FLAG_GENERAL_PATH;
+  RowDebug dbg;
+  dbg.sum_exp = 0; dbg.resum = 1.0; dbg.edge_lo = 0; dbg.edge_hi = 0; dbg.kept = 0;
+  dbg.max_scaled = 0; dbg.threshold = __int_as_float(0x7fc00000); dbg.path = 2;
+  for (int q = 0; q < 8; q++) dbg.cycles[q] = 0;
+  long long tprev = clock64();
+  auto stamp = [&](int slot) { const long long now = clock64(); dbg.cycles[slot] = static_cast<uint32_t>(now - tprev); tprev = now; };
+  auto write_row = [&](int id, uint32_t fl) {
+    if (tid == 0) {
+      A.out_ids[row_id] = id;
+      if (A.out_flags) A.out_flags[row_id] = fl;
+      if (A.out_debug) A.out_debug[row_id] = dbg;
+    }
+  };
+  auto fill_probs_row = [&](double v) {
+    if (A.out_probs) {
+      double* pr = A.out_probs + row_id * static_cast<int64_t>(V);
+      for (int i = tid; i < V; i += W_NT) pr[i] = v;
+    }
+  };
+
+  // the warp's span: 1/32 of the row, rounded up to whole steps
+  const int span = (((rv.nvec + W_NW - 1) / W_NW + SV - 1) / SV) * SV;
+  const int steps_max = span / SV;
+  if (steps_max > W_MAX_STEPS) {
+    if (tid == 0) hand_to_single(BA, row_id);
+    return;
+  }
+  const int ppw = (steps_max + W_G - 1) / W_G;               // pieces per warp
+  const int npiece = W_NW * ppw;
+  WSpan sp;
+  sp.first = warp * span;
+  {
+    const int end = min(rv.nvec, sp.first + span);
+    sp.nst = (end > sp.first) ? (end - sp.first + SV - 1) / SV : 0;
+  }
+  sp.rel = rv.nvec - sp.first - lane;
+  sp.lane_src = rv.vbase + (sp.rel > 0 ? sp.first + lane : 0);
+  sp.omax = max(sp.rel - 1, 0);
+  // a step is clean when all its SV vectors exist and none is the row's first or last
+  sp.clean_lo = (sp.first == 0) ? min(1, sp.nst) : 0;
+  sp.clean_hi = max(sp.clean_lo, min(sp.nst, (rv.nvec - 1 - sp.first) / SV));
+
+  // ---- a sample of the row (every warp's first step) gives an upper estimate of the maximum
+  // and the bucket width, so that pass 1 can already count the histogram the cut needs
+  bool anchored = false;
+  float anchor = 0.0f, scale = 128.0f, width = 0.0078125f, dclamp = -31.99f;
+  auto set_scale = [&](float range) {      // power of two (1/128 .. 1/65536) at which `range` just fits
+    int jexp = 7;
+    const float q = 4094.0f / range;                         // +Inf for range 0, 0 for an infinite range
+    if (q >= 65536.0f) jexp = 16; else if (q >= 128.0f) jexp = ilogbf(q);
+    scale = __int_as_float((127 + jexp) << 23);
+    width = 1.0f / scale;
+    dclamp = -4095.4f * width;
+  };
+  if (cut_on) {
+    for (int j = tid; j < W_NB; j += W_NT) hist[j] = 0;
+    float smax = -INFINITY, smin = INFINITY;
+    bool snan = false;
+#pragma unroll
+    for (int h = 0; h < 8 / VEC; h++) {
+      const int g = sp.first + 32 * h + lane;
+      if (sp.nst > 0 && g < rv.nvec) rv.visit(g, [&](float xv, int) { smax = fmaxf(smax, xv); smin = fminf(smin, xv); snan |= (xv != xv); });
+    }
+    const int bad_sample = bu::max_i<W_NW>(snan ? 1 : 0, sc, tid);
+    smax = okey_to_float(static_cast<uint32_t>(bu::max_u64<W_NW>(static_cast<unsigned long long>(okey(smax)), sc, tid)));
+    smin = okey_to_float(static_cast<uint32_t>(bu::min_u64<W_NW>(static_cast<unsigned long long>(okey(smin)), sc, tid)));
+    const float s_hi = scale_t(smax, Tm), s_lo = scale_t(smin, Tm);
+    const float r0 = s_hi - s_lo;
+    if (!bad_sample && r0 >= 0.0f && r0 < 1e30f && fabsf(s_hi) < 1e30f) {
+      const float margin = fmaxf(0.25f * r0, 1e-3f * fmaxf(1.0f, fabsf(s_hi)));
+      anchor = s_hi + margin;
+      set_scale(r0 + 2.0f * margin);
+      anchored = true;
+    }
+  }
+
+  // ---- pass 1: max, min, NaN (from HBM; L2 is asked to keep the row)
+  float xmax = -INFINITY, xmin = INFINITY;
+  bool nan_seen = false;
+  {
+    const uint32_t hb = smem_addr(hist) - 0x4B000000u * 4u;
+    if (!anchored) wide_pass1<T, false, true>(sp, rv, pol_keep, lane, hb, anchor, Tm, scale, dclamp, xmax, xmin, nan_seen);
+    else if (t_is_one) wide_pass1<T, true, true>(sp, rv, pol_keep, lane, hb, anchor, Tm, scale, dclamp, xmax, xmin, nan_seen);
+    else wide_pass1<T, true, false>(sp, rv, pol_keep, lane, hb, anchor, Tm, scale, dclamp, xmax, xmin, nan_seen);
+  }
+  __syncthreads();
+  const int anynan = bu::max_i<W_NW>(nan_seen ? 1 : 0, sc, tid);
+  xmax = okey_to_float(static_cast<uint32_t>(bu::max_u64<W_NW>(static_cast<unsigned long long>(okey(xmax)), sc, tid)));
+  xmin = okey_to_float(static_cast<uint32_t>(bu::min_u64<W_NW>(static_cast<unsigned long long>(okey(xmin)), sc, tid)));
+  const float m = scale_t(xmax, Tm);
+  dbg.max_scaled = m;
+  stamp(0);
+  // A NaN anywhere, or an infinite maximum, makes the softmax sum NaN upstream
+  // (generate.go:173-181): every comparison of the walk fails, result n-1 (:239).
+  if (anynan || !(fabsf(m) < INFINITY)) {
+    fill_probs_row(QNAN);
+    dbg.sum_exp = QNAN;
+    write_row(V - 1, flags | FLAG_NONFINITE | FLAG_FALLBACK);
+    return;
+  }
+  const float dlow = scale_t(xmin, Tm) - m;                  // smallest d of the row (-Inf with a -Inf logit)
+  const bool fast_ok = (dlow > -31.9f);                      // every d inside the bucket table's range
+
+  // ---- bracket of the cut from the count histogram
+  float dA = -INFINITY, dB = -INFINITY;    // certainly kept: d >= dA; zone: dB <= d < dA; dropped: d < dB
+  if (cut_on) {
+    // The histogram of pass 1 counts q = s - anchor; it stands when no logit lies above the anchor.
+    // Mass bounds relative to exp(anchor) serve as well as bounds relative to exp(max): only their
+    // ratios are used. q and d are each rounded once, so a logit's true mass can differ from
+    // exp(q) exp(anchor - max) by the factor exp(+-2^-24 * 64): `slack` covers it.
+    double slack = 1e-5;
+    if (!(anchored && m <= anchor)) {
+      anchored = false;
+      slack = 1e-7;
+      set_scale(-dlow);
+      __syncthreads();
+      for (int j = tid; j < W_NB; j += W_NT) hist[j] = 0;
+      __syncthreads();
+      if (t_is_one) wide_pass2<T, true>(sp, rv, pol_keep, lane, smem_addr(hist) - 0x4B000000u * 4u, m, Tm, scale, dclamp);
+      else wide_pass2<T, false>(sp, rv, pol_keep, lane, smem_addr(hist) - 0x4B000000u * 4u, m, Tm, scale, dclamp);
+    }
+    __syncthreads();
+    constexpr int PER = W_NB / W_NT;                         // buckets per thread
+    double lo_inc[PER], hi_inc[PER];
+    int cb[PER];
+    double slo = 0.0, shi = 0.0;
+    {
+      // bucket b holds q (or d) in [-(b+.5) width, -(b-.5) width], the last one everything below.
+      // Its members' masses lie between edge(b+1) and edge(b), edge(k) = exp(-(k-.5) width): one
+      // exponential per thread, the next edges by the common ratio (rounding far inside `slack`).
+      const double ratio = exp_safe(-width, s_tab);
+      double edge = exp_safe(-(tid * PER - 0.5f) * width, s_tab);
+#pragma unroll
+      for (int j = 0; j < PER; j++) {
+        const int b = tid * PER + j;
+        cb[j] = static_cast<int>(hist[b]);
+        const double c = static_cast<double>(cb[j]);
+        const double ehi = fmin(edge, 1.0) * (1.0 + slack);
+        edge *= ratio;
+        const double elo = (b == W_NB - 1) ? 0.0 : edge * (1.0 - slack);
+        slo += c * elo; shi += c * ehi;
+        lo_inc[j] = slo; hi_inc[j] = shi;
+      }
+    }
+    double ex_lo, ex_hi, tot_lo, tot_hi;
+    bu::scan_excl_d2<W_NW>(slo, shi, ex_lo, ex_hi, tot_lo, tot_hi, sc, tid);
+    int b1 = W_NB - 1, b2 = W_NB - 1;
+    const double p_lo = plim * (1.0 - 1e-9), p_hi = plim * (1.0 + 1e-9);
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+      const int b = tid * PER + j;
+      const double a_lo = ex_lo + lo_inc[j], a_hi = ex_hi + hi_inc[j];
+      // largest / smallest possible mass fraction through bucket b against the limit, as products
+      const double den_hi = a_hi + (tot_lo - a_lo), den_lo = a_lo + (tot_hi - a_hi);
+      bool c1, c2;
+      if (mode == 0) { c1 = a_hi > p_lo * den_hi; c2 = a_lo > p_hi * den_lo; }
+      else           { c1 = a_hi >= p_lo * den_hi; c2 = a_lo >= p_hi * den_lo; }
+      if (c1 && a_hi > 0.0) b1 = min(b1, b);
+      if (c2 && a_lo > 0.0) b2 = min(b2, b);
+    }
+    bu::min_i2<W_NW>(b1, b2, sc, tid);
+    if (b2 < b1) b2 = b1;
+    int nz_part = 0;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+      const int b = tid * PER + j;
+      if (b >= b1 && b <= b2) nz_part += cb[j];
+    }
+    const int nzone = bu::sum_i<W_NW>(nz_part, sc, tid);
+    if (nzone > W_ZCAP) {                                    // zone larger than the exact list
+      if (tid == 0) hand_to_single(BA, row_id);
+      return;
+    }
+    const float qA = bucket_floor_w(b1 - 1, scale, dclamp);  // certainly kept: q >= qA
+    const float qB = bucket_floor_w(b2, scale, dclamp);      // certainly dropped: q < qB
+    if (!anchored) {
+      dA = qA; dB = qB;
+    } else {
+      // Thresholds on d = rn(s - max) that are at least as cautious as those on q = rn(s - anchor):
+      // d >= dA must imply q >= qA, and q >= qB must imply d >= dB. Both roundings are monotone:
+      // s - anchor >= qA implies q >= qA, and q >= qB implies s - anchor >= pred(qB).
+      if (qA == INFINITY) dA = INFINITY;
+      else dA = nextafterf(__double2float_ru(static_cast<double>(anchor) + static_cast<double>(qA) - static_cast<double>(m)), INFINITY);
+      if (qB == -INFINITY) dB = -INFINITY;
+      else dB = nextafterf(__double2float_rd(static_cast<double>(anchor) + static_cast<double>(nextafterf(qB, -INFINITY)) - static_cast<double>(m)), -INFINITY);
+      if (dA > 0.0f) dA = INFINITY;                          // no d reaches it: nothing is certainly kept
+    }
+  }
+  stamp(1);
+
+  // ---- pass 3: exponentials (last use of the row: evict-first)
+  // exponential table: sixteen conflict-free copies of the first 128 entries when the row's range
+  // allows it, else the plain 1024 entries
+  const bool eb_rep = fast_ok && (dlow > -(W_EB_REP_ENTRIES - 2.0f) / 32.0f);
+  if (eb_rep) {
+    for (int j = tid; j < W_EB_REP * W_EB_REP_ENTRIES; j += W_NT) ebs[j] = __ldg(BA.eb_table + j / W_EB_REP);
+  } else if (fast_ok) {
+    for (int j = tid; j < NB1; j += W_NT) ebs[j] = __ldg(BA.eb_table + j);
+  }
+  if (tid < npiece) part[tid] = 0.0;                         // pieces past the row's end stay empty
+  if (tid == 0) sh.cnt = 0;
+  __syncthreads();
+  double Ssum = 0.0, Ksum = 0.0;
+  const uint32_t eb_mul = eb_rep ? 8u * W_EB_REP : 8u;
+  const uint32_t eb_bias = smem_addr(ebs) + (eb_rep ? 8u * (lane & (W_EB_REP - 1)) : 0u) - 0x4B000000u * eb_mul;
+#define GS_P3(F, O, C) wide_pass3<T, F, O, C>(sp, rv, pol_drop, lane, warp, m, Tm, dA, dB, eb_mul, eb_bias, s_tab, part, ppw, zl, &sh.cnt, Ssum, Ksum)
+  if (cut_on) {
+    if (fast_ok) { if (t_is_one) GS_P3(true, true, true); else GS_P3(true, false, true); }
+    else         { if (t_is_one) GS_P3(false, true, true); else GS_P3(false, false, true); }
+  } else {
+    if (fast_ok) { if (t_is_one) GS_P3(true, true, false); else GS_P3(true, false, false); }
+    else         { if (t_is_one) GS_P3(false, true, false); else GS_P3(false, false, false); }
+  }
+#undef GS_P3
+  __syncthreads();
+  if (lane != 0) Ksum = 0.0;                                 // kept mass is already warp-reduced into lane 0
+  double S = Ssum, Ktot = Ksum, unused = 0.0;
+  bu::sum_d3<W_NW>(S, Ktot, unused, sc, tid);
+  const int nz = sh.cnt;
+  stamp(2);
+  if (nz > W_ZCAP) {
+    if (tid == 0) hand_to_single(BA, row_id);
+    return;
+  }
+  dbg.sum_exp = S;
+
+  // ---- exact cut inside the zone by weighted selection
+  unsigned long long cut_key = 0ull;       // zone entries are kept when key < cut_key, or == with cut_incl
+  int cut_incl = 0;
+  bool bad = false;
+  if (cut_on && nz > 0) {
+    for (int j = tid; j < nz; j += W_NT) {                   // entries -> keys, in place
+      const uint2 e = zl[j];
+      zk[j] = zone_key(__uint_as_float(e.x), static_cast<int>(e.y), mode);
+    }
+    __syncthreads();
+    // G(c) = Ktot + mass{key <= c} rises along the zone order. Both flavours need the first key c*
+    // where G crosses: mode B (first G/S >= p) keeps through c*, mode A (first G/S > 1.5p) keeps
+    // everything before it. Narrow [lo, hi] around c* with linear sub-buckets until at most 32
+    // keys remain, then one warp finishes.
+    auto crossed = [&](double g) -> bool { return mode == 0 ? (g / S > plim) : (g / S >= plim); };
+    if (Ktot > 0.0 && crossed(Ktot)) bad = true;             // the bracket was wrong
+    double* sm = reinterpret_cast<double*>(hist);            // [W_NSUB] mass per sub-bucket
+    int* scn = reinterpret_cast<int*>(hist) + 2 * W_NSUB;    // [W_NSUB] count per sub-bucket
+    unsigned long long lo = ~0ull, hi = 0ull;
+    for (int j = tid; j < nz; j += W_NT) { const unsigned long long k = zk[j]; lo = k < lo ? k : lo; hi = k > hi ? k : hi; }
+    lo = bu::min_u64<W_NW>(lo, sc, tid);
+    hi = bu::max_u64<W_NW>(hi, sc, tid);
+    double gbase = Ktot;                                     // Ktot + mass of keys below lo; never crossed
+    int inrange = nz;
+    bool all_in = false;
+    for (int iter = 0; iter < 8 && inrange > 32 && !bad && !all_in; iter++) {
+      const unsigned long long spn = hi - lo;
+      int shf = 0;
+      while (shf < 63 && (spn >> shf) >= static_cast<unsigned long long>(W_NSUB)) shf++;
+      __syncthreads();
+      sm[tid] = 0.0; scn[tid] = 0;                           // W_NT == W_NSUB
+      __syncthreads();
+      for (int j = tid; j < nz; j += W_NT) {
+        const unsigned long long k = zk[j];
+        if (k >= lo && k <= hi) {
+          const int sb = static_cast<int>((k - lo) >> shf);
+          atomicAdd(&sm[sb], exp_safe(zone_key_d(k), s_tab));
+          atomicAdd(&scn[sb], 1);
+        }
+      }
+      __syncthreads();
+      const double mine = sm[tid];
+      double totm;
+      const double exm = bu::scan_excl_d<W_NW>(mine, totm, sc, tid);
+      const int first = (scn[tid] > 0 && crossed(gbase + exm + mine)) ? tid : W_NSUB;
+      const int sbx = bu::min_i<W_NW>(first, sc, tid);
+      if (sbx == W_NSUB) { all_in = true; break; }
+      if (tid == sbx) { sh.bcd[0] = gbase + exm; sh.bc[0] = scn[tid]; }
+      __syncthreads();
+      gbase = sh.bcd[0];
+      inrange = sh.bc[0];
+      const unsigned long long nlo = lo + (static_cast<unsigned long long>(sbx) << shf);
+      unsigned long long nhi = nlo + ((1ull << shf) - 1ull);
+      if (nhi < nlo || nhi > hi) nhi = hi;
+      lo = nlo; hi = nhi;
+    }
+    if (inrange > 32 && !all_in) bad = true;
+    double g_at = gbase, g_before = gbase;
+    if (!bad && !all_in) {
+      unsigned long long* few = reinterpret_cast<unsigned long long*>(hist);   // [32]
+      __syncthreads();
+      if (tid == 0) sh.cnt = 0;
+      __syncthreads();
+      for (int j = tid; j < nz; j += W_NT) {
+        const unsigned long long k = zk[j];
+        if (k >= lo && k <= hi) { const int slot = atomicAdd(&sh.cnt, 1); if (slot < 32) few[slot] = k; }
+      }
+      __syncthreads();
+      const int nf = min(32, sh.cnt);
+      if (warp == 0) {
+        const unsigned long long k = (lane < nf) ? few[lane] : ~0ull;
+        const double e = (lane < nf) ? exp_safe(zone_key_d(k), s_tab) : 0.0;
+        double g = gbase;                                    // G(k) = gbase + masses of the keys <= k
+        for (int l = 0; l < nf; l++) {
+          const unsigned long long kl = __shfl_sync(FULL, k, l);
+          const double el = __shfl_sync(FULL, e, l);
+          if (kl <= k) g += el;
+        }
+        const bool cr = (lane < nf) && crossed(g);
+        unsigned long long candk = cr ? k : ~0ull;           // first crossed key = smallest crossed key
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const unsigned long long tt = __shfl_xor_sync(FULL, candk, o);
+          candk = tt < candk ? tt : candk;
+        }
+        const unsigned who = __ballot_sync(FULL, cr && k == candk);
+        if (lane == 0) { sc.u[0] = candk; sh.bc[1] = who ? 1 : 0; }
+        if (who && lane == __ffs(who) - 1) { sh.bcd[1] = g; sh.bcd[2] = g - e; }
+      }
+      __syncthreads();
+      if (sh.bc[1]) {
+        cut_key = sc.u[0];
+        g_at = sh.bcd[1];
+        g_before = sh.bcd[2];
+        cut_incl = (mode == 0) ? 0 : 1;
+      } else {
+        all_in = true;                                       // rounding: nothing in the last group crossed
+      }
+      __syncthreads();
+    }
+    if (!bad && all_in) {
+      cut_key = ~0ull; cut_incl = 1;
+      if (mode == 1 && dlow < dB) bad = true;                // logits below the zone exist: the bracket promised a crossing
+    }
+    if (!bad && !all_in) {
+      // the sums carry exp_fast_s's error; in G/S >= p it enters as 2 p (1-p) times that bound
+      const double etol = 1e-12 + (fast_ok ? 2.0 * plim * fabs(1.0 - plim) * W_EXP_REL_ERR : 0.0);
+      if (fabs(g_at / S - plim) <= etol || fabs(g_before / S - plim) <= etol) flags |= FLAG_TOPP_EDGE;
+      if (mode == 1) {
+        // a later key with the same d as c*: the cut separates equal probabilities
+        int tie = 0;
+        for (int j = tid; j < nz; j += W_NT) { const unsigned long long k = zk[j]; tie |= (k > cut_key && (k >> 32) == (cut_key >> 32)) ? 1 : 0; }
+        if (bu::max_i<W_NW>(tie, sc, tid)) flags |= FLAG_TIE_CUT;
+      }
+    }
+    if (bad) {
+      if (tid == 0) hand_to_single(BA, row_id);
+      return;
+    }
+    // kept zone entries add their mass to the piece they sit in
+    __syncthreads();
+    for (int j = tid; j < nz; j += W_NT) {
+      const unsigned long long k = zk[j];
+      if (k < cut_key || (cut_incl && k == cut_key)) {
+        const int v = rv.vec_of(zone_key_index(k, mode));
+        const int w = v / span;
+        atomicAdd(&part[w * ppw + (v - w * span) / PV], exp_safe(zone_key_d(k), s_tab));
+      }
+    }
+    __syncthreads();
+  }
+  // ---- kept mass and the piece that holds the drawn token: prefix over the pieces in row order
+  const double pm = (tid < npiece) ? part[tid] : 0.0;
+  double Re;
+  const double pex = bu::scan_excl_d<W_NW>(pm, Re, sc, tid);
+  dbg.resum = Re / S;
+  stamp(3);
+  if (!(S == S) || !(S > 0.0) || !(Re > 0.0)) {
+    // mode A removed every token (generate.go:221-227 divides by zero): the walk falls through
+    fill_probs_row(QNAN);
+    if (S == S && S > 0.0) dbg.resum = 0.0; else dbg.sum_exp = QNAN;
+    write_row(V - 1, flags | FLAG_NONFINITE | FLAG_FALLBACK);
+    return;
+  }
+  // final rule for one logit: its kept mass (0 when cut away)
+  auto kept_mass = [&](float xv, int i) -> double {
+    if (i < 0 || i >= V) return 0.0;
+    const float s = t_is_one ? xv : __fdiv_rn(xv, Tm);
+    const float d = s - m;
+    if (d < dA) {
+      if (!(d >= dB)) return 0.0;
+      const unsigned long long k = zone_key(d, i, mode);
+      if (!(k < cut_key || (cut_incl && k == cut_key))) return 0.0;
+    }
+    return exp_safe(d, s_tab);
+  };
+  if (A.out_probs || A.out_debug) {                          // parity runs only
+    double* pr = A.out_probs ? A.out_probs + row_id * static_cast<int64_t>(V) : nullptr;
+    const double rq = Re / S;
+    int kept_loc = 0;
+    for (int v = tid; v < rv.nvec; v += W_NT) {
+      float x[VEC];
+      Elem<T>::unpack(__ldg(rv.vbase + v), x);
+      const int i0 = v * VEC - rv.shift;
+#pragma unroll
+      for (int c = 0; c < VEC; c++) {
+        const int i = i0 + c;
+        if (i >= 0 && i < V) {
+          const double f = (kept_mass(x[c], i) / S) / rq;
+          kept_loc += (f > 0) ? 1 : 0;
+          if (pr) pr[i] = f;
+        }
+      }
+    }
+    dbg.kept = bu::sum_i<W_NW>(kept_loc, sc, tid);
+  }
+  // ---- draw (generate.go:231-239): u < prefix/Re is tested as u*Re < prefix
+  const double tgt = u * Re;
+  int psel = (tid < npiece && tgt < pex + pm) ? tid : 0x7fffffff;
+  psel = bu::min_i<W_NW>(psel, sc, tid);
+  if (tid == psel) sh.bcd[0] = pex;
+  __syncthreads();
+  int id = -1;
+  double edge_lo = 0.0, edge_hi = 0.0;
+  double run_end = (psel != 0x7fffffff) ? sh.bcd[0] : Re;
+  if (psel != 0x7fffffff) {
+    // walk pieces from the selected one (rounding can push the crossing into the next piece)
+    for (int pi = psel; pi < npiece && id < 0; pi++) {       // uniform; normally one trip
+      const int w = pi / ppw;
+      const int vb = w * span + (pi - w * ppw) * PV;
+      const int vend = min(min(vb + PV, w * span + span), rv.nvec);
+      const int j = vb + tid;
+      double em[VEC];
+      double tsum = 0.0;
+#pragma unroll
+      for (int c = 0; c < VEC; c++) em[c] = 0.0;
+      int i0 = 0;
+      if (j < vend) {
+        float x[VEC];
+        Elem<T>::unpack(__ldg(rv.vbase + j), x);
+        i0 = j * VEC - rv.shift;
+#pragma unroll
+        for (int c = 0; c < VEC; c++) { em[c] = kept_mass(x[c], i0 + c); tsum += em[c]; }
+      }
+      double totc;
+      const double ex = bu::scan_excl_d<W_NW>(tsum, totc, sc, tid);
+      int pick_loc = 0x7fffffff;
+      double run = run_end + ex, lo = 0.0, hi = 0.0;
+#pragma unroll
+      for (int c = 0; c < VEC; c++) {
+        const double before = run;
+        run += em[c];
+        if (em[c] > 0.0 && tgt < run && pick_loc == 0x7fffffff) { pick_loc = i0 + c; lo = before; hi = run; }
+      }
+      const int pick = bu::min_i<W_NW>(pick_loc, sc, tid);
+      if (pick != 0x7fffffff) {
+        if (pick_loc == pick) { sh.bcd[1] = lo; sh.bcd[2] = hi; }
+        __syncthreads();
+        id = pick;
+        edge_lo = sh.bcd[1] / Re;
+        edge_hi = sh.bcd[2] / Re;
+      }
+      run_end += totc;
+    }
+  }
+  if (id >= 0) {
+    dbg.edge_lo = edge_lo; dbg.edge_hi = edge_hi;
+    if ((edge_lo > 0.0 && u - edge_lo <= 1e-6) || edge_hi - u <= 1e-6) flags |= FLAG_BOUNDARY;
+  } else {
+    id = V - 1;                                              // generate.go:239
+    flags |= FLAG_FALLBACK;
+    dbg.edge_lo = dbg.edge_hi = run_end / Re;
+    if (u - run_end / Re <= 1e-6) flags |= FLAG_BOUNDARY;
+  }
+  stamp(4);
+  write_row(id, flags);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(W_NT, W_CTAS) wide_rows_kernel(BatchArgs BA) {
+  extern __shared__ __align__(16) unsigned char dyn[];
+  __shared__ WideShared sh;
+  if (threadIdx.x < 256) sh.tab[threadIdx.x] = BA.k.exp_table[threadIdx.x];
+  unsigned long long pol_keep, pol_drop;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_keep));
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol_drop));
+  const int n = BA.hdr[1];
+  for (;;) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int w = atomicAdd(&BA.hdr[3], 1);
+      sh.row = (w < n) ? BA.list_wide[w] : -1;
+    }
+    __syncthreads();
+    const int row = sh.row;
+    if (row < 0) break;
+    wide_row<T>(BA, row, dyn, sh, pol_keep, pol_drop);
+  }
+}
+
+}  // namespace gs

@@ -16,7 +16,7 @@
 #include <new>
 
 #include "../../include/gorch_cuda_shim.h"
-#include "sample_batch.cuh"
+#include "sample_wide.cuh"
 
 namespace {
 
@@ -187,17 +187,17 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
     CUDA_TRY(cudaMemsetAsync(ba.list_single, 0, sizeof(int32_t), c->stream), errOut);
     gs::classify_rows_kernel<<<static_cast<unsigned>((B + 255) / 256), 256, 0, c->stream>>>(ba);
     const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
-    const unsigned gw = static_cast<unsigned>(B < c->sm_count ? B : c->sm_count);
+    const unsigned gw = static_cast<unsigned>(B < gs::W_CTAS * c->sm_count ? B : gs::W_CTAS * c->sm_count);
     const unsigned gsgl = static_cast<unsigned>(B < 2 * c->sm_count ? B : 2 * c->sm_count);
     gs::KernelArgs aw = a;
     aw.worklist = ba.list_single;
     if (dtype == GORCH_CUDA_F32) {
       gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-      if (!force_greedy) gs::wide_rows_kernel<float><<<gw, gs::W_NT, gs::W2_DYN_BYTES, c->stream>>>(ba);
+      if (!force_greedy) gs::wide_rows_kernel<float><<<gw, gs::W_NT, gs::W_DYN_BYTES, c->stream>>>(ba);
       if (!force_greedy) gs::sample_rows_kernel<float><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
     } else {
       gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-      if (!force_greedy) gs::wide_rows_kernel<uint16_t><<<gw, gs::W_NT, gs::W2_DYN_BYTES, c->stream>>>(ba);
+      if (!force_greedy) gs::wide_rows_kernel<uint16_t><<<gw, gs::W_NT, gs::W_DYN_BYTES, c->stream>>>(ba);
       if (!force_greedy) gs::sample_rows_kernel<uint16_t><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
     }
     CUDA_TRY(cudaGetLastError(), errOut);
@@ -399,8 +399,8 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   if ((e = cudaFuncSetAttribute(gs::sample_cluster_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 109 * 1024)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::narrow_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::narrow_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
-  if ((e = cudaFuncSetAttribute(gs::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::W2_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
-  if ((e = cudaFuncSetAttribute(gs::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::W2_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   return c;
 }
 
@@ -637,17 +637,17 @@ int gorch_cuda_sample_dev_static(GorchCudaCtxRef ctx, const void* logits, int dt
   CUDA_TRY(cudaMemsetAsync(ba.list_single, 0, sizeof(int32_t), c->stream), errOut);
   gs::classify_rows_kernel<<<static_cast<unsigned>((B + 255) / 256), 256, 0, c->stream>>>(ba);
   const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
-  const unsigned gw = static_cast<unsigned>(B < c->sm_count ? B : c->sm_count);
+  const unsigned gw = static_cast<unsigned>(B < gs::W_CTAS * c->sm_count ? B : gs::W_CTAS * c->sm_count);
   const unsigned gsgl = static_cast<unsigned>(B < 2 * c->sm_count ? B : 2 * c->sm_count);
   gs::KernelArgs aw = ba.k;
   aw.worklist = ba.list_single;
   if (dtype == GORCH_CUDA_F32) {
     gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-    gs::wide_rows_kernel<float><<<gw, gs::W_NT, gs::W2_DYN_BYTES, c->stream>>>(ba);
+    gs::wide_rows_kernel<float><<<gw, gs::W_NT, gs::W_DYN_BYTES, c->stream>>>(ba);
     gs::sample_rows_kernel<float><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
   } else {
     gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-    gs::wide_rows_kernel<uint16_t><<<gw, gs::W_NT, gs::W2_DYN_BYTES, c->stream>>>(ba);
+    gs::wide_rows_kernel<uint16_t><<<gw, gs::W_NT, gs::W_DYN_BYTES, c->stream>>>(ba);
     gs::sample_rows_kernel<uint16_t><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
   }
   CUDA_TRY(cudaGetLastError(), errOut);
