@@ -1,11 +1,12 @@
 // wide_rows_kernel: rows whose softmax runs over the whole vocabulary (top-k off).
 //
-// 1024 threads, one persistent CTA per SM, one row at a time per CTA. Warp w owns one
-// contiguous span of the row (1/32 of it, rounded up to whole steps); in a step every lane
-// handles eight logits (two 16-byte vectors of f32, one of bf16), loaded straight into
-// registers one or two steps ahead of their use. Nothing is shared between threads inside a
-// pass, so a pass contains no barrier; the loads go through L2 (cache hints: keep in pass 1,
-// evict first in pass 3), where the later passes find the row again.
+// 256 threads per CTA, four persistent CTAs per SM, one row at a time per CTA: with four rows
+// per SM the load latency and the serial tail of one row hide behind the arithmetic of the others. Warp w owns one contiguous span of the row (1/8 of it,
+// rounded up to whole steps); in a step every lane handles eight logits (two 16-byte vectors
+// of f32, one of bf16), loaded straight into registers one or two steps ahead of their use
+// and asked from L2 two steps before that. Nothing is shared between threads inside a pass,
+// so a pass contains no barrier; the loads carry L2 cache hints (keep in pass 1, evict first
+// in pass 3), and the later passes find in L2 what has stayed there.
 //
 //   sample                     the first step of every warp: an upper estimate (anchor) of the
 //                              row's maximum and its range
@@ -27,7 +28,7 @@
 namespace gs {
 
 #ifndef GS_W_NT
-#define GS_W_NT 512
+#define GS_W_NT 256
 #endif
 constexpr int W_NT = GS_W_NT;           // threads per CTA
 constexpr int W_CTAS = 1024 / W_NT;     // CTAs per SM
@@ -35,8 +36,12 @@ constexpr int W_NSUB = W_NT;            // sub-buckets of one weighted-selection
 constexpr int W_NW = W_NT / 32;
 constexpr int W_NB = 4096;              // histogram buckets
 constexpr int W_ZCAP = 2048;            // exact zone list capacity
+#ifndef GS_W_PF
+#define GS_W_PF 2
+#endif
+constexpr int W_PF = GS_W_PF;           // L2 prefetch distance in steps
 constexpr int W_G = 4;                  // steps per piece (power of two)
-constexpr int W_MAX_STEPS = 64;         // steps per warp and pass; longer rows go to the single-CTA kernel
+constexpr int W_MAX_STEPS = (W_NT >= 512) ? 64 : 128;         // steps per warp and pass; longer rows go to the single-CTA kernel
 constexpr int W_MAX_PPW = W_MAX_STEPS / W_G;
 constexpr int W_MAX_PIECES = W_NW * W_MAX_PPW;                 // 512
 constexpr int W_EB_REP = 16;            // copies of a table entry in the conflict-free layout
@@ -47,7 +52,8 @@ constexpr int W_OFF_EB = W_OFF_ZONE + W_ZCAP * 8;              // 1024 entries, 
 constexpr int W_OFF_PART = W_OFF_EB + W_EB_REP * W_EB_REP_ENTRIES * 8;
 constexpr int W_DYN_BYTES = W_OFF_PART + W_MAX_PIECES * 8;     // 52 KB
 static_assert(W_EB_REP * W_EB_REP_ENTRIES >= NB1, "either layout fits");
-static_assert(W_MAX_PIECES <= W_NT && W_G * 64 <= W_NT && W_NSUB * 12 <= W_NB * 4, "piece prefix and sub-bucket arrays");
+static_assert(W_NT >= 256 && W_NT <= 1024 && W_MAX_PIECES <= W_NT && W_G * 64 <= W_NT && W_NSUB * 12 <= W_NB * 4,
+              "one piece / one vector of a piece / one sub-bucket per thread");
 
 // Histogram buckets of width 1/scale (scale a power of two): bucket = round(-d * scale),
 // clamped to W_NB - 1. Multiplying by a power of two is exact, so the bucket edges are exact.
@@ -91,6 +97,29 @@ __device__ __forceinline__ double exp_fast_s(float d, uint32_t eb_mul, uint32_t 
   const double E = lds_f64(__float_as_uint(f) * eb_mul + eb_bias);
   return fma(E, static_cast<double>(w), E);
 }
+// Two-wide f32 arithmetic (one issue slot for two results on sm_100).
+typedef unsigned long long f32x2_t;
+__device__ __forceinline__ f32x2_t pk2(float a, float b) { f32x2_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ void upk2(f32x2_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2_t fma2(f32x2_t a, f32x2_t b, f32x2_t c) { f32x2_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ f32x2_t add2(f32x2_t a, f32x2_t b) { f32x2_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ f32x2_t mul2(f32x2_t a, f32x2_t b) { f32x2_t d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+// exp_fast_s for two arguments at once
+__device__ __forceinline__ void exp_fast_s2(float d0, float d1, uint32_t eb_mul, uint32_t eb_bias, double& e0, double& e1) {
+  const f32x2_t D = pk2(d0, d1);
+  const f32x2_t F = fma2(D, pk2(-32.0f, -32.0f), pk2(8388608.0f, 8388608.0f));
+  const f32x2_t DL = fma2(add2(F, pk2(-8388608.0f, -8388608.0f)), pk2(0.03125f, 0.03125f), D);
+  f32x2_t T = fma2(DL, pk2(8.3333338e-3f, 8.3333338e-3f), pk2(4.1666668e-2f, 4.1666668e-2f));
+  T = fma2(T, DL, pk2(1.6666667e-1f, 1.6666667e-1f));
+  T = fma2(T, DL, pk2(0.5f, 0.5f));
+  const f32x2_t W = fma2(T, mul2(DL, DL), DL);
+  float f0, f1, w0, w1;
+  upk2(F, f0, f1); upk2(W, w0, w1);
+  const double E0 = lds_f64(__float_as_uint(f0) * eb_mul + eb_bias);
+  const double E1 = lds_f64(__float_as_uint(f1) * eb_mul + eb_bias);
+  e0 = fma(E0, static_cast<double>(w0), E0);
+  e1 = fma(E1, static_cast<double>(w1), E1);
+}
 constexpr double W_EXP_REL_ERR = 6e-10;   // bound of exp_fast_s against the exact exponential
 
 // What one thread needs to stream its warp's span of a row.
@@ -113,6 +142,13 @@ __device__ __forceinline__ void w_load(const WSpan& sp, int st, unsigned long lo
   ra = ldg_hint(sp.lane_src + min(o, sp.omax), pol);
   if (EPI == 2) rb = ldg_hint(sp.lane_src + min(o + 32, sp.omax), pol);
   else rb = ra;
+  // ask L2 for the step W_PF steps further on: costs no register, and the load above then finds
+  // its line in L2 whether the row came from HBM or was evicted since the last pass
+  if (W_PF > 0) {
+    const int o2 = o + W_PF * SV;
+    asm volatile("prefetch.global.L2 [%0];" :: "l"(sp.lane_src + min(o2, sp.omax)));
+    if (EPI == 2) asm volatile("prefetch.global.L2 [%0];" :: "l"(sp.lane_src + min(o2 + 32, sp.omax)));
+  }
 }
 
 // Steps [st0, st1) of one pass; qa/qb hold the vectors of steps st0 .. st0+D-1 on entry and of
@@ -233,20 +269,27 @@ __device__ __noinline__ void wide_pass3(const WSpan& sp_in, const RowView<T>& rv
   double stot = 0.0, ksum = 0.0;
 #define GS_BODY3(CL) [&](const float* x, uint32_t valid, int st, int gv) {                       \
     float nearest = INFINITY;                                                                    \
-    _Pragma("unroll") for (int c = 0; c < 8; c++) {                                              \
-      const float s = TONE ? x[c] : __fdiv_rn(x[c], Tm);                                         \
-      const float d = s - m;                                                                     \
-      double e;                                                                                  \
+    _Pragma("unroll") for (int c = 0; c < 8; c += 2) {                                           \
+      const float s0 = TONE ? x[c] : __fdiv_rn(x[c], Tm);                                        \
+      const float s1 = TONE ? x[c + 1] : __fdiv_rn(x[c + 1], Tm);                                \
+      const float d0 = s0 - m, d1 = s1 - m;                                                      \
+      double e0, e1;                                                                             \
       if (FAST) {                                                                                \
-        e = exp_fast_s(CL ? d : fmaxf(d, dfloor), eb_mul, eb_bias);                                      \
-        if (!CL) e = __hiloint2double(((valid >> c) & 1u) ? __double2hiint(e) : 0, ((valid >> c) & 1u) ? __double2loint(e) : 0); \
+        exp_fast_s2(CL ? d0 : fmaxf(d0, dfloor), CL ? d1 : fmaxf(d1, dfloor), eb_mul, eb_bias, e0, e1); \
+        if (!CL) {                                                                               \
+          const bool v0 = (valid >> c) & 1u, v1 = (valid >> (c + 1)) & 1u;                       \
+          e0 = __hiloint2double(v0 ? __double2hiint(e0) : 0, v0 ? __double2loint(e0) : 0);       \
+          e1 = __hiloint2double(v1 ? __double2hiint(e1) : 0, v1 ? __double2loint(e1) : 0);       \
+        }                                                                                        \
       } else {                                                                                   \
-        e = exp_safe(d, s_tab);                              /* exp_safe(-Inf) is exactly 0 */   \
+        e0 = exp_safe(d0, s_tab);                            /* exp_safe(-Inf) is exactly 0 */   \
+        e1 = exp_safe(d1, s_tab);                                                                \
       }                                                                                          \
-      if (c & 1) t1 += e; else t0 += e;                                                          \
+      t0 += e0; t1 += e1;                                                                        \
       if (CUT) {                                                                                 \
-        sub = fma(e, __hiloint2double((d < dA) ? 0x3ff00000 : 0, 0), sub);                       \
-        nearest = fminf(nearest, fabsf(d - dmid));                                               \
+        sub = fma(e0, __hiloint2double((d0 < dA) ? 0x3ff00000 : 0, 0), sub);                     \
+        sub = fma(e1, __hiloint2double((d1 < dA) ? 0x3ff00000 : 0, 0), sub);                     \
+        nearest = fminf(nearest, fminf(fabsf(d0 - dmid), fabsf(d1 - dmid)));                     \
       }                                                                                          \
     }                                                                                            \
     if (CUT && nearest <= dhalf) {                           /* rare: a logit of this lane near the zone */ \
@@ -321,6 +364,7 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
   dbg.max_scaled = 0; dbg.threshold = __int_as_float(0x7fc00000); dbg.path = 2;
   for (int q = 0; q < 8; q++) dbg.cycles[q] = 0;
   long long tprev = clock64();
+  { unsigned long long gt; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt)); dbg.cycles[6] = static_cast<uint32_t>(gt); }
   auto stamp = [&](int slot) { const long long now = clock64(); dbg.cycles[slot] = static_cast<uint32_t>(now - tprev); tprev = now; };
   auto write_row = [&](int id, uint32_t fl) {
     if (tid == 0) {
@@ -385,9 +429,11 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     const float s_hi = scale_t(smax, Tm), s_lo = scale_t(smin, Tm);
     const float r0 = s_hi - s_lo;
     if (!bad_sample && r0 >= 0.0f && r0 < 1e30f && fabsf(s_hi) < 1e30f) {
-      const float margin = fmaxf(0.25f * r0, 1e-3f * fmaxf(1.0f, fabsf(s_hi)));
+      // half the sample's range above its maximum (a maximum beyond that costs an extra pass),
+      // a quarter below its minimum (what lies lower shares the last bucket)
+      const float margin = fmaxf(0.5f * r0, 1e-3f * fmaxf(1.0f, fabsf(s_hi)));
       anchor = s_hi + margin;
-      set_scale(r0 + 2.0f * margin);
+      set_scale(r0 + 1.5f * margin);
       anchored = true;
     }
   }
@@ -718,6 +764,7 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     }
     dbg.kept = bu::sum_i<W_NW>(kept_loc, sc, tid);
   }
+  stamp(4);
   // ---- draw (generate.go:231-239): u < prefix/Re is tested as u*Re < prefix
   const double tgt = u * Re;
   int psel = (tid < npiece && tgt < pex + pm) ? tid : 0x7fffffff;
@@ -776,7 +823,8 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     dbg.edge_lo = dbg.edge_hi = run_end / Re;
     if (u - run_end / Re <= 1e-6) flags |= FLAG_BOUNDARY;
   }
-  stamp(4);
+  stamp(5);
+  { uint32_t smid; asm volatile("mov.u32 %0, %smid;" : "=r"(smid)); dbg.cycles[7] = smid; }
   write_row(id, flags);
 }
 
