@@ -41,6 +41,9 @@ def parse():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--vocab-sharded", action="store_true",
+                    help="every rank holds a column slice of the SAME rows (C5): local candidates, one all-gather, "
+                         "merge on every rank; total work fixed (strong scaling), no host-pointer leg")
     ap.add_argument("--profile", action="store_true",
                     help="short run for ncu: no e2e leg, no CPU baseline, no clock hold")
     return ap.parse_args()
@@ -60,7 +63,8 @@ def workload_config(w, args, world):
     return {
         "workload": w.name, "rows_per_gpu": int(w.B), "vocab": int(w.V), "logits_dtype": w.dtype,
         "topp_mode": "A(model/generate.go)" if mode == 0 else "B(model/qwen/generate.go)",
-        "sharding": f"rows x{world}, no collective",
+        "sharding": (f"vocab x{world}, one all-gather of {world}x{int(w.B)} records of 1040 B" if args.vocab_sharded
+                     else f"rows x{world}, no collective"),
         "l2": "inputs larger than L2" if w.logits.nbytes > 126 * 2 ** 20 else "L2 flushed between steps",
     }
 
@@ -192,7 +196,9 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     build.build()
-    workloads.set_shard(rank)
+    workloads.set_shard(0 if args.vocab_sharded else rank)
+    if args.vocab_sharded:
+        args.no_e2e = True
     w = workloads.make(args.workload, args.rows, args.mode)
     B, V = w.B, w.V
     dt_code = DTYPE_BF16 if w.dtype == "bf16" else DTYPE_F32
@@ -220,6 +226,25 @@ def main():
     def step():
         smp.sample_dev_ptrs(d_logits.data_ptr(), dt_code, B, V, V, d_cfgs.data_ptr(), d_uni.data_ptr(),
                             d_ids.data_ptr(), d_flags.data_ptr())
+
+    if args.vocab_sharded:
+        lo, hi = workloads.shard_vocab(V, rank, world)
+        d_slice = d_logits[:, lo:hi].contiguous()
+        del d_logits
+        d_rec = torch.empty((B, sampling.VS_RECORD_BYTES), dtype=torch.uint8, device="cuda")
+        d_all = torch.empty((world, B, sampling.VS_RECORD_BYTES), dtype=torch.uint8, device="cuda")
+        if flush is None and d_slice.numel() * d_slice.element_size() <= 126 * 2 ** 20:
+            flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+
+        def step():  # noqa: F811
+            smp.vocab_local_ptrs(d_slice.data_ptr(), dt_code, B, hi - lo, hi - lo, lo, d_cfgs.data_ptr(), d_rec.data_ptr())
+            if world > 1:
+                dist.all_gather_into_tensor(d_all.view(-1), d_rec.view(-1))
+            else:
+                d_all[0].copy_(d_rec)
+            smp.vocab_merge_ptrs(d_all.data_ptr(), world, B, V, d_cfgs.data_ptr(), d_uni.data_ptr(),
+                                 d_ids.data_ptr(), d_flags.data_ptr())
 
     def barrier():
         if world > 1:
@@ -280,15 +305,17 @@ def main():
     total_ms_max, e2e_ms_max = t.tolist()
     if rank == 0:
         peak, peak_kind = peaks()
-        rows_total = B * world * K
+        rows_total = B * K if args.vocab_sharded else B * world * K
         value = rows_total / (total_ms_max / 1e3)
         alg_bytes = B * w.bytes_per_row
+        if args.vocab_sharded:                 # per GPU: its column slice of every row
+            alg_bytes = B * (-(-V // world)) * w.logits.dtype.itemsize
         avg_launch_ms = float(np.mean(kernel_ms))
         achieved = alg_bytes / (avg_launch_ms / 1e3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": K,
             "warmup": max(args.warmup, 3), "ms_per_step": total_ms_max / K, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "scaling": "strong" if args.vocab_sharded else "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
             "config": workload_config(w, args, world),
             "logits_gbs_per_gpu": achieved,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -326,12 +353,15 @@ def dominant_kernel(w):
 
 
 def measured_traffic(w):
-    """DRAM bytes per launch from the committed ncu capture of this workload
-    (profiles/), or None when no capture covers it."""
+    """DRAM bytes per launch of the dominant kernel from the committed ncu capture
+    of this workload (profiles/), or None when no capture covers it."""
     path = os.path.join(ROOT, "gorch_b200", "measured_traffic.json")
     try:
         with open(path) as f:
-            return json.load(f).get(w.name)
+            rec = json.load(f).get(w.name)
+        if rec is None or rec.get("rows") != w.B or rec.get("topp_mode") != int(w.cfgs["topp_mode"][0]):
+            return None
+        return rec["dram_bytes_per_launch"]
     except Exception:
         return None
 

@@ -19,6 +19,7 @@ EXPORTS = [
     "gorch_cuda_buffer_device_ptr", "gorch_cuda_buffer_upload", "gorch_cuda_buffer_download",
     "gorch_cuda_sample_host", "gorch_cuda_sample_dev", "gorch_cuda_sample_dev_static", "gorch_cuda_sample_row",
     "gorch_cuda_argmax_host", "gorch_cuda_argmax_dev",
+    "gorch_cuda_vocab_local_dev", "gorch_cuda_vocab_merge_dev",
 ]
 
 
@@ -66,6 +67,8 @@ def load() -> C.CDLL:
         "gorch_cuda_sample_row": (i64, [p, p, i64, f32, i64, f32, i32, f64, C.POINTER(C.c_uint32), err]),
         "gorch_cuda_argmax_host": (i32, [p, p, i32, i64, i64, i64, p, err]),
         "gorch_cuda_argmax_dev": (i32, [p, p, i32, i64, i64, i64, p, err]),
+        "gorch_cuda_vocab_local_dev": (i32, [p, p, i32, i64, i64, i64, i64, p, p, err]),
+        "gorch_cuda_vocab_merge_dev": (i32, [p, p, i32, i64, i64, p, p, p, p, err]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)

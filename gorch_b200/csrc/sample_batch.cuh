@@ -7,10 +7,13 @@
 //   narrow_rows_kernel     256 threads, four CTAs per SM. One streaming pass per
 //                          row: the first 4096 logits give a threshold (k-th
 //                          largest of the 256 per-thread maxima, a lower bound
-//                          of the k-th largest logit), later tiles append the
-//                          few logits above it; the list is pruned to the exact
-//                          k-th largest when it fills. Everything after the pass
-//                          happens on a few hundred candidates in shared memory.
+//                          of the k-th largest logit); then every warp walks
+//                          its own span of the rest (row_stream.cuh) and appends
+//                          the few logits above the threshold, with no barrier
+//                          per step; the list is pruned to the exact k-th
+//                          largest when a warp sees it half full. Everything
+//                          after the pass happens on a few hundred candidates
+//                          in shared memory.
 //   wide_rows_kernel       (sample_wide.cuh) rows whose softmax runs over the
 //                          whole vocabulary.
 //
@@ -20,6 +23,7 @@
 #pragma once
 
 #include "block_util.cuh"
+#include "row_stream.cuh"
 #include "sample_cluster.cuh"
 
 namespace gs {
@@ -32,6 +36,21 @@ constexpr int N_WARM_ELEMS = 4096;      // logits of the warm-up chunk
 constexpr int N_DYN_BYTES = 16384 + N_CAP * 8;
 
 
+// Vocab-sharded sampling: what one rank knows about one row of its column slice. cand holds every
+// local logit at or above the local k-th largest (global indices); the global kept set is a
+// subset of the union of the ranks' lists, because the global k-th largest is at least every
+// local one.
+constexpr int VS_CAND = 128;
+constexpr uint32_t VS_NONFINITE = 1u, VS_BAD_CFG = 2u, VS_OVERFLOW = 4u, VS_UNSUPPORTED = 8u, VS_NAN_AT_0 = 16u;
+struct VsRecord {
+  float xmax;              // largest local logit (not yet divided by the temperature)
+  int32_t n;               // entries in cand
+  uint32_t flags;          // VS_*
+  int32_t pad;
+  uint2 cand[VS_CAND];     // (logit bits, global index)
+};
+static_assert(sizeof(VsRecord) == 16 + 8 * VS_CAND, "record layout is part of the C ABI");
+
 struct BatchArgs {
   KernelArgs k;
   const double* eb_table;   // 1024 doubles: exp(-b/32)
@@ -41,6 +60,13 @@ struct BatchArgs {
   int32_t* list_single;     // [0] = count, [1..] rows for the single-CTA kernel
   int64_t B;
 };
+
+// every row on the narrow list (vocab-sharded local pass)
+__global__ void iota_list_kernel(BatchArgs BA) {
+  const int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (b < BA.B) BA.list_narrow[b] = static_cast<int32_t>(b);
+  if (b == 0) BA.hdr[0] = static_cast<int32_t>(BA.B);
+}
 
 __global__ void classify_rows_kernel(BatchArgs BA) {
   const int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -214,13 +240,12 @@ __device__ __forceinline__ uint4 mask_edges(const RowView<T>& rv, int v, uint4 r
 // ---------------------------------------------------------------------------
 template <typename T>
 __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned char* dyn, bu::Scratch& sc,
-                           uint32_t* s_sel, int* s_bc, double* s_bcd, int* s_cnt, float* s_thr) {
+                           uint32_t* s_sel, int* s_bc, double* s_bcd, int* s_cnt, float* s_thr, int* s_flag) {
   const KernelArgs& A = BA.k;
   const int tid = threadIdx.x;
   const int V = A.V;
   constexpr int VEC = Elem<T>::VEC;
   constexpr int WARM_VECS = N_WARM_ELEMS / VEC;
-  constexpr int TILE_ELEMS = N_NT * VEC;
   const T* row = static_cast<const T*>(A.logits) + row_id * A.row_stride;
   RowView<T> rv;
   rv.init(row, V);
@@ -267,7 +292,19 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     int id = static_cast<int>(~static_cast<uint32_t>(best & 0xffffffffull));
     float x0 = 0.f;
     rv.visit(0, [&](float x, int i) { if (i == 0) x0 = x; });
-    if (x0 != x0) id = 0;                                    // a NaN at index 0 is never beaten
+    // a NaN at index 0 is never beaten (index 0 of the whole row: a later slice has no such column)
+    if (x0 != x0 && (!A.vs_records || A.vs_col_offset == 0)) id = 0;
+    if (A.vs_records) {                                      // vocab-sharded: this slice's champion
+      if (tid == 0) {
+        VsRecord& rec = static_cast<VsRecord*>(A.vs_records)[row_id];
+        float xid = 0.f;
+        rv.visit(rv.vec_of(id), [&](float x, int i) { if (i == id) xid = x; });
+        rec.xmax = xid; rec.n = 1; rec.pad = 0;
+        rec.flags = (x0 != x0 && A.vs_col_offset == 0) ? VS_NAN_AT_0 : 0u;
+        rec.cand[0] = make_uint2(__float_as_uint(xid), static_cast<uint32_t>(id + A.vs_col_offset));
+      }
+      return;
+    }
     fill_probs_row(0.0);
     __syncthreads();
     if (A.out_probs && tid == 0) A.out_probs[row_id * static_cast<int64_t>(V) + id] = 1.0;
@@ -275,9 +312,20 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     write_row(id, 0u);
     return;
   }
+  auto vs_flag_only = [&](uint32_t fl) {
+    if (tid == 0) {
+      VsRecord& rec = static_cast<VsRecord*>(A.vs_records)[row_id];
+      rec.xmax = 0.f; rec.n = 0; rec.flags = fl; rec.pad = 0;
+    }
+  };
   if (!(Tm > 0.0f) || !(Tm < INFINITY)) {
+    if (A.vs_records) { vs_flag_only(VS_BAD_CFG); return; }
     fill_probs_row(QNAN);
     write_row(-1, FLAG_BAD_CFG);
+    return;
+  }
+  if (A.vs_records && !(cfg.top_k > 0 && cfg.top_k <= VS_CAND)) {   // the merge needs a top-k to bound the lists
+    vs_flag_only(VS_UNSUPPORTED);
     return;
   }
   const int topk = cfg.top_k;                                // 0 < top_k <= KFAST, < V (classified)
@@ -289,7 +337,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   // ---- warm-up chunk: park it, one running maximum per thread
   float xmax = -INFINITY, xmin = INFINITY;
   bool nan_seen = false;
-  if (tid == 0) *s_cnt = 0;
+  if (tid == 0) { *s_cnt = 0; *s_flag = 0; }
   const int warm = min(rv.nvec, WARM_VECS);
   {
     constexpr int G = WARM_VECS / N_NT;
@@ -367,6 +415,23 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     }
   }
   __syncthreads();
+  // A tighter threshold for the rest of the row, taken as an estimate rather than a bound: the
+  // r-th largest logit of the warm-up chunk, with r chosen so that about four times top_k logits
+  // of the whole row are expected above it. If the row ends with at least top_k candidates, its
+  // top_k-th largest is among them and nothing was lost; if not (the chunk was not typical of
+  // the row), the row is redone by the single-CTA kernel. Not used for vocab-sharded slices.
+  bool tight = false;
+  if (!A.vs_records && rv.nvec > warm) {
+    const int cnt0 = *s_cnt;
+    const long long welems = static_cast<long long>(warm) * VEC;
+    const int r = static_cast<int>((4ll * topk * welems + V - 1) / V) + 4;
+    if (r < cnt0) {                                          // uniform
+      const uint32_t rkey = bu::select_kth<N_NT>(cand, cnt0, r, s_sel, s_bc, tid);
+      const float t = okey_to_float(rkey);
+      if (t > thr) { thr = t; tight = true; }
+      __syncthreads();
+    }
+  }
   stamp(0);
   bool giveup = false;
   // exact k-th largest of the list -> threshold; keepers move through the chunk buffer
@@ -387,57 +452,84 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     __syncthreads();
     return kept;
   };
-  int do_prune = (*s_cnt + TILE_ELEMS > N_CAP) ? 1 : 0;
-  __syncthreads();                                           // everybody has read the count before anyone appends again
-  // ---- stream the rest. Raw vectors are fetched two tiles ahead and only looked at when
-  // their tile comes up, so two loads per thread stay in flight.
-  const uint4 NEUT = make_uint4(Neutral<T>::word, Neutral<T>::word, Neutral<T>::word, Neutral<T>::word);
-  constexpr int PF = 4;                                      // tiles in flight per thread
-  uint4 nxt[PF];
+  // ---- stream the rest of the row: every warp walks its own span of it, eight logits per lane
+  // and step (two 16-byte vectors of f32, one of bf16), loaded NQ steps ahead in registers. No
+  // barrier per step: a warp that sees the list past TRIGGER raises *s_flag; every warp looks at
+  // the flag before each step and comes to the barrier below, where the list is pruned to the
+  // exact k-th largest, and then walks on. Between the flag going up and a warp seeing it that
+  // warp appends at most one step (256 entries, 2048 for the block): the room above TRIGGER.
+  constexpr int SV = 32 * (8 / VEC);
+  constexpr int NQ = 2;                                      // steps in flight
+  constexpr int TRIGGER = N_CAP - N_NW * 32 * 8;
+  static_assert(TRIGGER >= N_KEEP, "a pruned list must sit below the trigger");
+  const int lane = tid & 31, warp = tid >> 5;
+  const int rest = max(rv.nvec - warm, 0);
+  const int span = (((rest + N_NW - 1) / N_NW + SV - 1) / SV) * SV;
+  const WSpan sp = make_span<T>(rv, warm + warp * span, span, lane);
+  unsigned long long pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  volatile int* vflag = s_flag;
+  float run = xmax;                                          // NaN-propagating running maximum of this thread
+  int st = 0;
+  uint4 qa[NQ], qb[NQ];
 #pragma unroll
-  for (int q = 0; q < PF; q++) {
-    nxt[q] = NEUT;
-    if (warm + q * N_NT + tid < rv.nvec) nxt[q] = __ldg(rv.vbase + warm + q * N_NT + tid);
-  }
-  for (int base = warm; base < rv.nvec; base += N_NT) {      // uniform loop
-    uint4 raw = nxt[0];
+  for (int q = 0; q < NQ; q++) w_load<T, N_PF>(sp, q, pol, qa[q], qb[q]);
+  if (*s_cnt >= TRIGGER && tid == 0) *s_flag = 1;            // the warm-up chunk alone may have filled it
+  __syncthreads();
+  for (;;) {                                                 // uniform: one trip per prune, plus one
+#pragma unroll 1
+    while (st < sp.nst && *vflag == 0) {
+      const uint4 ca = qa[0], cb = qb[0];
 #pragma unroll
-    for (int q = 0; q + 1 < PF; q++) nxt[q] = nxt[q + 1];
-    nxt[PF - 1] = NEUT;
-    const int v = base + tid;
-    if (v + PF * N_NT < rv.nvec) nxt[PF - 1] = __ldg(rv.vbase + v + PF * N_NT);
-    if (do_prune) {
-      const int cnt = prune(*s_cnt);
-      if (cnt > N_KEEP) { giveup = true; break; }            // ties at the threshold fill the buffer
-    }
-    if (v == rv.nvec - 1) raw = mask_edges(rv, v, raw);      // lanes past the row's end become -Inf
-    float x[VEC];
-    Elem<T>::unpack(raw, x);
-    bool any = false;
+      for (int q = 0; q + 1 < NQ; q++) { qa[q] = qa[q + 1]; qb[q] = qb[q + 1]; }
+      w_load<T, N_PF>(sp, st + NQ, pol, qa[NQ - 1], qb[NQ - 1]);
+      const bool clean = st < sp.clean_hi;                   // else: the row's last vector, or past the end
+      float hi8 = -INFINITY;
+      if (clean) {
+        hi8 = step_max_nan<T>(ca, cb);
+        run = maxnan(run, hi8);
+      }
+      if (!clean || hi8 >= thr) {                            // this lane holds a logit for the list (or an edge)
+        float x[8];
+        if (VEC == 4) { Elem<T>::unpack(ca, x); Elem<T>::unpack(cb, x + 4 * (8 / VEC - 1)); }
+        else Elem<T>::unpack(ca, x);
+        const int gv = sp.first + st * SV + lane;
 #pragma unroll
-    for (int c = 0; c < VEC; c++) {
-      xmax = fmaxf(xmax, x[c]);
-      nan_seen |= (x[c] != x[c]);
-      any |= (x[c] >= thr);
-    }
-    bool want = false;
-    if (any) {                                               // threads past the row hold -Inf: thr > -Inf here or i is checked
-      const int i0 = v * VEC - rv.shift;
-#pragma unroll
-      for (int c = 0; c < VEC; c++) {
-        const int i = i0 + c;
-        if (x[c] >= thr && i >= 0 && i < V) {
-          const int slot = atomicAdd(s_cnt, 1);
-          cand[slot] = make_uint2(__float_as_uint(x[c]), static_cast<uint32_t>(i));
-          want |= (slot + 1 + TILE_ELEMS > N_CAP);
+        for (int c = 0; c < 8; c++) {
+          const int g = gv + 32 * (c / VEC);
+          const int i = g * VEC - rv.shift + (c % VEC);
+          if (clean || (g < rv.nvec && i < V)) {
+            if (!clean) run = maxnan(run, x[c]);
+            if (x[c] >= thr) {
+              const int slot = atomicAdd(s_cnt, 1);
+              if (slot < N_CAP) cand[slot] = make_uint2(__float_as_uint(x[c]), static_cast<uint32_t>(i));
+              if (slot >= TRIGGER) *vflag = 1;
+            }
+          }
         }
       }
+      st++;
     }
-    do_prune = __syncthreads_or(want ? 1 : 0);
+    const int more = __syncthreads_or((st < sp.nst) ? 1 : 0);
+    const int full = __syncthreads_or(*vflag);               // every thread reads it before anyone can raise it again
+    if (full) {
+      const int raw = *s_cnt;
+      __syncthreads();
+      if (tid == 0) *s_flag = 0;
+      __syncthreads();
+      if (raw > N_CAP) { giveup = true; break; }             // entries were dropped
+      const int cnt = prune(raw);
+      if (cnt > N_KEEP) { giveup = true; break; }            // ties at the threshold fill the buffer
+    }
+    if (!more) break;
   }
+  nan_seen |= (run != run);
+  xmax = run;
   stamp(1);
   dbg.cycles[5] = static_cast<uint32_t>(*s_cnt);
   int nk = 0;
+  if (!giveup && *s_cnt > N_CAP) giveup = true;
+  if (!giveup && tight && *s_cnt < topk) giveup = true;      // the estimated threshold was too tight for this row
   if (!giveup) {
     nk = prune(*s_cnt);
     if (nk > KEEP_MAX) giveup = true;                        // long run of ties at the threshold
@@ -448,6 +540,16 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   dbg.max_scaled = m;
   // A NaN anywhere, or an infinite maximum, makes the softmax sum NaN upstream
   // (generate.go:173-181): every comparison of the walk fails, result n-1 (:239).
+  if (A.vs_records) {                                        // vocab-sharded: hand the list over instead of drawing
+    VsRecord& rec = static_cast<VsRecord*>(A.vs_records)[row_id];
+    uint32_t fl = 0u;
+    if (anynan || !(fabsf(m) < INFINITY)) fl |= VS_NONFINITE;
+    if (giveup || nk > VS_CAND) fl |= VS_OVERFLOW;
+    const int nout = (fl == 0u) ? nk : 0;
+    if (tid == 0) { rec.xmax = xmax; rec.n = nout; rec.flags = fl; rec.pad = 0; }
+    for (int j = tid; j < nout; j += N_NT) rec.cand[j] = make_uint2(cand[j].x, cand[j].y + static_cast<uint32_t>(A.vs_col_offset));
+    return;
+  }
   if (anynan || !(fabsf(m) < INFINITY)) {
     fill_probs_row(QNAN);
     dbg.sum_exp = QNAN;
@@ -472,6 +574,7 @@ __global__ void __launch_bounds__(N_NT, 4) narrow_rows_kernel(BatchArgs BA) {
   __shared__ double s_bcd[4];
   __shared__ int s_cnt;
   __shared__ float s_thr;
+  __shared__ int s_flag;
   __shared__ int s_row;
   const int n = BA.hdr[0];
   for (;;) {
@@ -483,7 +586,7 @@ __global__ void __launch_bounds__(N_NT, 4) narrow_rows_kernel(BatchArgs BA) {
     __syncthreads();
     const int row = s_row;
     if (row < 0) break;
-    narrow_row<T>(BA, row, dyn, sc, s_sel, s_bc, s_bcd, &s_cnt, &s_thr);
+    narrow_row<T>(BA, row, dyn, sc, s_sel, s_bc, s_bcd, &s_cnt, &s_thr, &s_flag);
   }
 }
 

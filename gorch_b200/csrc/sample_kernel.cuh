@@ -52,6 +52,8 @@ struct KernelArgs {
   const double* exp_table; // 256 doubles: 2^(j/256)
   int64_t row_offset;      // first row handled by this launch (for chunked launches)
   const int32_t* worklist; // single-CTA kernel only: [0] = count, [1..] = rows to process (null: every row)
+  void* vs_records;        // vocab-sharded local pass (narrow kernel only): [B] VsRecord to fill instead of drawing
+  int32_t vs_col_offset;   // global index of this slice's first column
 };
 
 template <typename T> struct Elem;

@@ -1,0 +1,129 @@
+// Vocab-sharded sampling: each rank holds a contiguous column slice of every row.
+//
+//   step 1 (every rank)   narrow_rows_kernel with KernelArgs::vs_records set: one pass over the
+//                         rank's slice per row, leaving a VsRecord (local maximum, every local
+//                         logit at or above the local k-th largest, with global indices)
+//   exchange              one all-gather of the records, rank order (done by the caller: NCCL)
+//   step 2 (every rank)   vocab_merge_kernel: joins the ranks' lists of a row, takes the global
+//                         k-th largest (ties kept, generate.go:157-164), and finishes the row
+//                         (softmax over the kept set, top-p, draw) exactly like the one-GPU path.
+//                         Every rank computes every id: the result needs no second exchange.
+//
+// The reference has no multi-device path; the row semantics are model/generate.go:147-240 and
+// model/qwen/generate.go:92-153 applied to the whole row.
+#pragma once
+
+#include "sample_batch.cuh"
+
+namespace gs {
+
+constexpr int VM_NT = 256;
+constexpr int VM_MAX_RANKS = 16;
+constexpr int VM_LIST = VM_MAX_RANKS * VS_CAND;             // 2048 entries
+constexpr int VM_DYN_BYTES = VM_LIST * 8 + 16384 + KEEP_MAX * 8;
+
+struct MergeArgs {
+  KernelArgs k;             // V = whole vocabulary; logits unused
+  const VsRecord* records;  // [nranks][B]
+  int32_t nranks;
+  int64_t B;
+};
+
+__global__ void __launch_bounds__(VM_NT, 4) vocab_merge_kernel(MergeArgs M) {
+  extern __shared__ __align__(16) unsigned char dyn[];
+  __shared__ bu::Scratch sc;
+  __shared__ uint32_t s_sel[256];
+  __shared__ int s_bc[4];
+  __shared__ double s_bcd[4];
+  __shared__ int s_cnt;
+  uint2* list = reinterpret_cast<uint2*>(dyn);                                   // joined candidates
+  unsigned char* work = dyn + VM_LIST * 8;                                        // 16 KB for finish_small_set
+  uint2* kept = reinterpret_cast<uint2*>(dyn + VM_LIST * 8 + 16384);             // KEEP_MAX entries
+  const KernelArgs& A = M.k;
+  const int tid = threadIdx.x;
+  constexpr int NW = VM_NT / 32;
+  for (int64_t row = blockIdx.x; row < M.B; row += gridDim.x) {
+    __syncthreads();
+    const RowCfg cfg = A.cfgs[row];
+    const float Tm = cfg.temperature;
+    RowDebug dbg;
+    dbg.sum_exp = 0; dbg.resum = 1.0; dbg.edge_lo = 0; dbg.edge_hi = 0; dbg.kept = 0;
+    dbg.max_scaled = 0; dbg.threshold = __int_as_float(0x7fc00000); dbg.path = 3;
+    for (int q = 0; q < 8; q++) dbg.cycles[q] = 0;
+    auto write_row = [&](int id, uint32_t fl) {
+      if (tid == 0) {
+        A.out_ids[row] = id;
+        if (A.out_flags) A.out_flags[row] = fl;
+        if (A.out_debug) A.out_debug[row] = dbg;
+      }
+    };
+    // ---- join the ranks' records
+    if (tid == 0) s_cnt = 0;
+    __syncthreads();
+    uint32_t fl_loc = 0u;
+    unsigned long long mx = 0ull;
+    for (int r = 0; r < M.nranks; r++) {
+      const VsRecord& rec = M.records[static_cast<int64_t>(r) * M.B + row];
+      const int n = min(max(rec.n, 0), VS_CAND);
+      fl_loc |= rec.flags;
+      if (n > 0) { const unsigned long long k = okey(rec.xmax); mx = k > mx ? k : mx; }
+      int base = 0;
+      if (tid == 0) { base = s_cnt; s_cnt = base + n; }
+      __syncthreads();
+      base = s_cnt - n;
+      for (int j = tid; j < n; j += VM_NT) list[base + j] = rec.cand[j];
+      __syncthreads();
+    }
+    const int cnt = s_cnt;
+    const uint32_t vfl = fl_loc;                             // uniform: every thread read every record header
+    if (vfl & VS_BAD_CFG) { write_row(-1, FLAG_BAD_CFG); continue; }
+    if ((vfl & (VS_OVERFLOW | VS_UNSUPPORTED)) || cnt == 0) { write_row(-1, FLAG_INTERNAL); continue; }
+    // ---- greedy (generate.go:134-144): largest logit, lowest index; a NaN at index 0 is never beaten
+    if (Tm == 0.0f) {
+      unsigned long long best = 0ull;
+      for (int j = tid; j < cnt; j += VM_NT) {
+        const unsigned long long p = (static_cast<unsigned long long>(okey(__uint_as_float(list[j].x))) << 32) |
+                                     static_cast<uint32_t>(~list[j].y);
+        best = p > best ? p : best;
+      }
+      best = bu::max_u64<NW>(best, sc, tid);
+      int id = static_cast<int>(~static_cast<uint32_t>(best & 0xffffffffull));
+      if (vfl & VS_NAN_AT_0) id = 0;
+      dbg.kept = 1;
+      write_row(id, 0u);
+      continue;
+    }
+    const float xmax = okey_to_float(static_cast<uint32_t>(mx));
+    const float m = scale_t(xmax, Tm);
+    dbg.max_scaled = m;
+    // A NaN anywhere, or an infinite maximum: the walk of generate.go:231-239 falls through
+    if ((vfl & VS_NONFINITE) || !(fabsf(m) < INFINITY)) {
+      dbg.sum_exp = __longlong_as_double(0x7ff8000000000000ll);
+      write_row(A.V - 1, FLAG_NONFINITE | FLAG_FALLBACK);
+      continue;
+    }
+    // ---- global k-th largest with ties (generate.go:157-164), then the kept set
+    const int topk = cfg.top_k;                              // 0 < top_k <= VS_CAND (checked by the local pass)
+    float thr = -INFINITY;
+    if (cnt > topk) {
+      const uint32_t kkey = bu::select_kth<VM_NT>(list, cnt, topk, s_sel, s_bc, tid);
+      thr = quotient_class_floor(okey_to_float(kkey), Tm);
+    }
+    __syncthreads();
+    if (tid == 0) s_cnt = 0;
+    __syncthreads();
+    for (int j = tid; j < cnt; j += VM_NT) {
+      const uint2 e = list[j];
+      if (__uint_as_float(e.x) >= thr) { const int slot = atomicAdd(&s_cnt, 1); if (slot < KEEP_MAX) kept[slot] = e; }
+    }
+    __syncthreads();
+    const int nk = s_cnt;
+    if (nk > KEEP_MAX) { write_row(-1, FLAG_INTERNAL); continue; }
+    const bool topp_on = (cfg.top_p > 0.0f && cfg.top_p < 1.0f);
+    const int mode = cfg.topp_mode;
+    const double plim = (mode == 0) ? static_cast<double>(cfg.top_p) * 1.5 : static_cast<double>(cfg.top_p);
+    finish_small_set<VM_NT>(A, row, kept, nk, m, Tm, topp_on, mode, plim, A.uniforms[row], work, sc, s_bcd, dbg, 0u);
+  }
+}
+
+}  // namespace gs

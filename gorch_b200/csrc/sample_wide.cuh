@@ -23,7 +23,7 @@
 // Row semantics: model/generate.go:147-240 (mode A), model/qwen/generate.go:92-153 (mode B).
 #pragma once
 
-#include "sample_batch.cuh"
+#include "sample_batch.cuh"   // includes row_stream.cuh
 
 namespace gs {
 
@@ -36,10 +36,6 @@ constexpr int W_NSUB = W_NT;            // sub-buckets of one weighted-selection
 constexpr int W_NW = W_NT / 32;
 constexpr int W_NB = 4096;              // histogram buckets
 constexpr int W_ZCAP = 2048;            // exact zone list capacity
-#ifndef GS_W_PF
-#define GS_W_PF 2
-#endif
-constexpr int W_PF = GS_W_PF;           // L2 prefetch distance in steps
 constexpr int W_G = 4;                  // steps per piece (power of two)
 constexpr int W_MAX_STEPS = (W_NT >= 512) ? 64 : 128;         // steps per warp and pass; longer rows go to the single-CTA kernel
 constexpr int W_MAX_PPW = W_MAX_STEPS / W_G;
@@ -69,11 +65,6 @@ __device__ __forceinline__ float bucket_floor_w(int bmax, float scale, float dcl
   return (bucket_w(t, scale, dclamp) <= bmax) ? t : __uint_as_float(__float_as_uint(t) - 1u);
 }
 
-__device__ __forceinline__ uint4 ldg_hint(const uint4* p, unsigned long long pol) {
-  uint4 v;
-  asm volatile("ld.global.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol));
-  return v;
-}
 __device__ __forceinline__ double lds_f64(uint32_t addr) {
   double v;
   asm("ld.shared.f64 %0, [%1];" : "=d"(v) : "r"(addr));
@@ -121,35 +112,6 @@ __device__ __forceinline__ void exp_fast_s2(float d0, float d1, uint32_t eb_mul,
   e1 = fma(E1, static_cast<double>(w1), E1);
 }
 constexpr double W_EXP_REL_ERR = 6e-10;   // bound of exp_fast_s against the exact exponential
-
-// What one thread needs to stream its warp's span of a row.
-struct WSpan {
-  const uint4* lane_src;   // this lane's first vector: row vector (first + lane)
-  int first;               // first vector of the warp's span
-  int rel;                 // vectors from lane_src to the row's end (<= 0: none)
-  int nst;                 // steps this warp runs
-  int omax;                // largest valid vector offset from lane_src
-  int clean_lo, clean_hi;  // steps [clean_lo, clean_hi) hold no logit outside the row (warp-uniform)
-};
-
-// The lane's vectors of step st. A vector past the row's end is replaced by the lane's last one
-// (or the row's first when the lane has none): always a valid address, and such vectors are
-// masked by the caller from their true index.
-template <typename T>
-__device__ __forceinline__ void w_load(const WSpan& sp, int st, unsigned long long pol, uint4& ra, uint4& rb) {
-  constexpr int EPI = 8 / Elem<T>::VEC, SV = 32 * EPI;
-  const int o = st * SV;
-  ra = ldg_hint(sp.lane_src + min(o, sp.omax), pol);
-  if (EPI == 2) rb = ldg_hint(sp.lane_src + min(o + 32, sp.omax), pol);
-  else rb = ra;
-  // ask L2 for the step W_PF steps further on: costs no register, and the load above then finds
-  // its line in L2 whether the row came from HBM or was evicted since the last pass
-  if (W_PF > 0) {
-    const int o2 = o + W_PF * SV;
-    asm volatile("prefetch.global.L2 [%0];" :: "l"(sp.lane_src + min(o2, sp.omax)));
-    if (EPI == 2) asm volatile("prefetch.global.L2 [%0];" :: "l"(sp.lane_src + min(o2 + 32, sp.omax)));
-  }
-}
 
 // Steps [st0, st1) of one pass; qa/qb hold the vectors of steps st0 .. st0+D-1 on entry and of
 // st1 .. st1+D-1 on exit (D steps of register prefetch). CLEAN runs hold no logit outside the
@@ -209,13 +171,19 @@ __device__ __noinline__ void wide_pass1(const WSpan& sp_in, const RowView<T>& rv
                                         float& xmax, float& xmin, bool& nan_seen) {
   const WSpan sp = sp_in;                // registers, not memory, inside the loop
   const RowView<T> rv = rv_in;
-  float vmax = -INFINITY, vmin = INFINITY;
-  uint32_t amax = 0u;                    // largest |bits|: above 0x7f800000 means a NaN
+  float vmax = -INFINITY, vmin = INFINITY;   // vmax with NaN-propagating maxima: NaN iff the span held one
 #define GS_BODY1(CL) [&](const float* x, uint32_t valid, int, int) {                             \
+    if (CL) {                                                                                    \
+      vmax = max3nan(vmax, x[0], x[1]); vmax = max3nan(vmax, x[2], x[3]);                        \
+      vmax = max3nan(vmax, x[4], x[5]); vmax = max3nan(vmax, x[6], x[7]);                        \
+      vmin = min3f(vmin, x[0], x[1]); vmin = min3f(vmin, x[2], x[3]);                            \
+      vmin = min3f(vmin, x[4], x[5]); vmin = min3f(vmin, x[6], x[7]);                            \
+    }                                                                                            \
     _Pragma("unroll") for (int c = 0; c < 8; c++) {                                              \
-      vmax = fmaxf(vmax, x[c]);                                                                  \
-      vmin = fminf(vmin, (CL || ((valid >> c) & 1u)) ? x[c] : INFINITY);                         \
-      amax = max(amax, __float_as_uint(x[c]) & 0x7fffffffu);                                     \
+      if (!CL) {                                                                                 \
+        vmax = maxnan(vmax, x[c]);                           /* masked logits read as -Inf */    \
+        vmin = fminf(vmin, ((valid >> c) & 1u) ? x[c] : INFINITY);                               \
+      }                                                                                          \
       if (HIST) {                                                                                \
         const float s = TONE ? x[c] : __fdiv_rn(x[c], Tm);                                       \
         /* NaN and anything above the anchor land in bucket 0 or W_NB-1: such rows are redone */ \
@@ -226,7 +194,7 @@ __device__ __noinline__ void wide_pass1(const WSpan& sp_in, const RowView<T>& rv
     } }
   GS_WIDE_STREAM(T, 2, sp, rv, pol, lane, GS_BODY1);
 #undef GS_BODY1
-  xmax = vmax; xmin = vmin; nan_seen = amax > 0x7f800000u;
+  xmax = vmax; xmin = vmin; nan_seen = (vmax != vmax);
 }
 
 // pass 2: count histogram of d (logits outside the row are not counted).
@@ -389,18 +357,7 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
   }
   const int ppw = (steps_max + W_G - 1) / W_G;               // pieces per warp
   const int npiece = W_NW * ppw;
-  WSpan sp;
-  sp.first = warp * span;
-  {
-    const int end = min(rv.nvec, sp.first + span);
-    sp.nst = (end > sp.first) ? (end - sp.first + SV - 1) / SV : 0;
-  }
-  sp.rel = rv.nvec - sp.first - lane;
-  sp.lane_src = rv.vbase + (sp.rel > 0 ? sp.first + lane : 0);
-  sp.omax = max(sp.rel - 1, 0);
-  // a step is clean when all its SV vectors exist and none is the row's first or last
-  sp.clean_lo = (sp.first == 0) ? min(1, sp.nst) : 0;
-  sp.clean_hi = max(sp.clean_lo, min(sp.nst, (rv.nvec - 1 - sp.first) / SV));
+  const WSpan sp = make_span<T>(rv, warp * span, span, lane);
 
   // ---- a sample of the row (every warp's first step) gives an upper estimate of the maximum
   // and the bucket width, so that pass 1 can already count the histogram the cut needs

@@ -17,6 +17,7 @@
 
 #include "../../include/gorch_cuda_shim.h"
 #include "sample_wide.cuh"
+#include "sample_vocab.cuh"
 
 namespace {
 
@@ -166,6 +167,8 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
   a.exp_table = c->exp_table;
   a.row_offset = 0;
   a.worklist = nullptr;
+  a.vs_records = nullptr;
+  a.vs_col_offset = 0;
   if (c->timing) CUDA_TRY(cudaEventRecord(c->ev0, c->stream), errOut);
   int klaunch = 1;
   const bool batch_mode = c->variant == 2 || (c->variant == 0 && B >= kBatchModeRows);
@@ -399,6 +402,7 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   if ((e = cudaFuncSetAttribute(gs::sample_cluster_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 109 * 1024)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::narrow_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::narrow_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::vocab_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::VM_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   return c;
@@ -548,6 +552,80 @@ int gorch_cuda_sample_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, in
                      out_probs, out_debug, 0, errOut);
 }
 
+int gorch_cuda_vocab_local_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                               int64_t Vslice, int64_t row_stride, int64_t col_offset,
+                               const GorchSampleCfg* cfgs, void* records, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = check_shape(dtype, B, Vslice, row_stride, errOut);
+  if (rc) return rc;
+  static_assert(sizeof(gs::VsRecord) == GORCH_VS_RECORD_BYTES, "record layout");
+  if (col_offset < 0 || col_offset + Vslice > 0x7fffff00ll) {
+    set_err(errOut, "gorch_cuda: column offset %lld out of range", (long long)col_offset);
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!logits || !cfgs || !records) { set_err(errOut, "gorch_cuda: null pointer argument"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if ((reinterpret_cast<uintptr_t>(logits) % elem_size(dtype)) != 0) {
+    set_err(errOut, "gorch_cuda: logits pointer not aligned to its element size");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  // every row goes through the narrow kernel: its work list is simply 0..B-1
+  const size_t ints = 16 + 3 * static_cast<size_t>(B) + 1;
+  rc = ensure(c->worklist, ints * sizeof(int32_t), errOut);
+  if (rc) return rc;
+  int32_t* base = static_cast<int32_t*>(c->worklist.ptr);
+  gs::BatchArgs ba;
+  ba.k.logits = logits; ba.k.row_stride = row_stride; ba.k.V = static_cast<int32_t>(Vslice);
+  ba.k.force_greedy = 0; ba.k.cfgs = reinterpret_cast<const gs::RowCfg*>(cfgs); ba.k.uniforms = nullptr;
+  ba.k.out_ids = nullptr; ba.k.out_flags = nullptr; ba.k.out_probs = nullptr; ba.k.out_debug = nullptr;
+  ba.k.exp_table = c->exp_table; ba.k.row_offset = 0; ba.k.worklist = nullptr;
+  ba.k.vs_records = records; ba.k.vs_col_offset = static_cast<int32_t>(col_offset);
+  ba.eb_table = c->eb_table;
+  ba.hdr = base; ba.list_narrow = base + 16; ba.list_wide = base + 16 + B; ba.list_single = base + 16 + 2 * B;
+  ba.B = B;
+  CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
+  gs::iota_list_kernel<<<static_cast<unsigned>((B + 255) / 256), 256, 0, c->stream>>>(ba);
+  const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
+  if (dtype == GORCH_CUDA_F32) gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
+  else gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
+  CUDA_TRY(cudaGetLastError(), errOut);
+  c->counters.kernel_launches += 2;
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_vocab_merge_dev(GorchCudaCtxRef ctx, const void* all_records, int nranks, int64_t B,
+                               int64_t V, const GorchSampleCfg* cfgs, const double* uniforms,
+                               int32_t* out_ids, uint32_t* out_flags, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if (nranks < 1 || nranks > gs::VM_MAX_RANKS) {
+    set_err(errOut, "gorch_cuda: vocab merge takes 1..%d ranks, got %d", gs::VM_MAX_RANKS, nranks);
+    return GORCH_CUDA_ERR_LIMIT;
+  }
+  int rc = check_shape(GORCH_CUDA_F32, B, V, V, errOut);
+  if (rc) return rc;
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!all_records || !cfgs || !uniforms || !out_ids) { set_err(errOut, "gorch_cuda: null pointer argument"); return GORCH_CUDA_ERR_BAD_ARG; }
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  gs::MergeArgs m;
+  m.k.logits = nullptr; m.k.row_stride = V; m.k.V = static_cast<int32_t>(V); m.k.force_greedy = 0;
+  m.k.cfgs = reinterpret_cast<const gs::RowCfg*>(cfgs); m.k.uniforms = uniforms;
+  m.k.out_ids = out_ids; m.k.out_flags = out_flags; m.k.out_probs = nullptr; m.k.out_debug = nullptr;
+  m.k.exp_table = c->exp_table; m.k.row_offset = 0; m.k.worklist = nullptr; m.k.vs_records = nullptr; m.k.vs_col_offset = 0;
+  m.records = static_cast<const gs::VsRecord*>(all_records);
+  m.nranks = nranks;
+  m.B = B;
+  const unsigned g = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
+  gs::vocab_merge_kernel<<<g, gs::VM_NT, gs::VM_DYN_BYTES, c->stream>>>(m);
+  CUDA_TRY(cudaGetLastError(), errOut);
+  c->counters.kernel_launches += 1;
+  c->counters.sample_launches += 1;
+  c->counters.rows += B;
+  return GORCH_CUDA_OK;
+}
+
 int64_t gorch_cuda_sample_row(GorchCudaCtxRef ctx, const float* logits, int64_t n,
                               float temperature, int64_t top_k, float top_p, int topp_mode,
                               double uniform, uint32_t* out_flag, char** errOut) {
@@ -623,6 +701,8 @@ int gorch_cuda_sample_dev_static(GorchCudaCtxRef ctx, const void* logits, int dt
   ba.k.out_flags = out_flags;
   ba.k.out_probs = nullptr;
   ba.k.out_debug = nullptr;
+  ba.k.vs_records = nullptr;
+  ba.k.vs_col_offset = 0;
   ba.k.exp_table = c->exp_table;
   ba.k.row_offset = 0;
   ba.k.worklist = nullptr;

@@ -57,6 +57,10 @@ def _logits_arg(logits: np.ndarray):
     return x, DTYPE_F32
 
 
+VS_CAND = 128                      # GORCH_VS_CAND
+VS_RECORD_BYTES = 16 + 8 * VS_CAND  # GORCH_VS_RECORD_BYTES
+
+
 class CudaSampler:
     """One device context (cf. metal.NewDevice, metal/metal.go:228-234): a
     device, a stream and grow-only staging buffers."""
@@ -223,6 +227,73 @@ class CudaSampler:
         rc = self._lib.gorch_cuda_sample_dev_static(self._ctx, logits_ptr, dtype, B, V, row_stride,
                                                     cfgs_ptr, uniforms_ptr, ids_ptr, flags_ptr, C.byref(err))
         _check(self._lib, rc, err)
+
+    # ---- vocab-sharded sampling (every rank holds a column slice of every row)
+    def vocab_local_ptrs(self, logits_ptr: int, dtype: int, B: int, Vslice: int, row_stride: int,
+                         col_offset: int, cfgs_ptr: int, records_ptr: int) -> None:
+        """gorch_cuda_vocab_local_dev: device pointers; fills B records of VS_RECORD_BYTES."""
+        err = C.c_void_p()
+        rc = self._lib.gorch_cuda_vocab_local_dev(self._ctx, logits_ptr, dtype, B, Vslice, row_stride,
+                                                  col_offset, cfgs_ptr, records_ptr, C.byref(err))
+        _check(self._lib, rc, err)
+
+    def vocab_merge_ptrs(self, records_ptr: int, nranks: int, B: int, V: int, cfgs_ptr: int,
+                         uniforms_ptr: int, ids_ptr: int, flags_ptr: int | None = None) -> None:
+        """gorch_cuda_vocab_merge_dev: device pointers; records of all ranks in rank order."""
+        err = C.c_void_p()
+        rc = self._lib.gorch_cuda_vocab_merge_dev(self._ctx, records_ptr, nranks, B, V, cfgs_ptr,
+                                                  uniforms_ptr, ids_ptr, flags_ptr, C.byref(err))
+        _check(self._lib, rc, err)
+
+    def vocab_local(self, logits_slice, cfgs, col_offset: int) -> np.ndarray:
+        """Step 1 on host arrays: this rank's [B, Vslice] columns -> records [B, VS_RECORD_BYTES] (uint8)."""
+        x, dtype = _logits_arg(logits_slice)
+        B, Vs = x.shape
+        cfgs = np.ascontiguousarray(cfgs, dtype=CFG_DTYPE)
+        rec = np.zeros((B, VS_RECORD_BYTES), dtype=np.uint8)
+        bufs = []
+        try:
+            b_log = self._buf(max(x.nbytes, 16)); bufs.append(b_log)
+            b_cfg = self._buf(cfgs.nbytes); bufs.append(b_cfg)
+            b_rec = self._buf(rec.nbytes); bufs.append(b_rec)
+            self._upload(b_log, x)
+            self._upload(b_cfg, cfgs)
+            ptr = self._lib.gorch_cuda_buffer_device_ptr
+            self.vocab_local_ptrs(ptr(b_log), dtype, B, Vs, Vs, int(col_offset), ptr(b_cfg), ptr(b_rec))
+            self.sync()
+            self._download(b_rec, rec)
+        finally:
+            for b in bufs:
+                self._lib.gorch_cuda_buffer_free(b)
+        return rec
+
+    def vocab_merge(self, all_records, cfgs, uniforms, V: int):
+        """Step 2 on host arrays: records [nranks, B, VS_RECORD_BYTES] -> (ids, flags) for all B rows."""
+        rec = np.ascontiguousarray(all_records, dtype=np.uint8)
+        nranks, B = rec.shape[0], rec.shape[1]
+        cfgs = np.ascontiguousarray(cfgs, dtype=CFG_DTYPE)
+        uniforms = np.ascontiguousarray(uniforms, dtype=np.float64)
+        ids = np.empty(B, dtype=np.int32)
+        flags = np.zeros(B, dtype=np.uint32)
+        bufs = []
+        try:
+            b_rec = self._buf(rec.nbytes); bufs.append(b_rec)
+            b_cfg = self._buf(cfgs.nbytes); bufs.append(b_cfg)
+            b_uni = self._buf(uniforms.nbytes); bufs.append(b_uni)
+            b_ids = self._buf(ids.nbytes); bufs.append(b_ids)
+            b_flg = self._buf(flags.nbytes); bufs.append(b_flg)
+            self._upload(b_rec, rec)
+            self._upload(b_cfg, cfgs)
+            self._upload(b_uni, uniforms)
+            ptr = self._lib.gorch_cuda_buffer_device_ptr
+            self.vocab_merge_ptrs(ptr(b_rec), nranks, B, int(V), ptr(b_cfg), ptr(b_uni), ptr(b_ids), ptr(b_flg))
+            self.sync()
+            self._download(b_ids, ids)
+            self._download(b_flg, flags)
+        finally:
+            for b in bufs:
+                self._lib.gorch_cuda_buffer_free(b)
+        return ids, flags
 
     def argmax_batch(self, logits) -> np.ndarray:
         x, dtype = _logits_arg(logits)

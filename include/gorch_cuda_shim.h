@@ -172,6 +172,27 @@ int gorch_cuda_sample_dev_static(GorchCudaCtxRef ctx, const void* logits, int dt
                                  const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
                                  char** errOut);
 
+/* Vocab-sharded sampling (no counterpart in the reference, which runs on one device): every
+ * rank holds the same B rows but only the columns [col_offset, col_offset + Vslice) of the
+ * vocabulary. Rows must have 0 < top_k <= GORCH_VS_CAND (the top-k bounds what has to cross the
+ * link) or temperature 0; other rows come back with id -1 and GORCH_FLAG_INTERNAL.
+ *   1. every rank: gorch_cuda_vocab_local_dev fills B records of GORCH_VS_RECORD_BYTES (local
+ *      maximum, and every local logit at or above the local top_k-th largest with its global
+ *      index: 16 header bytes + GORCH_VS_CAND pairs of (f32 bits, u32 index));
+ *   2. the caller all-gathers the records in rank order (NCCL; nranks * B records);
+ *   3. every rank: gorch_cuda_vocab_merge_dev joins the lists, keeps everything at or above the
+ *      global top_k-th largest (ties kept, model/generate.go:157-164) and finishes the row as
+ *      gorch_cuda_sample_dev does. Every rank computes all B ids, so no second exchange is needed.
+ * Device pointers, asynchronous on the context's stream. */
+#define GORCH_VS_CAND 128
+#define GORCH_VS_RECORD_BYTES (16 + 8 * GORCH_VS_CAND)
+int gorch_cuda_vocab_local_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                               int64_t Vslice, int64_t row_stride, int64_t col_offset,
+                               const GorchSampleCfg* cfgs, void* records, char** errOut);
+int gorch_cuda_vocab_merge_dev(GorchCudaCtxRef ctx, const void* all_records, int nranks, int64_t B,
+                               int64_t V, const GorchSampleCfg* cfgs, const double* uniforms,
+                               int32_t* out_ids, uint32_t* out_flags, char** errOut);
+
 /* One row, the exact shape of the reference's calls: sample(logits,
  * temperature, topK, topP) (generate.go:147) with the uniform passed in, and
  * argmax when temperature == 0. Returns the token id, or -1 with *errOut set. */

@@ -1,0 +1,81 @@
+"""Vocab-sharded sampling on one GPU: the N ranks' local passes run one after another on column
+slices of the same batch (through the C ABI), their records are stacked in rank order as the
+all-gather would leave them, and the merge must give what the CPU oracle gives on whole rows."""
+import numpy as np
+import pytest
+
+from gorch_b200 import workloads
+from gorch_b200.config import CFG_DTYPE, FLAG_BOUNDARY, FLAG_INTERNAL, FLAG_TIE_CUT, FLAG_TOPP_EDGE
+
+pytestmark = pytest.mark.gpu
+
+
+def run_sharded(sampler, logits, cfgs, uniforms, world):
+    V = logits.shape[1]
+    recs = []
+    for r in range(world):
+        lo, hi = workloads.shard_vocab(V, r, world)
+        recs.append(sampler.vocab_local(np.ascontiguousarray(logits[:, lo:hi]), cfgs, lo))
+    return sampler.vocab_merge(np.stack(recs), cfgs, uniforms, V)
+
+
+def check(sampler, oracle, logits, cfgs, uniforms, world):
+    ids, flags = run_sharded(sampler, logits, cfgs, uniforms, world)
+    want = oracle.sample_batch(logits, cfgs, uniforms, want_info=False, flags=oracle.FAST_KTH)["ids"]
+    excused = (flags & (FLAG_BOUNDARY | FLAG_TIE_CUT | FLAG_TOPP_EDGE)) != 0
+    assert not np.any(flags & FLAG_INTERNAL), "rows the kernels could not take"
+    bad = (ids != want) & ~excused
+    assert not bad.any(), f"rows {np.nonzero(bad)[0][:8]}: got {ids[bad][:8]} want {want[bad][:8]}"
+    return int(excused.sum())
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_c5_rows(sampler, oracle, world):
+    w = workloads.vocab_sharded(48)
+    check(sampler, oracle, w.logits, w.cfgs, w.uniforms, world)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_mixed_small_rows(sampler, oracle, world, mode):
+    rng = np.random.Generator(np.random.Philox(key=0xC0FFEE + world + mode))
+    B, V = 64, 5003                                    # V not divisible by the rank count
+    logits = (rng.standard_normal((B, V)) * 2.0).astype(np.float32)
+    logits[:, ::5] = np.round(logits[:, ::5] * 2) / 2   # many ties, some at the threshold
+    cfgs = np.zeros(B, dtype=CFG_DTYPE)
+    for i in range(B):
+        cfgs[i] = [(0.0, 0, 0.0, mode), (0.7, 50, 0.95, mode), (1.0, 1, 0.0, mode), (1.3, 96, 0.9, mode), (0.9, 7, 0.5, mode)][i % 5]
+    check(sampler, oracle, logits, cfgs, rng.random(B), world)
+
+
+def test_bf16_ties_and_tiny_slices(sampler, oracle):
+    rng = np.random.Generator(np.random.Philox(key=77))
+    B, V = 16, 40                                      # slices of 5 columns: top_k above the slice width
+    logits = workloads.f32_to_bf16_bits((rng.standard_normal((B, V)) * 3.0).astype(np.float32))
+    cfgs = np.zeros(B, dtype=CFG_DTYPE)
+    cfgs[:] = (0.7, 8, 0.95, 1)
+    check(sampler, oracle, logits, cfgs, rng.random(B), 8)
+
+
+def test_greedy_lowest_index_across_ranks(sampler):
+    B, V = 4, 4096
+    logits = np.zeros((B, V), np.float32)
+    logits[0, [100, 3000]] = 5.0                       # tie across two ranks: lowest index wins
+    logits[1, 4095] = 1.0
+    logits[2, 0] = np.nan                              # a NaN at index 0 is never beaten
+    logits[2, 77] = 9.0
+    logits[3, 2048] = np.nan                           # a NaN elsewhere is never selected
+    logits[3, 2049] = 2.0
+    cfgs = np.zeros(B, dtype=CFG_DTYPE)                # temperature 0
+    ids, flags = run_sharded(sampler, logits, cfgs, np.zeros(B), 4)
+    assert ids.tolist() == [100, 4095, 0, 2049]
+
+
+def test_rows_without_top_k_are_flagged(sampler):
+    B, V = 2, 1024
+    logits = np.random.default_rng(1).standard_normal((B, V)).astype(np.float32)
+    cfgs = np.zeros(B, dtype=CFG_DTYPE)
+    cfgs[0] = (1.0, 0, 0.9, 1)                         # top-k off: not supported when vocab-sharded
+    cfgs[1] = (1.0, 200, 0.9, 1)                       # above the record capacity
+    ids, flags = run_sharded(sampler, logits, cfgs, np.full(B, 0.5), 2)
+    assert ids.tolist() == [-1, -1] and np.all(flags & FLAG_INTERNAL)
