@@ -20,6 +20,7 @@ EXPORTS = [
     "gorch_cuda_sample_host", "gorch_cuda_sample_dev", "gorch_cuda_sample_dev_static", "gorch_cuda_sample_row",
     "gorch_cuda_argmax_host", "gorch_cuda_argmax_dev",
     "gorch_cuda_vocab_local_dev", "gorch_cuda_vocab_merge_dev",
+    "gorch_cuda_topk_dev", "gorch_cuda_multinomial_dev",
 ]
 
 
@@ -69,6 +70,8 @@ def load() -> C.CDLL:
         "gorch_cuda_argmax_dev": (i32, [p, p, i32, i64, i64, i64, p, err]),
         "gorch_cuda_vocab_local_dev": (i32, [p, p, i32, i64, i64, i64, i64, p, p, err]),
         "gorch_cuda_vocab_merge_dev": (i32, [p, p, i32, i64, i64, p, p, p, p, err]),
+        "gorch_cuda_topk_dev": (i32, [p, p, i32, i64, i64, i64, i64, p, p, p, err]),
+        "gorch_cuda_multinomial_dev": (i32, [p, p, i64, i64, i64, p, p, p, err]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)

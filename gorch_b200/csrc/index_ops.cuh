@@ -1,0 +1,164 @@
+// Tensor-level index ops of the reference as batched device ops.
+//
+//   Multinomial (index_ops.go:203-227): per row, the first index j with u < sum_{i<=j} probs[i]
+//   (f32 probabilities, f64 running sum), else V-1. multinomial_rows_kernel: 256 threads, rows
+//   pulled by a grid-stride loop; every warp sums its span of the row step by step (one f64 sum
+//   per warp-step of 256 probabilities), a block scan over the steps finds the step the uniform
+//   falls into, and one warp rescans that step in index order. The running sum is formed in a
+//   different order than the reference's sequential loop: a row whose uniform lies within 1e-6 of
+//   an edge of the chosen interval is flagged FLAG_BOUNDARY.
+//   TopK (index_ops.go:153-190) is the narrow kernel of sample_batch.cuh with KernelArgs::tk_k set.
+#pragma once
+
+#include "sample_batch.cuh"
+
+namespace gs {
+
+constexpr int MN_NT = 256;
+constexpr int MN_NW = MN_NT / 32;
+constexpr int MN_MAX_STEPS = 256;                          // steps per warp: rows up to 8 * 256 * 256 = 524288 probabilities
+constexpr int MN_DYN_BYTES = MN_NW * MN_MAX_STEPS * 8;     // 16 KB of step sums
+
+struct MultinomialArgs {
+  const float* probs;      // [B, row_stride]
+  int64_t row_stride;
+  int32_t V;
+  const double* uniforms;  // [B]
+  int32_t* out_ids;        // [B]
+  uint32_t* out_flags;     // [B] or null
+  int64_t B;
+};
+
+__global__ void __launch_bounds__(MN_NT, 4) multinomial_rows_kernel(MultinomialArgs M) {
+  extern __shared__ __align__(16) unsigned char dyn[];
+  __shared__ bu::Scratch sc;
+  __shared__ double s_bcd[4];
+  __shared__ int s_bc[2];
+  double* stepsum = reinterpret_cast<double*>(dyn);        // [warp][step], row order
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int SV = 64;                                   // vectors per warp-step (two per lane)
+  unsigned long long pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  for (int64_t row = blockIdx.x; row < M.B; row += gridDim.x) {
+    __syncthreads();
+    RowView<float> rv;
+    rv.init(M.probs + row * M.row_stride, M.V);
+    const double u = M.uniforms[row];
+    const int span = (((rv.nvec + MN_NW - 1) / MN_NW + SV - 1) / SV) * SV;
+    const int steps = span / SV;
+    int id = -1;
+    uint32_t fl = 0u;
+    if (steps > MN_MAX_STEPS) {                            // beyond the step table: not supported
+      if (tid == 0) { M.out_ids[row] = -1; if (M.out_flags) M.out_flags[row] = FLAG_INTERNAL; }
+      continue;
+    }
+    const WSpan sp = make_span<float>(rv, warp * span, span, lane);
+    for (int j = tid; j < MN_NW * steps; j += MN_NT) stepsum[j] = 0.0;
+    __syncthreads();
+    // masked value of element c of this lane's vectors in step st (0 outside the row)
+    auto vals = [&](int st, const uint4& a, const uint4& b, double* v) {
+      float x[8];
+      Elem<float>::unpack(a, x); Elem<float>::unpack(b, x + 4);
+      const int gv = sp.first + st * SV + lane;
+#pragma unroll
+      for (int c = 0; c < 8; c++) {
+        const int g = gv + 32 * (c / 4);
+        const int i = g * 4 - rv.shift + (c % 4);
+        v[c] = (g < rv.nvec && i >= 0 && i < rv.V) ? static_cast<double>(x[c]) : 0.0;
+      }
+    };
+    {
+      uint4 q0a, q0b, q1a, q1b;
+      w_load<float, N_PF>(sp, 0, pol, q0a, q0b);
+      w_load<float, N_PF>(sp, 1, pol, q1a, q1b);
+#pragma unroll 1
+      for (int st = 0; st < sp.nst; st++) {
+        const uint4 ca = q0a, cb = q0b;
+        q0a = q1a; q0b = q1b;
+        w_load<float, N_PF>(sp, st + 2, pol, q1a, q1b);
+        double v[8];
+        vals(st, ca, cb, v);
+        double s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+        s = warp_sum_d(s);
+        if (lane == 0) stepsum[warp * steps + st] = s;
+      }
+    }
+    __syncthreads();
+    // prefix over the warp-steps in row order: thread t owns steps [t*PER, t*PER+PER)
+    constexpr int PER = (MN_NW * MN_MAX_STEPS) / MN_NT;    // 8
+    const int nsteps = MN_NW * steps;
+    double loc[PER], acc = 0.0;
+#pragma unroll
+    for (int q = 0; q < PER; q++) { const int j = tid * PER + q; acc += (j < nsteps) ? stepsum[j] : 0.0; loc[q] = acc; }
+    double total;
+    const double ex = bu::scan_excl_d<MN_NW>(acc, total, sc, tid);
+    int mine = 0x7fffffff;
+#pragma unroll
+    for (int q = PER - 1; q >= 0; q--) { const int j = tid * PER + q; if (j < nsteps && u < ex + loc[q]) mine = j; }
+    const int jsel = bu::min_i<MN_NW>(mine, sc, tid);
+    if (jsel != 0x7fffffff && tid == jsel / PER) s_bcd[0] = ex + ((jsel % PER) ? loc[jsel % PER - 1] : 0.0);
+    if (tid == 0) s_bc[0] = -1;
+    __syncthreads();
+    if (jsel != 0x7fffffff && warp == 0) {
+      // rescan the chosen warp-step in index order: first vectors of lanes 0..31, then the second
+      const int w = jsel / steps, st = jsel % steps;
+      const WSpan sw = make_span<float>(rv, w * span, span, lane);
+      uint4 a, b;
+      w_load<float, 0>(sw, st, pol, a, b);
+      double v[8];
+      {
+        float x[8];
+        Elem<float>::unpack(a, x); Elem<float>::unpack(b, x + 4);
+        const int gv = sw.first + st * SV + lane;
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+          const int g = gv + 32 * (c / 4);
+          const int i = g * 4 - rv.shift + (c % 4);
+          v[c] = (g < rv.nvec && i >= 0 && i < rv.V) ? static_cast<double>(x[c]) : 0.0;
+        }
+      }
+      const double s0 = (v[0] + v[1]) + (v[2] + v[3]), s1 = (v[4] + v[5]) + (v[6] + v[7]);
+      const double i0 = warp_scan_incl_d(s0, lane), i1 = warp_scan_incl_d(s1, lane);
+      const double tot0 = __shfl_sync(FULL, i0, 31);
+      const double base = s_bcd[0];
+      double run = base + (i0 - s0);
+      int pick = 0x7fffffff;
+      double lo = 0.0, hi = 0.0;
+      const int gv = sw.first + st * SV + lane;
+#pragma unroll
+      for (int c = 0; c < 8; c++) {
+        if (c == 4) run = base + tot0 + (i1 - s1);
+        const double before = run;
+        run += v[c];
+        const int i = (gv + 32 * (c / 4)) * 4 - rv.shift + (c % 4);
+        if (pick == 0x7fffffff && u < run && i >= 0 && i < rv.V) { pick = i; lo = before; hi = run; }
+      }
+      const int best = __reduce_min_sync(FULL, pick);
+      if (best != 0x7fffffff && pick == best) { s_bc[0] = best; s_bcd[1] = lo; s_bcd[2] = hi; }
+      if (best == 0x7fffffff) {
+        // the block scan put u inside this step, this rescan (another order of additions) just past
+        // its end: u sits on the step's last edge to within rounding. Take the step's last index.
+        int last = -1;
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+          const int i = (gv + 32 * (c / 4)) * 4 - rv.shift + (c % 4);
+          if (i >= 0 && i < rv.V && (gv + 32 * (c / 4)) < rv.nvec) last = max(last, i);
+        }
+        last = __reduce_max_sync(FULL, last);
+        if (lane == 0) { s_bc[0] = last; s_bcd[1] = u; s_bcd[2] = u; }
+      }
+    }
+    __syncthreads();
+    if (jsel != 0x7fffffff && s_bc[0] >= 0) {
+      id = s_bc[0];
+      if ((s_bcd[1] > 0.0 && u - s_bcd[1] <= 1e-6) || s_bcd[2] - u <= 1e-6) fl |= FLAG_BOUNDARY;
+    } else {
+      id = M.V - 1;                                        // index_ops.go: falls through to the last index
+      fl |= FLAG_FALLBACK;
+      if (u - total <= 1e-6) fl |= FLAG_BOUNDARY;
+    }
+    if (tid == 0) { M.out_ids[row] = id; if (M.out_flags) M.out_flags[row] = fl; }
+  }
+}
+
+}  // namespace gs

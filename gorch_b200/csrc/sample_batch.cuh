@@ -255,6 +255,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
 
   RowCfg cfg;
   if (A.force_greedy) { cfg.temperature = 0.f; cfg.top_k = 0; cfg.top_p = 0.f; cfg.topp_mode = 0; }
+  else if (A.tk_k > 0) { cfg.temperature = 1.f; cfg.top_k = A.tk_k; cfg.top_p = 0.f; cfg.topp_mode = 0; }
   else cfg = A.cfgs[row_id];
   const float Tm = cfg.temperature;
   RowDebug dbg;
@@ -421,7 +422,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   // top_k-th largest is among them and nothing was lost; if not (the chunk was not typical of
   // the row), the row is redone by the single-CTA kernel. Not used for vocab-sharded slices.
   bool tight = false;
-  if (!A.vs_records && rv.nvec > warm) {
+  if (!A.vs_records && A.tk_k == 0 && rv.nvec > warm) {
     const int cnt0 = *s_cnt;
     const long long welems = static_cast<long long>(warm) * VEC;
     const int r = static_cast<int>((4ll * topk * welems + V - 1) / V) + 4;
@@ -540,6 +541,28 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   dbg.max_scaled = m;
   // A NaN anywhere, or an infinite maximum, makes the softmax sum NaN upstream
   // (generate.go:173-181): every comparison of the walk fails, result n-1 (:239).
+  if (A.tk_k > 0) {
+    // TopK op (index_ops.go:153-190): the k largest, descending, equal values by ascending index.
+    // NaNs order last here (the reference's comparator leaves them unspecified).
+    float* ov = A.tk_values + row_id * static_cast<int64_t>(topk);
+    int32_t* oi = A.tk_indices + row_id * static_cast<int64_t>(topk);
+    if (giveup) {                                            // more than 512 logits tie at the k-th value
+      for (int j = tid; j < topk; j += N_NT) { ov[j] = __int_as_float(0x7fc00000); oi[j] = -1; }
+      if (tid == 0 && A.out_flags) A.out_flags[row_id] = FLAG_INTERNAL;
+      return;
+    }
+    for (int j = tid; j < nk; j += N_NT) {
+      const uint32_t kj = okey(__uint_as_float(cand[j].x)), ij = cand[j].y;
+      int r = 0;
+      for (int l = 0; l < nk; l++) {
+        const uint32_t kl = okey(__uint_as_float(cand[l].x));
+        r += (kl > kj || (kl == kj && cand[l].y < ij)) ? 1 : 0;
+      }
+      if (r < topk) { ov[r] = __uint_as_float(cand[j].x); oi[r] = static_cast<int32_t>(ij); }
+    }
+    if (tid == 0 && A.out_flags) A.out_flags[row_id] = 0u;
+    return;
+  }
   if (A.vs_records) {                                        // vocab-sharded: hand the list over instead of drawing
     VsRecord& rec = static_cast<VsRecord*>(A.vs_records)[row_id];
     uint32_t fl = 0u;

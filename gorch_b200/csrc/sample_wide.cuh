@@ -95,9 +95,8 @@ __device__ __forceinline__ void upk2(f32x2_t v, float& a, float& b) { asm("mov.b
 __device__ __forceinline__ f32x2_t fma2(f32x2_t a, f32x2_t b, f32x2_t c) { f32x2_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
 __device__ __forceinline__ f32x2_t add2(f32x2_t a, f32x2_t b) { f32x2_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
 __device__ __forceinline__ f32x2_t mul2(f32x2_t a, f32x2_t b) { f32x2_t d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
-// exp_fast_s for two arguments at once
-__device__ __forceinline__ void exp_fast_s2(float d0, float d1, uint32_t eb_mul, uint32_t eb_bias, double& e0, double& e1) {
-  const f32x2_t D = pk2(d0, d1);
+// exp_fast_s for two arguments at once (D = the pair of d values)
+__device__ __forceinline__ void exp_fast_s2(f32x2_t D, uint32_t eb_mul, uint32_t eb_bias, double& e0, double& e1) {
   const f32x2_t F = fma2(D, pk2(-32.0f, -32.0f), pk2(8388608.0f, 8388608.0f));
   const f32x2_t DL = fma2(add2(F, pk2(-8388608.0f, -8388608.0f)), pk2(0.03125f, 0.03125f), D);
   f32x2_t T = fma2(DL, pk2(8.3333338e-3f, 8.3333338e-3f), pk2(4.1666668e-2f, 4.1666668e-2f));
@@ -243,7 +242,8 @@ __device__ __noinline__ void wide_pass3(const WSpan& sp_in, const RowView<T>& rv
       const float d0 = s0 - m, d1 = s1 - m;                                                      \
       double e0, e1;                                                                             \
       if (FAST) {                                                                                \
-        exp_fast_s2(CL ? d0 : fmaxf(d0, dfloor), CL ? d1 : fmaxf(d1, dfloor), eb_mul, eb_bias, e0, e1); \
+        if (CL) exp_fast_s2(pk2(d0, d1), eb_mul, eb_bias, e0, e1);                               \
+        else exp_fast_s2(pk2(fmaxf(d0, dfloor), fmaxf(d1, dfloor)), eb_mul, eb_bias, e0, e1);    \
         if (!CL) {                                                                               \
           const bool v0 = (valid >> c) & 1u, v1 = (valid >> (c + 1)) & 1u;                       \
           e0 = __hiloint2double(v0 ? __double2hiint(e0) : 0, v0 ? __double2loint(e0) : 0);       \

@@ -18,6 +18,7 @@
 #include "../../include/gorch_cuda_shim.h"
 #include "sample_wide.cuh"
 #include "sample_vocab.cuh"
+#include "index_ops.cuh"
 
 namespace {
 
@@ -169,6 +170,9 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
   a.worklist = nullptr;
   a.vs_records = nullptr;
   a.vs_col_offset = 0;
+  a.tk_values = nullptr;
+  a.tk_indices = nullptr;
+  a.tk_k = 0;
   if (c->timing) CUDA_TRY(cudaEventRecord(c->ev0, c->stream), errOut);
   int klaunch = 1;
   const bool batch_mode = c->variant == 2 || (c->variant == 0 && B >= kBatchModeRows);
@@ -402,6 +406,7 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   if ((e = cudaFuncSetAttribute(gs::sample_cluster_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 109 * 1024)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::narrow_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::narrow_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::multinomial_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::MN_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::vocab_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::VM_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
@@ -582,6 +587,7 @@ int gorch_cuda_vocab_local_dev(GorchCudaCtxRef ctx, const void* logits, int dtyp
   ba.k.out_ids = nullptr; ba.k.out_flags = nullptr; ba.k.out_probs = nullptr; ba.k.out_debug = nullptr;
   ba.k.exp_table = c->exp_table; ba.k.row_offset = 0; ba.k.worklist = nullptr;
   ba.k.vs_records = records; ba.k.vs_col_offset = static_cast<int32_t>(col_offset);
+  ba.k.tk_values = nullptr; ba.k.tk_indices = nullptr; ba.k.tk_k = 0;
   ba.eb_table = c->eb_table;
   ba.hdr = base; ba.list_narrow = base + 16; ba.list_wide = base + 16 + B; ba.list_single = base + 16 + 2 * B;
   ba.B = B;
@@ -614,6 +620,7 @@ int gorch_cuda_vocab_merge_dev(GorchCudaCtxRef ctx, const void* all_records, int
   m.k.cfgs = reinterpret_cast<const gs::RowCfg*>(cfgs); m.k.uniforms = uniforms;
   m.k.out_ids = out_ids; m.k.out_flags = out_flags; m.k.out_probs = nullptr; m.k.out_debug = nullptr;
   m.k.exp_table = c->exp_table; m.k.row_offset = 0; m.k.worklist = nullptr; m.k.vs_records = nullptr; m.k.vs_col_offset = 0;
+  m.k.tk_values = nullptr; m.k.tk_indices = nullptr; m.k.tk_k = 0;
   m.records = static_cast<const gs::VsRecord*>(all_records);
   m.nranks = nranks;
   m.B = B;
@@ -623,6 +630,73 @@ int gorch_cuda_vocab_merge_dev(GorchCudaCtxRef ctx, const void* all_records, int
   c->counters.kernel_launches += 1;
   c->counters.sample_launches += 1;
   c->counters.rows += B;
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_topk_dev(GorchCudaCtxRef ctx, const void* x, int dtype, int64_t B, int64_t V,
+                        int64_t row_stride, int64_t k, float* out_values, int32_t* out_indices,
+                        uint32_t* out_flags, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = check_shape(dtype, B, V, row_stride, errOut);
+  if (rc) return rc;
+  if (k < 1 || k > V) {                                    // the reference panics here (index_ops.go:160-162)
+    set_err(errOut, "gorch_cuda: TopK k=%lld out of range [1, %lld]", (long long)k, (long long)V);
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  if (k > gs::KFAST) {
+    set_err(errOut, "gorch_cuda: TopK supports k <= %d, got %lld", gs::KFAST, (long long)k);
+    return GORCH_CUDA_ERR_LIMIT;
+  }
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!x || !out_values || !out_indices) { set_err(errOut, "gorch_cuda: null pointer argument"); return GORCH_CUDA_ERR_BAD_ARG; }
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  const size_t ints = 16 + 3 * static_cast<size_t>(B) + 1;
+  rc = ensure(c->worklist, ints * sizeof(int32_t), errOut);
+  if (rc) return rc;
+  int32_t* base = static_cast<int32_t*>(c->worklist.ptr);
+  gs::BatchArgs ba;
+  ba.k.logits = x; ba.k.row_stride = row_stride; ba.k.V = static_cast<int32_t>(V);
+  ba.k.force_greedy = 0; ba.k.cfgs = nullptr; ba.k.uniforms = nullptr;
+  ba.k.out_ids = nullptr; ba.k.out_flags = out_flags; ba.k.out_probs = nullptr; ba.k.out_debug = nullptr;
+  ba.k.exp_table = c->exp_table; ba.k.row_offset = 0; ba.k.worklist = nullptr;
+  ba.k.vs_records = nullptr; ba.k.vs_col_offset = 0;
+  ba.k.tk_values = out_values; ba.k.tk_indices = out_indices; ba.k.tk_k = static_cast<int32_t>(k);
+  ba.eb_table = c->eb_table;
+  ba.hdr = base; ba.list_narrow = base + 16; ba.list_wide = base + 16 + B; ba.list_single = base + 16 + 2 * B;
+  ba.B = B;
+  CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
+  gs::iota_list_kernel<<<static_cast<unsigned>((B + 255) / 256), 256, 0, c->stream>>>(ba);
+  const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
+  if (dtype == GORCH_CUDA_F32) gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
+  else gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
+  CUDA_TRY(cudaGetLastError(), errOut);
+  c->counters.kernel_launches += 2;
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_multinomial_dev(GorchCudaCtxRef ctx, const float* probs, int64_t B, int64_t V,
+                               int64_t row_stride, const double* uniforms, int32_t* out_ids,
+                               uint32_t* out_flags, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = check_shape(GORCH_CUDA_F32, B, V, row_stride, errOut);
+  if (rc) return rc;
+  if (V > 8ll * gs::MN_MAX_STEPS * 256 - 64) {
+    set_err(errOut, "gorch_cuda: Multinomial supports rows up to %d probabilities", 8 * gs::MN_MAX_STEPS * 256 - 64);
+    return GORCH_CUDA_ERR_LIMIT;
+  }
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!probs || !uniforms || !out_ids) { set_err(errOut, "gorch_cuda: null pointer argument"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if ((reinterpret_cast<uintptr_t>(probs) % 4) != 0) { set_err(errOut, "gorch_cuda: probs pointer not aligned"); return GORCH_CUDA_ERR_BAD_ARG; }
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  gs::MultinomialArgs m;
+  m.probs = probs; m.row_stride = row_stride; m.V = static_cast<int32_t>(V);
+  m.uniforms = uniforms; m.out_ids = out_ids; m.out_flags = out_flags; m.B = B;
+  const unsigned g = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
+  gs::multinomial_rows_kernel<<<g, gs::MN_NT, gs::MN_DYN_BYTES, c->stream>>>(m);
+  CUDA_TRY(cudaGetLastError(), errOut);
+  c->counters.kernel_launches += 1;
   return GORCH_CUDA_OK;
 }
 
@@ -703,6 +777,9 @@ int gorch_cuda_sample_dev_static(GorchCudaCtxRef ctx, const void* logits, int dt
   ba.k.out_debug = nullptr;
   ba.k.vs_records = nullptr;
   ba.k.vs_col_offset = 0;
+  ba.k.tk_values = nullptr;
+  ba.k.tk_indices = nullptr;
+  ba.k.tk_k = 0;
   ba.k.exp_table = c->exp_table;
   ba.k.row_offset = 0;
   ba.k.worklist = nullptr;

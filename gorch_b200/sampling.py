@@ -295,6 +295,61 @@ class CudaSampler:
                 self._lib.gorch_cuda_buffer_free(b)
         return ids, flags
 
+    # ---- tensor-level index ops (index_ops.go:153-227)
+    def topk(self, x, k: int):
+        """gorch.TopK over the last axis of x [B,V] (f32, or uint16 holding bf16): (values [B,k]
+        float32 descending, indices [B,k] int32; equal values by ascending index)."""
+        a, dtype = _logits_arg(x)
+        B, V = a.shape
+        vals = np.empty((B, max(int(k), 0)), dtype=np.float32)   # a bad k is refused by the library below
+        idx = np.empty((B, max(int(k), 0)), dtype=np.int32)
+        bufs = []
+        try:
+            b_x = self._buf(max(a.nbytes, 16)); bufs.append(b_x)
+            b_v = self._buf(max(vals.nbytes, 16)); bufs.append(b_v)
+            b_i = self._buf(max(idx.nbytes, 16)); bufs.append(b_i)
+            self._upload(b_x, a)
+            ptr = self._lib.gorch_cuda_buffer_device_ptr
+            err = C.c_void_p()
+            rc = self._lib.gorch_cuda_topk_dev(self._ctx, ptr(b_x), dtype, B, V, V, int(k), ptr(b_v), ptr(b_i), None, C.byref(err))
+            _check(self._lib, rc, err)
+            self.sync()
+            if B:
+                self._download(b_v, vals)
+                self._download(b_i, idx)
+        finally:
+            for b in bufs:
+                self._lib.gorch_cuda_buffer_free(b)
+        return vals, idx
+
+    def multinomial(self, probs, uniforms):
+        """gorch.Multinomial with the uniforms supplied: probs [B,V] float32 -> (ids [B] int32, flags [B])."""
+        p = np.ascontiguousarray(probs, dtype=np.float32)
+        B, V = p.shape
+        uniforms = np.ascontiguousarray(uniforms, dtype=np.float64)
+        ids = np.empty(B, dtype=np.int32)
+        flags = np.zeros(B, dtype=np.uint32)
+        bufs = []
+        try:
+            b_p = self._buf(max(p.nbytes, 16)); bufs.append(b_p)
+            b_u = self._buf(max(uniforms.nbytes, 16)); bufs.append(b_u)
+            b_i = self._buf(max(ids.nbytes, 16)); bufs.append(b_i)
+            b_f = self._buf(max(flags.nbytes, 16)); bufs.append(b_f)
+            self._upload(b_p, p)
+            self._upload(b_u, uniforms)
+            ptr = self._lib.gorch_cuda_buffer_device_ptr
+            err = C.c_void_p()
+            rc = self._lib.gorch_cuda_multinomial_dev(self._ctx, ptr(b_p), B, V, V, ptr(b_u), ptr(b_i), ptr(b_f), C.byref(err))
+            _check(self._lib, rc, err)
+            self.sync()
+            if B:
+                self._download(b_i, ids)
+                self._download(b_f, flags)
+        finally:
+            for b in bufs:
+                self._lib.gorch_cuda_buffer_free(b)
+        return ids, flags
+
     def argmax_batch(self, logits) -> np.ndarray:
         x, dtype = _logits_arg(logits)
         B, V = x.shape

@@ -193,6 +193,24 @@ int gorch_cuda_vocab_merge_dev(GorchCudaCtxRef ctx, const void* all_records, int
                                int64_t V, const GorchSampleCfg* cfgs, const double* uniforms,
                                int32_t* out_ids, uint32_t* out_flags, char** errOut);
 
+/* The reference's tensor-level index ops as batched device ops (device pointers, asynchronous on
+ * the context's stream).
+ * TopK (index_ops.go:153-190): the k largest of each row of x [B,V] (f32, or bf16 upcast), values
+ * [B,k] descending and their indices [B,k]; equal values by ascending index (upstream's sort is
+ * unstable, so that order is unspecified there); NaNs order last. 1 <= k <= min(V, 256). A row with
+ * more than 512 logits tied at its k-th value gets indices -1 and GORCH_FLAG_INTERNAL in out_flags
+ * (may be NULL).
+ * Multinomial (index_ops.go:203-227): out_ids[b] = first j with uniforms[b] < sum_{i<=j} probs[b,i]
+ * (f64 running sum over f32 probabilities), else V-1 (GORCH_FLAG_FALLBACK). The sum is formed in a
+ * different order than upstream's loop; rows whose uniform lies within 1e-6 of an edge of the
+ * chosen interval carry GORCH_FLAG_BOUNDARY. Rows up to 524 224 probabilities. */
+int gorch_cuda_topk_dev(GorchCudaCtxRef ctx, const void* x, int dtype, int64_t B, int64_t V,
+                        int64_t row_stride, int64_t k, float* out_values, int32_t* out_indices,
+                        uint32_t* out_flags, char** errOut);
+int gorch_cuda_multinomial_dev(GorchCudaCtxRef ctx, const float* probs, int64_t B, int64_t V,
+                               int64_t row_stride, const double* uniforms, int32_t* out_ids,
+                               uint32_t* out_flags, char** errOut);
+
 /* One row, the exact shape of the reference's calls: sample(logits,
  * temperature, topK, topP) (generate.go:147) with the uniform passed in, and
  * argmax when temperature == 0. Returns the token id, or -1 with *errOut set. */

@@ -1,0 +1,84 @@
+"""gorch.TopK and gorch.Multinomial (index_ops.go:153-227) as device ops, through the C ABI:
+the reference's own known answers, then seeded cases against the CPU oracle."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from gorch_b200 import workloads
+from gorch_b200.config import FLAG_BOUNDARY, FLAG_FALLBACK
+from gorch_b200.sampling import GorchCudaError
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.fixture(scope="module")
+def known():
+    with open(os.path.join(HERE, "golden", "reference_known_answers.json")) as f:
+        return json.load(f)
+
+
+def test_reference_topk_cases(sampler, known):
+    for c in known["topk"]:
+        x = np.array(c["x"], dtype=np.float32)
+        vals, idx = sampler.topk(x, c["k"])
+        assert vals.tolist() == c["values"]
+        assert idx.tolist() == c["indices"]
+    bad = known["topk_invalid_k"]
+    for k in bad["ks"]:
+        with pytest.raises(GorchCudaError):
+            sampler.topk(np.zeros(bad["shape"], dtype=np.float32), k)
+
+
+@pytest.mark.parametrize("B,V,k", [(3, 8, 2), (5, 257, 7), (16, 50257, 40), (4, 4097, 256), (2, 5, 5), (7, 1000, 1)])
+def test_topk_matches_oracle(sampler, oracle, B, V, k):
+    rng = np.random.Generator(np.random.Philox(key=B * 1000003 + V * 17 + k))
+    x = (rng.standard_normal((B, V)) * 2.0).astype(np.float32)
+    x[:, ::3] = np.round(x[:, ::3] * 4) / 4            # ties, also across the k-th value
+    vals, idx = sampler.topk(x, k)
+    wv, wi = oracle.topk(x, k)
+    assert np.array_equal(vals, wv)
+    assert np.array_equal(idx.astype(np.int64), wi)    # ascending index among equals, as the oracle
+
+
+def test_topk_bf16_rows(sampler, oracle):
+    w = workloads.vocab_sharded(8)
+    vals, idx = sampler.topk(w.logits, 64)
+    wv, wi = oracle.topk(oracle.bf16_bits_to_f32(w.logits), 64)
+    assert np.array_equal(vals, wv) and np.array_equal(idx.astype(np.int64), wi)
+
+
+def test_reference_multinomial_one_hot(sampler, known):
+    for c in known["multinomial_one_hot"]:
+        p = np.array(c["probs"], dtype=np.float32)
+        for u in (0.0, 0.25, 0.5, 0.999999):
+            ids, _ = sampler.multinomial(p, [u] * p.shape[0])
+            assert ids.tolist() == c["want"]
+
+
+@pytest.mark.parametrize("B,V", [(4, 1), (6, 7), (9, 255), (5, 4096), (32, 50257), (3, 151936)])
+def test_multinomial_matches_oracle(sampler, oracle, B, V):
+    rng = np.random.Generator(np.random.Philox(key=B * 7919 + V))
+    logits = rng.standard_normal((B, V)) * 2.0
+    p = np.exp(logits - logits.max(axis=1, keepdims=True))
+    p = (p / p.sum(axis=1, keepdims=True)).astype(np.float32)
+    p[:, ::5] = 0.0                                     # zero-probability tokens are never drawn
+    u = rng.random(B)
+    u[0] = 0.0
+    if B > 1:
+        u[1] = 0.999999999                              # beyond the (deflated) total: falls through to V-1
+    ids, flags = sampler.multinomial(p, u)
+    want = oracle.multinomial(p, u)
+    excused = (flags & FLAG_BOUNDARY) != 0
+    assert np.array_equal(ids[~excused].astype(np.int64), want[~excused])
+    assert np.all(p[np.arange(B), ids][(flags & FLAG_FALLBACK) == 0] > 0)
+
+
+def test_multinomial_nan_row_falls_through(sampler, oracle):
+    p = np.full((2, 300), 1.0 / 300, dtype=np.float32)
+    p[0, 10] = np.nan                                   # every later comparison fails upstream
+    u = np.array([0.5, 0.5])
+    ids, flags = sampler.multinomial(p, u)
+    assert ids.tolist() == oracle.multinomial(p, u).tolist()
