@@ -75,24 +75,6 @@ struct Xchg {
   double local_target, base_mass, Re, S;
 };
 
-__device__ __forceinline__ uint32_t dkey_of(float d) {   // d <= 0 (or NaN): ascending = falling probability
-  return (d != d) ? 0x7fffffffu : (__float_as_uint(-d) & 0x7fffffffu);
-}
-// Zone order: falling probability, equal d by ascending index in mode B; mode A
-// removes the lowest index of a tie first (generate.go:208-212), so its survivors
-// are the highest indices and the index is complemented.
-__device__ __forceinline__ unsigned long long zone_key(float d, int idx, int mode) {
-  const uint32_t ix = (mode == 0) ? ~static_cast<uint32_t>(idx) : static_cast<uint32_t>(idx);
-  return (static_cast<unsigned long long>(dkey_of(d)) << 32) | ix;
-}
-__device__ __forceinline__ int zone_key_index(unsigned long long k, int mode) {
-  const uint32_t ix = static_cast<uint32_t>(k);
-  return static_cast<int>(mode == 0 ? ~ix : ix);
-}
-__device__ __forceinline__ float zone_key_d(unsigned long long k) {
-  return -__uint_as_float(static_cast<uint32_t>(k >> 32));
-}
-
 // 1024 buckets of width 1/32: round(-32 d) clamped to 1023. Non-decreasing as d falls.
 __device__ __forceinline__ int bucket1(float d) {
   float f = fmaf(fmaxf(d, -31.97f), -32.0f, 8388608.0f);

@@ -153,8 +153,9 @@ struct Cut {       // how the top-p cut applies to a full-row element
   int active;      // 0: every live element is kept
   int b1, b2;      // zone buckets; b < b1 kept, b > b2 dropped
   int mode;
-  int idx_c;       // index of the last kept zone element
-  double e_c;      // its mass; +Inf when no zone element is kept
+  int idx_c;       // index of the zone element at the cut
+  double e_c;      // its mass; +Inf when no zone element is kept, -1 when all are
+  int incl;        // 1: the element at the cut is itself kept
 };
 
 __device__ __forceinline__ double block_sum_d(double v, Ctl& c, int tid) {
@@ -787,7 +788,7 @@ __device__ void single_cta_row(const KernelArgs& A, const int64_t row_id, unsign
   const int nseg = (rv.nvec + seg_vecs - 1) / seg_vecs;
 
   // ---- pass 2: count histogram over level-0 buckets, zone bracket
-  if (tid == 0) { cut.active = 0; cut.b1 = 0; cut.b2 = NBUCKET - 1; cut.mode = mode; cut.idx_c = -1; cut.e_c = INFINITY; }
+  if (tid == 0) { cut.active = 0; cut.b1 = 0; cut.b2 = NBUCKET - 1; cut.mode = mode; cut.idx_c = -1; cut.e_c = INFINITY; cut.incl = 1; }
   int nzone = 0;
   __syncthreads();
   if (cut_on) {
@@ -845,12 +846,6 @@ __device__ void single_cta_row(const KernelArgs& A, const int64_t row_id, unsign
     if (tid == 0) { cut.active = 1; cut.b1 = b1; cut.b2 = b2; }
     __syncthreads();
   }
-  if (nzone > CAND_CAP) {
-    // Zone too large for the exact list (long runs of equal values): not served yet.
-    fill_probs(__longlong_as_double(0x7ff8000000000000ll));
-    finish(-1, flags | FLAG_INTERNAL, dbg);
-    return;
-  }
   const int zb1 = cut.b1, zb2 = cut.b2;
   const bool cut_active = cut.active != 0;
 
@@ -895,7 +890,142 @@ __device__ void single_cta_row(const KernelArgs& A, const int64_t row_id, unsign
   double Re = Ktot;           // kept mass in exp units
   int kept_zone = 0;
 
-  if (cut_active) {
+  // A zone that outgrew the list (long runs of equal logits around the cut) is cut by the same
+  // rule applied to the row itself: weighted selection on the keys (d, index), one pass per round.
+  const bool big_zone = cut_active && ctl.cand_count > CAND_CAP;
+  if (big_zone) {
+    auto each_zone = [&](auto&& fn) {
+      for (int v = tid; v < rv.nvec; v += NT) {
+        rv.visit(v, [&](float x, int i) {
+          if (!filt || x >= flt_lo) {
+            const float s = t_is_one ? x : __fdiv_rn(x, Tm);
+            const float d = s - m;
+            const int b = bucket0(d);
+            if (b >= zb1 && b <= zb2) fn(zone_key(d, i, mode), d);
+          }
+        });
+      }
+    };
+    auto crossed = [&](double g) -> bool { return mode == 0 ? (g / S > plim) : (g / S >= plim); };
+    double* sm = reinterpret_cast<double*>(pool + POOL_HIST);          // [NT] mass per sub-bucket
+    int* scn = reinterpret_cast<int*>(pool + POOL_HIST + NT * 8);      // [NT] count per sub-bucket
+    unsigned long long* few = reinterpret_cast<unsigned long long*>(pool + POOL_X);   // [32]
+    unsigned long long lo = ~0ull, hi = 0ull;
+    double z_loc = 0.0;
+    int n_loc = 0;
+    each_zone([&](unsigned long long k, float d) { lo = k < lo ? k : lo; hi = k > hi ? k : hi; z_loc += exp_neg_f64(d, s_tab); n_loc++; });
+    const double Z = block_sum_d(z_loc, ctl, tid);
+    int inrange = block_sum_i(n_loc, ctl, tid);
+    lo = ~block_max_u64(~lo, ctl, tid);
+    hi = block_max_u64(hi, ctl, tid);
+    S = Ktot + Z + Dtot;
+    bool bad = (Ktot > 0.0 && crossed(Ktot));                  // bracket violated
+    double gbase = Ktot;
+    bool all_in = false;
+    for (int iter = 0; iter < 10 && inrange > 32 && !bad && !all_in; iter++) {
+      const unsigned long long spn = hi - lo;
+      int shf = 0;
+      while (shf < 63 && (spn >> shf) >= static_cast<unsigned long long>(NT)) shf++;
+      __syncthreads();
+      sm[tid] = 0.0; scn[tid] = 0;
+      __syncthreads();
+      each_zone([&](unsigned long long k, float d) {
+        if (k >= lo && k <= hi) {
+          const int sb = static_cast<int>((k - lo) >> shf);
+          atomicAdd(&sm[sb], exp_neg_f64(d, s_tab));
+          atomicAdd(&scn[sb], 1);
+        }
+      });
+      __syncthreads();
+      const double mine = sm[tid];
+      double totm;
+      const double exm = block_scan_excl_d(mine, totm, ctl, tid);
+      const int first = (scn[tid] > 0 && crossed(gbase + exm + mine)) ? tid : NT;
+      const int sbx = block_min_i(first, ctl, tid);
+      if (sbx == NT) { all_in = true; break; }
+      if (tid == sbx) { ctl.bcast_d[0] = gbase + exm; ctl.bcast_i[0] = scn[tid]; }
+      __syncthreads();
+      gbase = ctl.bcast_d[0];
+      inrange = ctl.bcast_i[0];
+      const unsigned long long nlo = lo + (static_cast<unsigned long long>(sbx) << shf);
+      unsigned long long nhi = nlo + ((1ull << shf) - 1ull);
+      if (nhi < nlo || nhi > hi) nhi = hi;
+      lo = nlo; hi = nhi;
+    }
+    if (inrange > 32 && !all_in) bad = true;
+    unsigned long long cut_key = ~0ull;
+    int cut_incl = 1;
+    double g_at = gbase, g_before = gbase;
+    if (!bad && !all_in) {
+      __syncthreads();
+      if (tid == 0) ctl.cand_count = 0;
+      __syncthreads();
+      each_zone([&](unsigned long long k, float) {
+        if (k >= lo && k <= hi) { const int slot = atomicAdd(&ctl.cand_count, 1); if (slot < 32) few[slot] = k; }
+      });
+      __syncthreads();
+      const int nf = min(32, ctl.cand_count);
+      if (warp == 0) {
+        const unsigned long long k = (lane < nf) ? few[lane] : ~0ull;
+        const double e = (lane < nf) ? exp_neg_f64(zone_key_d(k), s_tab) : 0.0;
+        double g = gbase;
+        for (int l = 0; l < nf; l++) {
+          const unsigned long long kl = __shfl_sync(FULL, k, l);
+          const double el = __shfl_sync(FULL, e, l);
+          if (kl <= k) g += el;
+        }
+        const bool cr = (lane < nf) && crossed(g);
+        unsigned long long candk = cr ? k : ~0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const unsigned long long tt = __shfl_xor_sync(FULL, candk, o);
+          candk = tt < candk ? tt : candk;
+        }
+        const unsigned who = __ballot_sync(FULL, cr && k == candk);
+        if (lane == 0) { ctl.red_u64[0] = candk; ctl.bcast_i[1] = who ? 1 : 0; }
+        if (who && lane == __ffs(who) - 1) { ctl.bcast_d[1] = g; ctl.bcast_d[2] = g - e; }
+      }
+      __syncthreads();
+      if (ctl.bcast_i[1]) {
+        cut_key = ctl.red_u64[0];
+        g_at = ctl.bcast_d[1];
+        g_before = ctl.bcast_d[2];
+        cut_incl = (mode == 0) ? 0 : 1;
+      } else {
+        all_in = true;
+      }
+      __syncthreads();
+    }
+    if (!bad && all_in) {
+      cut_key = ~0ull; cut_incl = 1;
+      if (mode == 1 && !(Dtot == 0.0)) bad = true;             // the bracket promised the cut inside the zone
+    }
+    if (bad) {
+      fill_probs(__longlong_as_double(0x7ff8000000000000ll));
+      finish(-1, flags | FLAG_INTERNAL, dbg);
+      return;
+    }
+    if (!all_in) {
+      if (fabs(g_at / S - plim) <= 1e-12 || fabs(g_before / S - plim) <= 1e-12) flags |= FLAG_TOPP_EDGE;
+      if (mode == 1) {
+        int tie = 0;
+        each_zone([&](unsigned long long k, float) { tie |= (k > cut_key && (k >> 32) == (cut_key >> 32)) ? 1 : 0; });
+        if (block_max_i(tie, ctl, tid)) flags |= FLAG_TIE_CUT;
+      }
+    }
+    Re = all_in ? Ktot + Z : ((mode == 0) ? g_before : g_at);
+    __syncthreads();
+    each_zone([&](unsigned long long k, float d) {
+      if (k < cut_key || (cut_incl && k == cut_key)) {
+        atomicAdd(&s_kseg[rv.vec_of(zone_key_index(k, mode)) / seg_vecs], exp_neg_f64(d, s_tab));
+      }
+    });
+    if (tid == 0) {
+      if (all_in) { cut.e_c = -1.0; cut.idx_c = -1; cut.incl = 1; }
+      else { cut.e_c = exp_neg_f64(zone_key_d(cut_key), s_tab); cut.idx_c = zone_key_index(cut_key, mode); cut.incl = cut_incl; }
+    }
+    __syncthreads();
+  } else if (cut_active) {
     const int nz = min(ctl.cand_count, CAND_CAP);
     double* ze = reinterpret_cast<double*>(pool + POOL_HIST);   // [2048] mass per zone entry
     double* zs = reinterpret_cast<double*>(pool + POOL_X);      // [2048] masses in cut order, scanned
@@ -971,6 +1101,7 @@ __device__ void single_cta_row(const KernelArgs& A, const int64_t row_id, unsign
   }
   const double ec = cut.e_c;
   const int idxc = cut.idx_c;
+  const bool cincl = cut.incl != 0;
   // kept mass of one element (0 when filtered or cut away)
   auto kept_mass = [&](float x, int i) -> double {
     if (filt && !(x >= flt_lo)) return 0.0;
@@ -981,7 +1112,7 @@ __device__ void single_cta_row(const KernelArgs& A, const int64_t row_id, unsign
       int b = bucket0(d);
       if (b > zb2) return 0.0;
       if (b >= zb1) {
-        bool keep = (e > ec) || (e == ec && (mode == 0 ? i >= idxc : i <= idxc));
+        bool keep = (e > ec) || (e == ec && (mode == 0 ? (cincl ? i >= idxc : i > idxc) : (cincl ? i <= idxc : i < idxc)));
         if (!keep) return 0.0;
       }
     }

@@ -36,6 +36,10 @@ constexpr int W_NSUB = W_NT;            // sub-buckets of one weighted-selection
 constexpr int W_NW = W_NT / 32;
 constexpr int W_NB = 4096;              // histogram buckets
 constexpr int W_ZCAP = 2048;            // exact zone list capacity
+#ifndef GS_W_D1
+#define GS_W_D1 2
+#endif
+constexpr int W_D1 = GS_W_D1;           // steps of register prefetch in pass 1
 constexpr int W_G = 4;                  // steps per piece (power of two)
 constexpr int W_MAX_STEPS = (W_NT >= 512) ? 64 : 128;         // steps per warp and pass; longer rows go to the single-CTA kernel
 constexpr int W_MAX_PPW = W_MAX_STEPS / W_G;
@@ -191,7 +195,7 @@ __device__ __noinline__ void wide_pass1(const WSpan& sp_in, const RowView<T>& rv
         if (CL || ((valid >> c) & 1u)) asm volatile("red.shared.add.u32 [%0], 1;" :: "r"(a) : "memory"); \
       }                                                                                          \
     } }
-  GS_WIDE_STREAM(T, 2, sp, rv, pol, lane, GS_BODY1);
+  GS_WIDE_STREAM(T, W_D1, sp, rv, pol, lane, GS_BODY1);
 #undef GS_BODY1
   xmax = vmax; xmin = vmin; nan_seen = (vmax != vmax);
 }
@@ -284,6 +288,30 @@ __device__ __noinline__ void wide_pass3(const WSpan& sp_in, const RowView<T>& rv
   GS_WIDE_STREAM(T, 1, sp, rv, pol, lane, GS_BODY3);
 #undef GS_BODY3
   Ssum = stot; Ksum = ksum;
+}
+
+// fn(key, d) for every logit of the warp's span that lies in the zone dB <= d < dA, streamed from
+// global memory. Only rows whose zone outgrew the shared list come here (long runs of equal
+// logits around the cut), so every step takes the masked form.
+template <typename T, typename F>
+__device__ __forceinline__ void wide_for_zone(const WSpan& sp, const RowView<T>& rv, unsigned long long pol, int lane,
+                                              float m, float Tm, float dA, float dB, int mode, F&& fn) {
+  constexpr int VEC = Elem<T>::VEC;
+  uint4 qa[1], qb[1];
+  w_load<T>(sp, 0, pol, qa[0], qb[0]);
+  wide_steps<T, 1, false>(sp, rv, pol, lane, 0, sp.nst, qa, qb, [&](const float* x, uint32_t valid, int, int gv) {
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+      if ((valid >> c) & 1u) {
+        const float s = (Tm == 1.0f) ? x[c] : __fdiv_rn(x[c], Tm);
+        const float d = s - m;
+        if (d < dA && d >= dB) {
+          const int i = (gv + 32 * (c / VEC)) * VEC - rv.shift + (c % VEC);
+          fn(zone_key(d, i, mode), d);
+        }
+      }
+    }
+  });
 }
 
 struct WideShared {
@@ -488,10 +516,6 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
       if (b >= b1 && b <= b2) nz_part += cb[j];
     }
     const int nzone = bu::sum_i<W_NW>(nz_part, sc, tid);
-    if (nzone > W_ZCAP) {                                    // zone larger than the exact list
-      if (tid == 0) hand_to_single(BA, row_id);
-      return;
-    }
     const float qA = bucket_floor_w(b1 - 1, scale, dclamp);  // certainly kept: q >= qA
     const float qB = bucket_floor_w(b2, scale, dclamp);      // certainly dropped: q < qB
     if (!anchored) {
@@ -539,10 +563,9 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
   bu::sum_d3<W_NW>(S, Ktot, unused, sc, tid);
   const int nz = sh.cnt;
   stamp(2);
-  if (nz > W_ZCAP) {
-    if (tid == 0) hand_to_single(BA, row_id);
-    return;
-  }
+  // A zone that outgrew the list (long runs of equal logits around the cut): the same selection
+  // runs over the row itself, one more pass per round.
+  const bool big = cut_on && nz > W_ZCAP;
   dbg.sum_exp = S;
 
   // ---- exact cut inside the zone by weighted selection
@@ -550,11 +573,21 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
   int cut_incl = 0;
   bool bad = false;
   if (cut_on && nz > 0) {
-    for (int j = tid; j < nz; j += W_NT) {                   // entries -> keys, in place
-      const uint2 e = zl[j];
-      zk[j] = zone_key(__uint_as_float(e.x), static_cast<int>(e.y), mode);
+    if (!big) {
+      for (int j = tid; j < nz; j += W_NT) {                 // entries -> keys, in place
+        const uint2 e = zl[j];
+        zk[j] = zone_key(__uint_as_float(e.x), static_cast<int>(e.y), mode);
+      }
     }
     __syncthreads();
+    // every zone key with its d: from the list, or from the row when the list overflowed
+    auto each_zone = [&](auto&& fn) {
+      if (!big) {
+        for (int j = tid; j < nz; j += W_NT) { const unsigned long long k = zk[j]; fn(k, zone_key_d(k)); }
+      } else {
+        wide_for_zone<T>(sp, rv, pol_keep, lane, m, Tm, dA, dB, mode, fn);
+      }
+    };
     // G(c) = Ktot + mass{key <= c} rises along the zone order. Both flavours need the first key c*
     // where G crosses: mode B (first G/S >= p) keeps through c*, mode A (first G/S > 1.5p) keeps
     // everything before it. Narrow [lo, hi] around c* with linear sub-buckets until at most 32
@@ -564,27 +597,27 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     double* sm = reinterpret_cast<double*>(hist);            // [W_NSUB] mass per sub-bucket
     int* scn = reinterpret_cast<int*>(hist) + 2 * W_NSUB;    // [W_NSUB] count per sub-bucket
     unsigned long long lo = ~0ull, hi = 0ull;
-    for (int j = tid; j < nz; j += W_NT) { const unsigned long long k = zk[j]; lo = k < lo ? k : lo; hi = k > hi ? k : hi; }
+    int nz_loc = 0;
+    each_zone([&](unsigned long long k, float) { lo = k < lo ? k : lo; hi = k > hi ? k : hi; nz_loc++; });
     lo = bu::min_u64<W_NW>(lo, sc, tid);
     hi = bu::max_u64<W_NW>(hi, sc, tid);
     double gbase = Ktot;                                     // Ktot + mass of keys below lo; never crossed
-    int inrange = nz;
+    int inrange = big ? bu::sum_i<W_NW>(nz_loc, sc, tid) : nz;
     bool all_in = false;
-    for (int iter = 0; iter < 8 && inrange > 32 && !bad && !all_in; iter++) {
+    for (int iter = 0; iter < 10 && inrange > 32 && !bad && !all_in; iter++) {
       const unsigned long long spn = hi - lo;
       int shf = 0;
       while (shf < 63 && (spn >> shf) >= static_cast<unsigned long long>(W_NSUB)) shf++;
       __syncthreads();
       sm[tid] = 0.0; scn[tid] = 0;                           // W_NT == W_NSUB
       __syncthreads();
-      for (int j = tid; j < nz; j += W_NT) {
-        const unsigned long long k = zk[j];
+      each_zone([&](unsigned long long k, float d) {
         if (k >= lo && k <= hi) {
           const int sb = static_cast<int>((k - lo) >> shf);
-          atomicAdd(&sm[sb], exp_safe(zone_key_d(k), s_tab));
+          atomicAdd(&sm[sb], exp_safe(d, s_tab));
           atomicAdd(&scn[sb], 1);
         }
-      }
+      });
       __syncthreads();
       const double mine = sm[tid];
       double totm;
@@ -608,10 +641,9 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
       __syncthreads();
       if (tid == 0) sh.cnt = 0;
       __syncthreads();
-      for (int j = tid; j < nz; j += W_NT) {
-        const unsigned long long k = zk[j];
+      each_zone([&](unsigned long long k, float) {
         if (k >= lo && k <= hi) { const int slot = atomicAdd(&sh.cnt, 1); if (slot < 32) few[slot] = k; }
-      }
+      });
       __syncthreads();
       const int nf = min(32, sh.cnt);
       if (warp == 0) {
@@ -656,7 +688,7 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
       if (mode == 1) {
         // a later key with the same d as c*: the cut separates equal probabilities
         int tie = 0;
-        for (int j = tid; j < nz; j += W_NT) { const unsigned long long k = zk[j]; tie |= (k > cut_key && (k >> 32) == (cut_key >> 32)) ? 1 : 0; }
+        each_zone([&](unsigned long long k, float) { tie |= (k > cut_key && (k >> 32) == (cut_key >> 32)) ? 1 : 0; });
         if (bu::max_i<W_NW>(tie, sc, tid)) flags |= FLAG_TIE_CUT;
       }
     }
@@ -666,14 +698,13 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     }
     // kept zone entries add their mass to the piece they sit in
     __syncthreads();
-    for (int j = tid; j < nz; j += W_NT) {
-      const unsigned long long k = zk[j];
+    each_zone([&](unsigned long long k, float d) {
       if (k < cut_key || (cut_incl && k == cut_key)) {
         const int v = rv.vec_of(zone_key_index(k, mode));
         const int w = v / span;
-        atomicAdd(&part[w * ppw + (v - w * span) / PV], exp_safe(zone_key_d(k), s_tab));
+        atomicAdd(&part[w * ppw + (v - w * span) / PV], exp_safe(d, s_tab));
       }
-    }
+    });
     __syncthreads();
   }
   // ---- kept mass and the piece that holds the drawn token: prefix over the pieces in row order
