@@ -323,6 +323,145 @@ struct WideShared {
   int row;
 };
 
+// The exact cut for a zone that outgrew the shared list (long runs of equal logits around the
+// cut): the weighted selection of wide_row, with the row itself as the source of the zone's keys,
+// one more pass per round. Adds the kept zone mass to part[]; false: the bracket did not hold.
+template <typename T>
+__device__ __noinline__ bool wide_big_zone(const WSpan& sp_in, const RowView<T>& rv_in, unsigned long long pol, WideShared& sh,
+                                           uint32_t* hist, double* part, const double* s_tab, float m, float Tm, float dA,
+                                           float dB, float dlow, int mode, double plim, double S, double Ktot, bool fast_ok,
+                                           int span, int ppw, unsigned long long& cut_key_out, int& cut_incl_out, uint32_t& flags) {
+  const WSpan sp = sp_in;
+  const RowView<T> rv = rv_in;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int PV = W_G * 32 * (8 / Elem<T>::VEC);
+  bu::Scratch& sc = sh.sc;
+  unsigned long long cut_key = 0ull;
+  int cut_incl = 0;
+  bool bad = false;
+  {
+    // every zone key with its d: from the list, or from the row when the list overflowed
+    auto each_zone = [&](auto&& fn) { wide_for_zone<T>(sp, rv, pol, lane, m, Tm, dA, dB, mode, fn); };
+    // G(c) = Ktot + mass{key <= c} rises along the zone order. Both flavours need the first key c*
+    // where G crosses: mode B (first G/S >= p) keeps through c*, mode A (first G/S > 1.5p) keeps
+    // everything before it. Narrow [lo, hi] around c* with linear sub-buckets until at most 32
+    // keys remain, then one warp finishes.
+    auto crossed = [&](double g) -> bool { return mode == 0 ? (g / S > plim) : (g / S >= plim); };
+    if (Ktot > 0.0 && crossed(Ktot)) bad = true;             // the bracket was wrong
+    double* sm = reinterpret_cast<double*>(hist);            // [W_NSUB] mass per sub-bucket
+    int* scn = reinterpret_cast<int*>(hist) + 2 * W_NSUB;    // [W_NSUB] count per sub-bucket
+    unsigned long long lo = ~0ull, hi = 0ull;
+    int nz_loc = 0;
+    each_zone([&](unsigned long long k, float) { lo = k < lo ? k : lo; hi = k > hi ? k : hi; nz_loc++; });
+    lo = bu::min_u64<W_NW>(lo, sc, tid);
+    hi = bu::max_u64<W_NW>(hi, sc, tid);
+    double gbase = Ktot;                                     // Ktot + mass of keys below lo; never crossed
+    int inrange = bu::sum_i<W_NW>(nz_loc, sc, tid);
+    bool all_in = false;
+    for (int iter = 0; iter < 10 && inrange > 32 && !bad && !all_in; iter++) {
+      const unsigned long long spn = hi - lo;
+      int shf = 0;
+      while (shf < 63 && (spn >> shf) >= static_cast<unsigned long long>(W_NSUB)) shf++;
+      __syncthreads();
+      sm[tid] = 0.0; scn[tid] = 0;                           // W_NT == W_NSUB
+      __syncthreads();
+      each_zone([&](unsigned long long k, float d) {
+        if (k >= lo && k <= hi) {
+          const int sb = static_cast<int>((k - lo) >> shf);
+          atomicAdd(&sm[sb], exp_safe(d, s_tab));
+          atomicAdd(&scn[sb], 1);
+        }
+      });
+      __syncthreads();
+      const double mine = sm[tid];
+      double totm;
+      const double exm = bu::scan_excl_d<W_NW>(mine, totm, sc, tid);
+      const int first = (scn[tid] > 0 && crossed(gbase + exm + mine)) ? tid : W_NSUB;
+      const int sbx = bu::min_i<W_NW>(first, sc, tid);
+      if (sbx == W_NSUB) { all_in = true; break; }
+      if (tid == sbx) { sh.bcd[0] = gbase + exm; sh.bc[0] = scn[tid]; }
+      __syncthreads();
+      gbase = sh.bcd[0];
+      inrange = sh.bc[0];
+      const unsigned long long nlo = lo + (static_cast<unsigned long long>(sbx) << shf);
+      unsigned long long nhi = nlo + ((1ull << shf) - 1ull);
+      if (nhi < nlo || nhi > hi) nhi = hi;
+      lo = nlo; hi = nhi;
+    }
+    if (inrange > 32 && !all_in) bad = true;
+    double g_at = gbase, g_before = gbase;
+    if (!bad && !all_in) {
+      unsigned long long* few = reinterpret_cast<unsigned long long*>(hist);   // [32]
+      __syncthreads();
+      if (tid == 0) sh.cnt = 0;
+      __syncthreads();
+      each_zone([&](unsigned long long k, float) {
+        if (k >= lo && k <= hi) { const int slot = atomicAdd(&sh.cnt, 1); if (slot < 32) few[slot] = k; }
+      });
+      __syncthreads();
+      const int nf = min(32, sh.cnt);
+      if (warp == 0) {
+        const unsigned long long k = (lane < nf) ? few[lane] : ~0ull;
+        const double e = (lane < nf) ? exp_safe(zone_key_d(k), s_tab) : 0.0;
+        double g = gbase;                                    // G(k) = gbase + masses of the keys <= k
+        for (int l = 0; l < nf; l++) {
+          const unsigned long long kl = __shfl_sync(FULL, k, l);
+          const double el = __shfl_sync(FULL, e, l);
+          if (kl <= k) g += el;
+        }
+        const bool cr = (lane < nf) && crossed(g);
+        unsigned long long candk = cr ? k : ~0ull;           // first crossed key = smallest crossed key
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const unsigned long long tt = __shfl_xor_sync(FULL, candk, o);
+          candk = tt < candk ? tt : candk;
+        }
+        const unsigned who = __ballot_sync(FULL, cr && k == candk);
+        if (lane == 0) { sc.u[0] = candk; sh.bc[1] = who ? 1 : 0; }
+        if (who && lane == __ffs(who) - 1) { sh.bcd[1] = g; sh.bcd[2] = g - e; }
+      }
+      __syncthreads();
+      if (sh.bc[1]) {
+        cut_key = sc.u[0];
+        g_at = sh.bcd[1];
+        g_before = sh.bcd[2];
+        cut_incl = (mode == 0) ? 0 : 1;
+      } else {
+        all_in = true;                                       // rounding: nothing in the last group crossed
+      }
+      __syncthreads();
+    }
+    if (!bad && all_in) {
+      cut_key = ~0ull; cut_incl = 1;
+      if (mode == 1 && dlow < dB) bad = true;                // logits below the zone exist: the bracket promised a crossing
+    }
+    if (!bad && !all_in) {
+      // the sums carry exp_fast_s's error; in G/S >= p it enters as 2 p (1-p) times that bound
+      const double etol = 1e-12 + (fast_ok ? 2.0 * plim * fabs(1.0 - plim) * W_EXP_REL_ERR : 0.0);
+      if (fabs(g_at / S - plim) <= etol || fabs(g_before / S - plim) <= etol) flags |= FLAG_TOPP_EDGE;
+      if (mode == 1) {
+        // a later key with the same d as c*: the cut separates equal probabilities
+        int tie = 0;
+        each_zone([&](unsigned long long k, float) { tie |= (k > cut_key && (k >> 32) == (cut_key >> 32)) ? 1 : 0; });
+        if (bu::max_i<W_NW>(tie, sc, tid)) flags |= FLAG_TIE_CUT;
+      }
+    }
+    if (bad) return false;
+    // kept zone entries add their mass to the piece they sit in
+    __syncthreads();
+    each_zone([&](unsigned long long k, float d) {
+      if (k < cut_key || (cut_incl && k == cut_key)) {
+        const int v = rv.vec_of(zone_key_index(k, mode));
+        const int w = v / span;
+        atomicAdd(&part[w * ppw + (v - w * span) / PV], exp_safe(d, s_tab));
+      }
+    });
+    __syncthreads();
+  }
+  cut_key_out = cut_key; cut_incl_out = cut_incl;
+  return true;
+}
+
 template <typename T>
 __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned char* dyn, WideShared& sh,
                          unsigned long long pol_keep, unsigned long long pol_drop) {
@@ -572,22 +711,18 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
   unsigned long long cut_key = 0ull;       // zone entries are kept when key < cut_key, or == with cut_incl
   int cut_incl = 0;
   bool bad = false;
-  if (cut_on && nz > 0) {
-    if (!big) {
-      for (int j = tid; j < nz; j += W_NT) {                 // entries -> keys, in place
-        const uint2 e = zl[j];
-        zk[j] = zone_key(__uint_as_float(e.x), static_cast<int>(e.y), mode);
-      }
+  if (big) {
+    if (!wide_big_zone<T>(sp, rv, pol_keep, sh, hist, part, s_tab, m, Tm, dA, dB, dlow, mode, plim, S, Ktot, fast_ok,
+                          span, ppw, cut_key, cut_incl, flags)) {
+      if (tid == 0) hand_to_single(BA, row_id);
+      return;
+    }
+  } else if (cut_on && nz > 0) {
+    for (int j = tid; j < nz; j += W_NT) {                   // entries -> keys, in place
+      const uint2 e = zl[j];
+      zk[j] = zone_key(__uint_as_float(e.x), static_cast<int>(e.y), mode);
     }
     __syncthreads();
-    // every zone key with its d: from the list, or from the row when the list overflowed
-    auto each_zone = [&](auto&& fn) {
-      if (!big) {
-        for (int j = tid; j < nz; j += W_NT) { const unsigned long long k = zk[j]; fn(k, zone_key_d(k)); }
-      } else {
-        wide_for_zone<T>(sp, rv, pol_keep, lane, m, Tm, dA, dB, mode, fn);
-      }
-    };
     // G(c) = Ktot + mass{key <= c} rises along the zone order. Both flavours need the first key c*
     // where G crosses: mode B (first G/S >= p) keeps through c*, mode A (first G/S > 1.5p) keeps
     // everything before it. Narrow [lo, hi] around c* with linear sub-buckets until at most 32
@@ -597,27 +732,27 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     double* sm = reinterpret_cast<double*>(hist);            // [W_NSUB] mass per sub-bucket
     int* scn = reinterpret_cast<int*>(hist) + 2 * W_NSUB;    // [W_NSUB] count per sub-bucket
     unsigned long long lo = ~0ull, hi = 0ull;
-    int nz_loc = 0;
-    each_zone([&](unsigned long long k, float) { lo = k < lo ? k : lo; hi = k > hi ? k : hi; nz_loc++; });
+    for (int j = tid; j < nz; j += W_NT) { const unsigned long long k = zk[j]; lo = k < lo ? k : lo; hi = k > hi ? k : hi; }
     lo = bu::min_u64<W_NW>(lo, sc, tid);
     hi = bu::max_u64<W_NW>(hi, sc, tid);
     double gbase = Ktot;                                     // Ktot + mass of keys below lo; never crossed
-    int inrange = big ? bu::sum_i<W_NW>(nz_loc, sc, tid) : nz;
+    int inrange = nz;
     bool all_in = false;
-    for (int iter = 0; iter < 10 && inrange > 32 && !bad && !all_in; iter++) {
+    for (int iter = 0; iter < 8 && inrange > 32 && !bad && !all_in; iter++) {
       const unsigned long long spn = hi - lo;
       int shf = 0;
       while (shf < 63 && (spn >> shf) >= static_cast<unsigned long long>(W_NSUB)) shf++;
       __syncthreads();
       sm[tid] = 0.0; scn[tid] = 0;                           // W_NT == W_NSUB
       __syncthreads();
-      each_zone([&](unsigned long long k, float d) {
+      for (int j = tid; j < nz; j += W_NT) {
+        const unsigned long long k = zk[j];
         if (k >= lo && k <= hi) {
           const int sb = static_cast<int>((k - lo) >> shf);
-          atomicAdd(&sm[sb], exp_safe(d, s_tab));
+          atomicAdd(&sm[sb], exp_safe(zone_key_d(k), s_tab));
           atomicAdd(&scn[sb], 1);
         }
-      });
+      }
       __syncthreads();
       const double mine = sm[tid];
       double totm;
@@ -641,9 +776,10 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
       __syncthreads();
       if (tid == 0) sh.cnt = 0;
       __syncthreads();
-      each_zone([&](unsigned long long k, float) {
+      for (int j = tid; j < nz; j += W_NT) {
+        const unsigned long long k = zk[j];
         if (k >= lo && k <= hi) { const int slot = atomicAdd(&sh.cnt, 1); if (slot < 32) few[slot] = k; }
-      });
+      }
       __syncthreads();
       const int nf = min(32, sh.cnt);
       if (warp == 0) {
@@ -688,7 +824,7 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
       if (mode == 1) {
         // a later key with the same d as c*: the cut separates equal probabilities
         int tie = 0;
-        each_zone([&](unsigned long long k, float) { tie |= (k > cut_key && (k >> 32) == (cut_key >> 32)) ? 1 : 0; });
+        for (int j = tid; j < nz; j += W_NT) { const unsigned long long k = zk[j]; tie |= (k > cut_key && (k >> 32) == (cut_key >> 32)) ? 1 : 0; }
         if (bu::max_i<W_NW>(tie, sc, tid)) flags |= FLAG_TIE_CUT;
       }
     }
@@ -698,13 +834,14 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     }
     // kept zone entries add their mass to the piece they sit in
     __syncthreads();
-    each_zone([&](unsigned long long k, float d) {
+    for (int j = tid; j < nz; j += W_NT) {
+      const unsigned long long k = zk[j];
       if (k < cut_key || (cut_incl && k == cut_key)) {
         const int v = rv.vec_of(zone_key_index(k, mode));
         const int w = v / span;
-        atomicAdd(&part[w * ppw + (v - w * span) / PV], exp_safe(d, s_tab));
+        atomicAdd(&part[w * ppw + (v - w * span) / PV], exp_safe(zone_key_d(k), s_tab));
       }
-    });
+    }
     __syncthreads();
   }
   // ---- kept mass and the piece that holds the drawn token: prefix over the pieces in row order
