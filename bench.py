@@ -345,7 +345,8 @@ def main():
 
 def dominant_kernel(w):
     """The kernel that does the streaming for this workload (see profiles/)."""
-    if w.B < 384:
+    row_bytes = w.V * w.logits.dtype.itemsize          # the library's dispatch rule (shim.cu: use_batch_mode)
+    if not (w.B >= 384 or (w.B >= 32 and w.B * row_bytes >= 24 << 20)):
         return "sample_cluster_kernel"
     if int(w.cfgs["top_k"][0]) > 0 or float(w.cfgs["temperature"][0]) == 0.0:
         return "narrow_rows_kernel"

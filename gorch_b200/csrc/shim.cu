@@ -28,7 +28,15 @@ constexpr int64_t kSliceCap = 109 * 1024 - gs::REGION_A - gs::REGION_B;
 
 // Batches of at least this many rows are sorted by kind and served by the narrow / wide
 // kernels; smaller ones use one cluster per row so that every SM still has work.
+// Batches go to the sorted-batch kernels (one CTA per row) from this many rows on; smaller ones to
+// the cluster kernel (several CTAs per row), whose latency is lower while the GPU is not full.
+// Measured crossovers on B200: 40 rows of 608 KB, ~120 rows of 200 KB.
 constexpr int64_t kBatchModeRows = 384;
+constexpr int64_t kBatchModeBytes = 24ll << 20;
+inline bool use_batch_mode(int64_t B, int64_t row_bytes) {
+  if (B >= kBatchModeRows) return true;
+  return B >= 32 && B * row_bytes >= kBatchModeBytes;
+}
 
 struct Buffer {
   int device;
@@ -46,6 +54,8 @@ struct Ctx {
   int sm_count = 148;
   cudaStream_t own_stream = nullptr;
   cudaStream_t stream = nullptr;
+  cudaStream_t side_stream = nullptr;     // the wide kernel of a mixed batch runs here, beside the narrow one
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   double* exp_table = nullptr;
   double* eb_table = nullptr;
   Scratch worklist;        // int32[1 + rows]: rows the cluster kernel leaves to the single-CTA kernel
@@ -175,7 +185,7 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
   a.tk_k = 0;
   if (c->timing) CUDA_TRY(cudaEventRecord(c->ev0, c->stream), errOut);
   int klaunch = 1;
-  const bool batch_mode = c->variant == 2 || (c->variant == 0 && B >= kBatchModeRows);
+  const bool batch_mode = c->variant == 2 || (c->variant == 0 && use_batch_mode(B, V * static_cast<int64_t>(elem_size(dtype))));
   if (batch_mode) {
     // classify -> narrow (greedy / top-k) -> wide (top-k off) -> single-CTA (whatever is left)
     const size_t ints = 16 + 3 * static_cast<size_t>(B) + 1;
@@ -198,14 +208,25 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
     const unsigned gsgl = static_cast<unsigned>(B < 2 * c->sm_count ? B : 2 * c->sm_count);
     gs::KernelArgs aw = a;
     aw.worklist = ba.list_single;
+    // The narrow and the wide kernel work on disjoint rows: the wide one runs on a side stream
+    // (fork after the classification, join before the hand-over kernel), so that a mixed batch
+    // does not pay for them one after the other.
+    if (!force_greedy) {
+      CUDA_TRY(cudaEventRecord(c->ev_fork, c->stream), errOut);
+      CUDA_TRY(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0), errOut);
+    }
     if (dtype == GORCH_CUDA_F32) {
+      if (!force_greedy) gs::wide_rows_kernel<float><<<gw, gs::W_NT, gs::W_DYN_BYTES, c->side_stream>>>(ba);
       gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-      if (!force_greedy) gs::wide_rows_kernel<float><<<gw, gs::W_NT, gs::W_DYN_BYTES, c->stream>>>(ba);
-      if (!force_greedy) gs::sample_rows_kernel<float><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
     } else {
+      if (!force_greedy) gs::wide_rows_kernel<uint16_t><<<gw, gs::W_NT, gs::W_DYN_BYTES, c->side_stream>>>(ba);
       gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-      if (!force_greedy) gs::wide_rows_kernel<uint16_t><<<gw, gs::W_NT, gs::W_DYN_BYTES, c->stream>>>(ba);
-      if (!force_greedy) gs::sample_rows_kernel<uint16_t><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
+    }
+    if (!force_greedy) {
+      CUDA_TRY(cudaEventRecord(c->ev_join, c->side_stream), errOut);
+      CUDA_TRY(cudaStreamWaitEvent(c->stream, c->ev_join, 0), errOut);
+      if (dtype == GORCH_CUDA_F32) gs::sample_rows_kernel<float><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
+      else gs::sample_rows_kernel<uint16_t><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
     }
     CUDA_TRY(cudaGetLastError(), errOut);
     klaunch = force_greedy ? 2 : 4;
@@ -390,6 +411,9 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   c->sm_count = prop.multiProcessorCount;
   if ((e = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking)) != cudaSuccess) return fail("cudaStreamCreate", e);
   c->stream = c->own_stream;
+  if ((e = cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking)) != cudaSuccess) return fail("cudaStreamCreate", e);
+  if ((e = cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming)) != cudaSuccess) return fail("cudaEventCreate", e);
+  if ((e = cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming)) != cudaSuccess) return fail("cudaEventCreate", e);
   if ((e = cudaEventCreate(&c->ev0)) != cudaSuccess) return fail("cudaEventCreate", e);
   if ((e = cudaEventCreate(&c->ev1)) != cudaSuccess) return fail("cudaEventCreate", e);
   double tab[256];
@@ -427,6 +451,9 @@ void gorch_cuda_release(GorchCudaCtxRef ctx) {
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
   if (c->own_stream) cudaStreamDestroy(c->own_stream);
+  if (c->side_stream) cudaStreamDestroy(c->side_stream);
+  if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+  if (c->ev_join) cudaEventDestroy(c->ev_join);
   delete c;
 }
 
