@@ -609,52 +609,51 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     }
     __syncthreads();
     constexpr int PER = W_NB / W_NT;                         // buckets per thread
-    double lo_inc[PER], hi_inc[PER];
-    int cb[PER];
+    // bucket b holds q (or d) in [-(b+.5) width, -(b-.5) width], the last one everything below.
+    // Its members' masses lie between edge(b+1) and edge(b), edge(k) = exp(-(k-.5) width): one
+    // exponential per thread, the next edges by the common ratio (rounding far inside `slack`).
+    // The walk over the thread's buckets is done twice (sums, then the tests against the scanned
+    // sums) rather than kept in registers.
+    const double ratio = exp_safe(-width, s_tab);
+    const double edge0 = exp_safe(-(tid * PER - 0.5f) * width, s_tab);
     double slo = 0.0, shi = 0.0;
     {
-      // bucket b holds q (or d) in [-(b+.5) width, -(b-.5) width], the last one everything below.
-      // Its members' masses lie between edge(b+1) and edge(b), edge(k) = exp(-(k-.5) width): one
-      // exponential per thread, the next edges by the common ratio (rounding far inside `slack`).
-      const double ratio = exp_safe(-width, s_tab);
-      double edge = exp_safe(-(tid * PER - 0.5f) * width, s_tab);
-#pragma unroll
+      double edge = edge0;
+#pragma unroll 4
       for (int j = 0; j < PER; j++) {
         const int b = tid * PER + j;
-        cb[j] = static_cast<int>(hist[b]);
-        const double c = static_cast<double>(cb[j]);
+        const double c = static_cast<double>(hist[b]);
         const double ehi = fmin(edge, 1.0) * (1.0 + slack);
         edge *= ratio;
         const double elo = (b == W_NB - 1) ? 0.0 : edge * (1.0 - slack);
         slo += c * elo; shi += c * ehi;
-        lo_inc[j] = slo; hi_inc[j] = shi;
       }
     }
     double ex_lo, ex_hi, tot_lo, tot_hi;
     bu::scan_excl_d2<W_NW>(slo, shi, ex_lo, ex_hi, tot_lo, tot_hi, sc, tid);
     int b1 = W_NB - 1, b2 = W_NB - 1;
     const double p_lo = plim * (1.0 - 1e-9), p_hi = plim * (1.0 + 1e-9);
-#pragma unroll
-    for (int j = 0; j < PER; j++) {
-      const int b = tid * PER + j;
-      const double a_lo = ex_lo + lo_inc[j], a_hi = ex_hi + hi_inc[j];
-      // largest / smallest possible mass fraction through bucket b against the limit, as products
-      const double den_hi = a_hi + (tot_lo - a_lo), den_lo = a_lo + (tot_hi - a_hi);
-      bool c1, c2;
-      if (mode == 0) { c1 = a_hi > p_lo * den_hi; c2 = a_lo > p_hi * den_lo; }
-      else           { c1 = a_hi >= p_lo * den_hi; c2 = a_lo >= p_hi * den_lo; }
-      if (c1 && a_hi > 0.0) b1 = min(b1, b);
-      if (c2 && a_lo > 0.0) b2 = min(b2, b);
+    {
+      double edge = edge0, a_lo = ex_lo, a_hi = ex_hi;
+#pragma unroll 4
+      for (int j = 0; j < PER; j++) {
+        const int b = tid * PER + j;
+        const double c = static_cast<double>(hist[b]);
+        const double ehi = fmin(edge, 1.0) * (1.0 + slack);
+        edge *= ratio;
+        const double elo = (b == W_NB - 1) ? 0.0 : edge * (1.0 - slack);
+        a_lo += c * elo; a_hi += c * ehi;
+        // largest / smallest possible mass fraction through bucket b against the limit, as products
+        const double den_hi = a_hi + (tot_lo - a_lo), den_lo = a_lo + (tot_hi - a_hi);
+        bool c1, c2;
+        if (mode == 0) { c1 = a_hi > p_lo * den_hi; c2 = a_lo > p_hi * den_lo; }
+        else           { c1 = a_hi >= p_lo * den_hi; c2 = a_lo >= p_hi * den_lo; }
+        if (c1 && a_hi > 0.0) b1 = min(b1, b);
+        if (c2 && a_lo > 0.0) b2 = min(b2, b);
+      }
     }
     bu::min_i2<W_NW>(b1, b2, sc, tid);
     if (b2 < b1) b2 = b1;
-    int nz_part = 0;
-#pragma unroll
-    for (int j = 0; j < PER; j++) {
-      const int b = tid * PER + j;
-      if (b >= b1 && b <= b2) nz_part += cb[j];
-    }
-    const int nzone = bu::sum_i<W_NW>(nz_part, sc, tid);
     const float qA = bucket_floor_w(b1 - 1, scale, dclamp);  // certainly kept: q >= qA
     const float qB = bucket_floor_w(b2, scale, dclamp);      // certainly dropped: q < qB
     if (!anchored) {
