@@ -196,12 +196,12 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
     ba.k = a;
     ba.eb_table = c->eb_table;
     ba.hdr = base;
-    ba.list_narrow = base + 16;
-    ba.list_wide = base + 16 + B;
-    ba.list_single = base + 16 + 2 * B;
+    // the hand-over list's count is the header's last word, its rows follow: one memset clears all
+    ba.list_single = base + 15;
+    ba.list_narrow = base + 16 + B;
+    ba.list_wide = base + 16 + 2 * B;
     ba.B = B;
     CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
-    CUDA_TRY(cudaMemsetAsync(ba.list_single, 0, sizeof(int32_t), c->stream), errOut);
     gs::classify_rows_kernel<<<static_cast<unsigned>((B + 255) / 256), 256, 0, c->stream>>>(ba);
     const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
     const unsigned gw = static_cast<unsigned>(B < gs::W_CTAS * c->sm_count ? B : gs::W_CTAS * c->sm_count);
