@@ -1,9 +1,12 @@
 // Large-batch kernels: rows are first sorted by what they need, then two
 // persistent kernels pull rows from work lists.
 //
-//   classify_rows_kernel   one thread per row: greedy / top-k rows go to the
-//                          "narrow" list, top-k-off rows to the "wide" list,
-//                          top-k above 256 to the single-CTA kernel's list.
+//   row_kind               what a row needs, from its config alone: greedy and
+//                          top-k <= 256 rows are "narrow", top-k-off rows "wide",
+//                          top-k above 256 goes to the single-CTA kernel. Each
+//                          persistent kernel walks ALL rows with its own atomic
+//                          cursor and takes the rows of its kind, so no separate
+//                          classification launch and no per-kind lists exist.
 //   narrow_rows_kernel     256 threads, four CTAs per SM. One streaming pass per
 //                          row: the first 4096 logits give a threshold (k-th
 //                          largest of the 256 per-thread maxima, a lower bound
@@ -54,38 +57,19 @@ static_assert(sizeof(VsRecord) == 16 + 8 * VS_CAND, "record layout is part of th
 struct BatchArgs {
   KernelArgs k;
   const double* eb_table;   // 1024 doubles: exp(-b/32)
-  int32_t* hdr;             // [0] narrow count, [1] wide count, [2] narrow cursor, [3] wide cursor
-  int32_t* list_narrow;     // [B]
-  int32_t* list_wide;       // [B]
+  int32_t* hdr;             // [2] narrow kernel's row cursor, [3] wide kernel's row cursor
   int32_t* list_single;     // [0] = count, [1..] rows for the single-CTA kernel
   int64_t B;
 };
 
-// every row on the narrow list (vocab-sharded local pass)
-__global__ void iota_list_kernel(BatchArgs BA) {
-  const int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (b < BA.B) BA.list_narrow[b] = static_cast<int32_t>(b);
-  if (b == 0) BA.hdr[0] = static_cast<int32_t>(BA.B);
-}
-
-__global__ void classify_rows_kernel(BatchArgs BA) {
-  const int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (b >= BA.B) return;
-  const KernelArgs& A = BA.k;
-  int kind = 0;   // 0 narrow, 1 wide, 2 single-CTA
-  if (!A.force_greedy) {
-    const RowCfg c = A.cfgs[b];
-    const float T = c.temperature;
-    if (T == 0.0f || !(T > 0.0f) || !(T < INFINITY)) {
-      kind = 0;   // greedy, or a bad temperature (reported by the narrow kernel)
-    } else {
-      const int topk = (c.top_k > 0 && c.top_k < A.V) ? c.top_k : 0;
-      kind = (topk == 0) ? 1 : (topk <= KFAST ? 0 : 2);
-    }
-  }
-  if (kind == 0) BA.list_narrow[atomicAdd(&BA.hdr[0], 1)] = static_cast<int32_t>(b);
-  else if (kind == 1) BA.list_wide[atomicAdd(&BA.hdr[1], 1)] = static_cast<int32_t>(b);
-  else BA.list_single[1 + atomicAdd(&BA.list_single[0], 1)] = static_cast<int32_t>(b);
+// 0: narrow kernel, 1: wide kernel, 2: single-CTA kernel
+__device__ __forceinline__ int row_kind(const KernelArgs& A, int64_t b) {
+  if (A.force_greedy || A.vs_records || A.tk_k > 0) return 0;
+  const RowCfg c = A.cfgs[b];
+  const float T = c.temperature;
+  if (T == 0.0f || !(T > 0.0f) || !(T < INFINITY)) return 0;   // greedy, or a bad temperature (reported by the narrow kernel)
+  const int topk = (c.top_k > 0 && c.top_k < A.V) ? c.top_k : 0;
+  return (topk == 0) ? 1 : (topk <= KFAST ? 0 : 2);
 }
 
 __device__ __forceinline__ void hand_to_single(const BatchArgs& BA, int64_t row_id) {
@@ -599,12 +583,19 @@ __global__ void __launch_bounds__(N_NT, 4) narrow_rows_kernel(BatchArgs BA) {
   __shared__ float s_thr;
   __shared__ int s_flag;
   __shared__ int s_row;
-  const int n = BA.hdr[0];
   for (;;) {
     __syncthreads();
     if (threadIdx.x == 0) {
-      const int w = atomicAdd(&BA.hdr[2], 1);
-      s_row = (w < n) ? BA.list_narrow[w] : -1;
+      // next row of this kernel's kind; rows for the single-CTA kernel are handed over here
+      int w;
+      for (;;) {
+        w = atomicAdd(&BA.hdr[2], 1);
+        if (w >= BA.B) { w = -1; break; }
+        const int kind = row_kind(BA.k, w);
+        if (kind == 0) break;
+        if (kind == 2) hand_to_single(BA, w);
+      }
+      s_row = w;
     }
     __syncthreads();
     const int row = s_row;

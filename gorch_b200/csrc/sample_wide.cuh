@@ -960,12 +960,16 @@ __global__ void __launch_bounds__(W_NT, W_CTAS) wide_rows_kernel(BatchArgs BA) {
   unsigned long long pol_keep, pol_drop;
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_keep));
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol_drop));
-  const int n = BA.hdr[1];
   for (;;) {
     __syncthreads();
     if (threadIdx.x == 0) {
-      const int w = atomicAdd(&BA.hdr[3], 1);
-      sh.row = (w < n) ? BA.list_wide[w] : -1;
+      int w;                                                 // next row of this kernel's kind
+      for (;;) {
+        w = atomicAdd(&BA.hdr[3], 1);
+        if (w >= BA.B) { w = -1; break; }
+        if (row_kind(BA.k, w) == 1) break;
+      }
+      sh.row = w;
     }
     __syncthreads();
     const int row = sh.row;

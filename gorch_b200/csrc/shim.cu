@@ -62,17 +62,17 @@ struct Ctx {
   Scratch st_logits, st_cfgs, st_uniforms, st_ids, st_flags;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int timing = 0;
-  int variant = 0;        // 0: by batch size, 1: single-CTA kernel, 2: classify + narrow/wide kernels, 3: cluster kernel
+  int variant = 0;        // 0: by batch size, 1: single-CTA kernel, 2: narrow/wide kernels, 3: cluster kernel
   int force_cluster = 0;  // 0: choose from the shape
   GorchCudaCounters counters{};
 };
 
 // Work lists for gorch_cuda_sample_dev_static: fixed storage inside the loaded module, so the
-// entry point never allocates. Every GPU that loads the library holds one copy (about 48 KB)
+// entry point never allocates. Every GPU that loads the library holds one copy (about 16 KB)
 // until the process exits. In host code this name is only a handle for cudaGetSymbolAddress;
 // the device address is looked up once per device (static_lists_ptr) and passed to the kernels.
 constexpr int64_t kStaticMaxRows = 4096;
-static __device__ __align__(256) int32_t g_static_worklists[16 + 3 * kStaticMaxRows + 1];
+static __device__ __align__(256) int32_t g_static_worklists[16 + kStaticMaxRows + 1];
 constexpr int kMaxDevices = 64;
 int32_t* g_static_ptr[kMaxDevices] = {};
 
@@ -187,8 +187,8 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
   int klaunch = 1;
   const bool batch_mode = c->variant == 2 || (c->variant == 0 && use_batch_mode(B, V * static_cast<int64_t>(elem_size(dtype))));
   if (batch_mode) {
-    // classify -> narrow (greedy / top-k) -> wide (top-k off) -> single-CTA (whatever is left)
-    const size_t ints = 16 + 3 * static_cast<size_t>(B) + 1;
+    // narrow (greedy / top-k) beside wide (top-k off), then single-CTA (whatever was handed over)
+    const size_t ints = 16 + static_cast<size_t>(B) + 1;
     int rc = ensure(c->worklist, ints * sizeof(int32_t), errOut);
     if (rc) return rc;
     int32_t* base = static_cast<int32_t*>(c->worklist.ptr);
@@ -198,11 +198,8 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
     ba.hdr = base;
     // the hand-over list's count is the header's last word, its rows follow: one memset clears all
     ba.list_single = base + 15;
-    ba.list_narrow = base + 16 + B;
-    ba.list_wide = base + 16 + 2 * B;
     ba.B = B;
     CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
-    gs::classify_rows_kernel<<<static_cast<unsigned>((B + 255) / 256), 256, 0, c->stream>>>(ba);
     const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
     const unsigned gw = static_cast<unsigned>(B < gs::W_CTAS * c->sm_count ? B : gs::W_CTAS * c->sm_count);
     const unsigned gsgl = static_cast<unsigned>(B < 2 * c->sm_count ? B : 2 * c->sm_count);
@@ -229,7 +226,7 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
       else gs::sample_rows_kernel<uint16_t><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
     }
     CUDA_TRY(cudaGetLastError(), errOut);
-    klaunch = force_greedy ? 2 : 4;
+    klaunch = force_greedy ? 1 : 3;
   } else if (c->variant == 1) {
     dim3 grid(static_cast<unsigned>(B)), block(gs::NT);
     if (dtype == GORCH_CUDA_F32) {
@@ -603,8 +600,8 @@ int gorch_cuda_vocab_local_dev(GorchCudaCtxRef ctx, const void* logits, int dtyp
     return GORCH_CUDA_ERR_BAD_ARG;
   }
   CUDA_TRY(cudaSetDevice(c->device), errOut);
-  // every row goes through the narrow kernel: its work list is simply 0..B-1
-  const size_t ints = 16 + 3 * static_cast<size_t>(B) + 1;
+  // every row goes through the narrow kernel (row_kind says so when vs_records is set)
+  const size_t ints = 16 + static_cast<size_t>(B) + 1;
   rc = ensure(c->worklist, ints * sizeof(int32_t), errOut);
   if (rc) return rc;
   int32_t* base = static_cast<int32_t*>(c->worklist.ptr);
@@ -616,15 +613,14 @@ int gorch_cuda_vocab_local_dev(GorchCudaCtxRef ctx, const void* logits, int dtyp
   ba.k.vs_records = records; ba.k.vs_col_offset = static_cast<int32_t>(col_offset);
   ba.k.tk_values = nullptr; ba.k.tk_indices = nullptr; ba.k.tk_k = 0;
   ba.eb_table = c->eb_table;
-  ba.hdr = base; ba.list_narrow = base + 16; ba.list_wide = base + 16 + B; ba.list_single = base + 16 + 2 * B;
+  ba.hdr = base; ba.list_single = base + 15;
   ba.B = B;
   CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
-  gs::iota_list_kernel<<<static_cast<unsigned>((B + 255) / 256), 256, 0, c->stream>>>(ba);
   const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
   if (dtype == GORCH_CUDA_F32) gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
   else gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
   CUDA_TRY(cudaGetLastError(), errOut);
-  c->counters.kernel_launches += 2;
+  c->counters.kernel_launches += 1;
   return GORCH_CUDA_OK;
 }
 
@@ -678,7 +674,7 @@ int gorch_cuda_topk_dev(GorchCudaCtxRef ctx, const void* x, int dtype, int64_t B
   if (B == 0) return GORCH_CUDA_OK;
   if (!x || !out_values || !out_indices) { set_err(errOut, "gorch_cuda: null pointer argument"); return GORCH_CUDA_ERR_BAD_ARG; }
   CUDA_TRY(cudaSetDevice(c->device), errOut);
-  const size_t ints = 16 + 3 * static_cast<size_t>(B) + 1;
+  const size_t ints = 16 + static_cast<size_t>(B) + 1;
   rc = ensure(c->worklist, ints * sizeof(int32_t), errOut);
   if (rc) return rc;
   int32_t* base = static_cast<int32_t*>(c->worklist.ptr);
@@ -690,15 +686,14 @@ int gorch_cuda_topk_dev(GorchCudaCtxRef ctx, const void* x, int dtype, int64_t B
   ba.k.vs_records = nullptr; ba.k.vs_col_offset = 0;
   ba.k.tk_values = out_values; ba.k.tk_indices = out_indices; ba.k.tk_k = static_cast<int32_t>(k);
   ba.eb_table = c->eb_table;
-  ba.hdr = base; ba.list_narrow = base + 16; ba.list_wide = base + 16 + B; ba.list_single = base + 16 + 2 * B;
+  ba.hdr = base; ba.list_single = base + 15;
   ba.B = B;
   CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
-  gs::iota_list_kernel<<<static_cast<unsigned>((B + 255) / 256), 256, 0, c->stream>>>(ba);
   const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
   if (dtype == GORCH_CUDA_F32) gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
   else gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
   CUDA_TRY(cudaGetLastError(), errOut);
-  c->counters.kernel_launches += 2;
+  c->counters.kernel_launches += 1;
   return GORCH_CUDA_OK;
 }
 
@@ -812,14 +807,11 @@ int gorch_cuda_sample_dev_static(GorchCudaCtxRef ctx, const void* logits, int dt
   ba.k.worklist = nullptr;
   ba.eb_table = c->eb_table;
   ba.hdr = base;
-  ba.list_narrow = base + 16;
-  ba.list_wide = base + 16 + B;
-  ba.list_single = base + 16 + 2 * B;
+  ba.list_single = base + 15;
   ba.B = B;
-  // the lists keep the previous call's contents: the counters and cursors must start at zero
+  // the array keeps the previous call's contents: the cursors and the hand-over count (the
+  // header's 16 words) must start at zero
   CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
-  CUDA_TRY(cudaMemsetAsync(ba.list_single, 0, sizeof(int32_t), c->stream), errOut);
-  gs::classify_rows_kernel<<<static_cast<unsigned>((B + 255) / 256), 256, 0, c->stream>>>(ba);
   const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
   const unsigned gw = static_cast<unsigned>(B < gs::W_CTAS * c->sm_count ? B : gs::W_CTAS * c->sm_count);
   const unsigned gsgl = static_cast<unsigned>(B < 2 * c->sm_count ? B : 2 * c->sm_count);
@@ -835,7 +827,7 @@ int gorch_cuda_sample_dev_static(GorchCudaCtxRef ctx, const void* logits, int dt
     gs::sample_rows_kernel<uint16_t><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
   }
   CUDA_TRY(cudaGetLastError(), errOut);
-  c->counters.kernel_launches += 4;
+  c->counters.kernel_launches += 3;
   c->counters.sample_launches++;
   c->counters.rows += static_cast<uint64_t>(B);
   return GORCH_CUDA_OK;

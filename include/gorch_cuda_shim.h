@@ -158,7 +158,7 @@ int gorch_cuda_sample_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, in
  * capture, where cudaMalloc is not permitted, or a serving process whose memory budget is
  * fixed up front and that treats any later cudaMalloc (which also synchronises the device)
  * as a fault. The row work lists that the other entry point keeps in a grow-only
- * cudaMalloc'd buffer live here in a fixed array inside the library image: about 48 KB of
+ * cudaMalloc'd buffer live here in a fixed array inside the library image: about 16 KB of
  * device memory on every GPU that loads the library, held until the process exits.
  *   - at most 4096 rows per call; more is refused with GORCH_CUDA_ERR_LIMIT;
  *   - the first call on a device looks up the array's device address
