@@ -1,12 +1,18 @@
 // wide_rows_kernel: rows whose softmax runs over the whole vocabulary (top-k off).
 //
-// 256 threads per CTA, four persistent CTAs per SM, one row at a time per CTA: with four rows
-// per SM the load latency and the serial tail of one row hide behind the arithmetic of the others. Warp w owns one contiguous span of the row (1/8 of it,
+// One row at a time per persistent CTA. Warp w owns one contiguous span of the row (1/W_NW of it,
 // rounded up to whole steps); in a step every lane handles eight logits (two 16-byte vectors
 // of f32, one of bf16), loaded straight into registers one or two steps ahead of their use
 // and asked from L2 two steps before that. Nothing is shared between threads inside a pass,
 // so a pass contains no barrier; the loads carry L2 cache hints (keep in pass 1, evict first
 // in pass 3), and the later passes find in L2 what has stayed there.
+//
+// This header has no include guard: it is included once per instance, with GS_W_NS naming the
+// instance's namespace inside gs and GS_W_NT its threads per CTA.
+//   256:  four CTAs per SM. With four rows per SM the load latency and the serial tail of one
+//         row hide behind the arithmetic of the others: the instance for batches that fill the GPU.
+//   1024: one CTA per SM. A row finishes about a quarter sooner: the instance for batches of at
+//         most one row per SM.
 //
 //   sample                     the first step of every warp: an upper estimate (anchor) of the
 //                              row's maximum and its range
@@ -21,25 +27,23 @@
 //                              rescan of the one piece that holds the drawn token
 //
 // Row semantics: model/generate.go:147-240 (mode A), model/qwen/generate.go:92-153 (mode B).
-#pragma once
-
 #include "sample_batch.cuh"   // includes row_stream.cuh
 
-namespace gs {
-
-#ifndef GS_W_NT
+#ifndef GS_W_NS
+#define GS_W_NS w256
 #define GS_W_NT 256
 #endif
+
+namespace gs {
+namespace GS_W_NS {
+
 constexpr int W_NT = GS_W_NT;           // threads per CTA
 constexpr int W_CTAS = 1024 / W_NT;     // CTAs per SM
 constexpr int W_NSUB = W_NT;            // sub-buckets of one weighted-selection round
 constexpr int W_NW = W_NT / 32;
 constexpr int W_NB = 4096;              // histogram buckets
 constexpr int W_ZCAP = 2048;            // exact zone list capacity
-#ifndef GS_W_D1
-#define GS_W_D1 2
-#endif
-constexpr int W_D1 = GS_W_D1;           // steps of register prefetch in pass 1
+constexpr int W_D1 = 2;                 // steps of register prefetch in pass 1
 constexpr int W_G = 4;                  // steps per piece (power of two)
 constexpr int W_MAX_STEPS = (W_NT >= 512) ? 64 : 128;         // steps per warp and pass; longer rows go to the single-CTA kernel
 constexpr int W_MAX_PPW = W_MAX_STEPS / W_G;
@@ -515,7 +519,7 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     }
   };
 
-  // the warp's span: 1/32 of the row, rounded up to whole steps
+  // the warp's span: 1/W_NW of the row, rounded up to whole steps
   const int span = (((rv.nvec + W_NW - 1) / W_NW + SV - 1) / SV) * SV;
   const int steps_max = span / SV;
   if (steps_max > W_MAX_STEPS) {
@@ -978,4 +982,8 @@ __global__ void __launch_bounds__(W_NT, W_CTAS) wide_rows_kernel(BatchArgs BA) {
   }
 }
 
+}  // namespace GS_W_NS
 }  // namespace gs
+
+#undef GS_W_NS
+#undef GS_W_NT

@@ -16,7 +16,12 @@
 #include <new>
 
 #include "../../include/gorch_cuda_shim.h"
-#include "sample_wide.cuh"
+#define GS_W_NS w256
+#define GS_W_NT 256
+#include "sample_wide.cuh"      // gs::w256: 256 threads, four CTAs per SM (throughput)
+#define GS_W_NS w1024
+#define GS_W_NT 1024
+#include "sample_wide.cuh"      // gs::w1024: 1024 threads, one CTA per SM (latency)
 #include "sample_vocab.cuh"
 #include "index_ops.cuh"
 
@@ -62,7 +67,8 @@ struct Ctx {
   Scratch st_logits, st_cfgs, st_uniforms, st_ids, st_flags;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int timing = 0;
-  int variant = 0;        // 0: by batch size, 1: single-CTA kernel, 2: narrow/wide kernels, 3: cluster kernel
+  int variant = 0;        // 0: by batch size, 1: single-CTA kernel, 2: narrow/wide kernels, 3: cluster kernel,
+                          // 4 / 5: as 2 with the wide kernel's 256- / 1024-thread instance forced
   int force_cluster = 0;  // 0: choose from the shape
   GorchCudaCounters counters{};
 };
@@ -185,7 +191,7 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
   a.tk_k = 0;
   if (c->timing) CUDA_TRY(cudaEventRecord(c->ev0, c->stream), errOut);
   int klaunch = 1;
-  const bool batch_mode = c->variant == 2 || (c->variant == 0 && use_batch_mode(B, V * static_cast<int64_t>(elem_size(dtype))));
+  const bool batch_mode = c->variant == 2 || c->variant >= 4 || (c->variant == 0 && use_batch_mode(B, V * static_cast<int64_t>(elem_size(dtype))));
   if (batch_mode) {
     // narrow (greedy / top-k) beside wide (top-k off), then single-CTA (whatever was handed over)
     const size_t ints = 16 + static_cast<size_t>(B) + 1;
@@ -201,7 +207,12 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
     ba.B = B;
     CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
     const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
-    const unsigned gw = static_cast<unsigned>(B < gs::W_CTAS * c->sm_count ? B : gs::W_CTAS * c->sm_count);
+    // at most one row per SM: a 1024-thread CTA finishes its row sooner than a 256-thread one, and no SM
+    // would have held a second row anyway. Beyond that the 256-thread instance wins (measured), also
+    // because a 1024-thread CTA takes the whole register file and keeps the narrow kernel off its SM
+    const bool wide_big_ctas = c->variant == 5 || (c->variant != 4 && B <= c->sm_count);
+    const int wctas = wide_big_ctas ? gs::w1024::W_CTAS : gs::w256::W_CTAS;
+    const unsigned gw = static_cast<unsigned>(B < wctas * c->sm_count ? B : wctas * c->sm_count);
     const unsigned gsgl = static_cast<unsigned>(B < 2 * c->sm_count ? B : 2 * c->sm_count);
     gs::KernelArgs aw = a;
     aw.worklist = ba.list_single;
@@ -213,10 +224,12 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
       CUDA_TRY(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0), errOut);
     }
     if (dtype == GORCH_CUDA_F32) {
-      if (!force_greedy) gs::wide_rows_kernel<float><<<gw, gs::W_NT, gs::W_DYN_BYTES, c->side_stream>>>(ba);
+      if (!force_greedy && wide_big_ctas) gs::w1024::wide_rows_kernel<float><<<gw, gs::w1024::W_NT, gs::w1024::W_DYN_BYTES, c->side_stream>>>(ba);
+      else if (!force_greedy) gs::w256::wide_rows_kernel<float><<<gw, gs::w256::W_NT, gs::w256::W_DYN_BYTES, c->side_stream>>>(ba);
       gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
     } else {
-      if (!force_greedy) gs::wide_rows_kernel<uint16_t><<<gw, gs::W_NT, gs::W_DYN_BYTES, c->side_stream>>>(ba);
+      if (!force_greedy && wide_big_ctas) gs::w1024::wide_rows_kernel<uint16_t><<<gw, gs::w1024::W_NT, gs::w1024::W_DYN_BYTES, c->side_stream>>>(ba);
+      else if (!force_greedy) gs::w256::wide_rows_kernel<uint16_t><<<gw, gs::w256::W_NT, gs::w256::W_DYN_BYTES, c->side_stream>>>(ba);
       gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
     }
     if (!force_greedy) {
@@ -431,8 +444,10 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   if ((e = cudaFuncSetAttribute(gs::narrow_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::multinomial_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::MN_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::vocab_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::VM_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
-  if ((e = cudaFuncSetAttribute(gs::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
-  if ((e = cudaFuncSetAttribute(gs::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::w256::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w256::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::w1024::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w1024::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::w256::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w256::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::w1024::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w1024::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   return c;
 }
 
@@ -482,9 +497,9 @@ int gorch_cuda_set_timing(GorchCudaCtxRef ctx, int on) {
 int gorch_cuda_set_kernel_variant(GorchCudaCtxRef ctx, int variant, int cluster_size, char** errOut) {
   Ctx* c = static_cast<Ctx*>(ctx);
   if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
-  if ((variant < 0 || variant > 3) ||
+  if ((variant < 0 || variant > 5) ||
       !(cluster_size == 0 || cluster_size == 1 || cluster_size == 2 || cluster_size == 4 || cluster_size == 8)) {
-    set_err(errOut, "gorch_cuda: variant must be 0..3, cluster_size 0, 1, 2, 4 or 8");
+    set_err(errOut, "gorch_cuda: variant must be 0..5, cluster_size 0, 1, 2, 4 or 8");
     return GORCH_CUDA_ERR_BAD_ARG;
   }
   c->variant = variant;
@@ -815,17 +830,17 @@ int gorch_cuda_sample_dev_static(GorchCudaCtxRef ctx, const void* logits, int dt
   // header's 16 words) must start at zero
   CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
   const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
-  const unsigned gw = static_cast<unsigned>(B < gs::W_CTAS * c->sm_count ? B : gs::W_CTAS * c->sm_count);
+  const unsigned gw = static_cast<unsigned>(B < gs::w256::W_CTAS * c->sm_count ? B : gs::w256::W_CTAS * c->sm_count);
   const unsigned gsgl = static_cast<unsigned>(B < 2 * c->sm_count ? B : 2 * c->sm_count);
   gs::KernelArgs aw = ba.k;
   aw.worklist = ba.list_single;
   if (dtype == GORCH_CUDA_F32) {
     gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-    gs::wide_rows_kernel<float><<<gw, gs::W_NT, gs::W_DYN_BYTES, c->stream>>>(ba);
+    gs::w256::wide_rows_kernel<float><<<gw, gs::w256::W_NT, gs::w256::W_DYN_BYTES, c->stream>>>(ba);
     gs::sample_rows_kernel<float><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
   } else {
     gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-    gs::wide_rows_kernel<uint16_t><<<gw, gs::W_NT, gs::W_DYN_BYTES, c->stream>>>(ba);
+    gs::w256::wide_rows_kernel<uint16_t><<<gw, gs::w256::W_NT, gs::w256::W_DYN_BYTES, c->stream>>>(ba);
     gs::sample_rows_kernel<uint16_t><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
   }
   CUDA_TRY(cudaGetLastError(), errOut);

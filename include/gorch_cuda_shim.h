@@ -105,11 +105,13 @@ int gorch_cuda_set_stream(GorchCudaCtxRef ctx, void* stream, int external, char*
 int gorch_cuda_set_timing(GorchCudaCtxRef ctx, int on);
 int gorch_cuda_get_counters(GorchCudaCtxRef ctx, GorchCudaCounters* out);
 /* Which kernels serve the sampling calls. variant 0 (default): by batch size
- * (large batches: rows sorted by kind, then the narrow and wide kernels; small
- * ones: one thread-block cluster per row); 1: one CTA per row re-reading global
- * memory (an independent second implementation); 2: force the large-batch
- * kernels; 3: force the cluster kernel. cluster_size 0 picks the cluster size
- * from the shape; 1, 2, 4, 8 force it. */
+ * (large batches: the narrow and wide kernels, each taking the rows of its
+ * kind; small ones: one thread-block cluster per row); 1: one CTA per row
+ * re-reading global memory (an independent second implementation); 2: force the
+ * large-batch kernels; 3: force the cluster kernel; 4 / 5: as 2, with the wide
+ * kernel's 256-thread (four CTAs per SM) / 1024-thread (one CTA per SM)
+ * instance forced instead of chosen by batch size. cluster_size 0 picks the
+ * cluster size from the shape; 1, 2, 4, 8 force it. */
 int gorch_cuda_set_kernel_variant(GorchCudaCtxRef ctx, int variant, int cluster_size, char** errOut);
 
 /* ---- device buffers: replaces metal_create_shared_buffer /
