@@ -21,7 +21,21 @@ EXPORTS = [
     "gorch_cuda_argmax_host", "gorch_cuda_argmax_dev",
     "gorch_cuda_vocab_local_dev", "gorch_cuda_vocab_merge_dev",
     "gorch_cuda_topk_dev", "gorch_cuda_multinomial_dev",
+    "gorch_cuda_generate_control_dev", "gorch_cuda_generate_step_dev",
 ]
+
+
+GEN_MAX_STOPS = 16   # GORCH_GEN_MAX_STOPS
+
+
+class GenControl(C.Structure):
+    """GorchGenControl of include/gorch_cuda_shim.h."""
+    _fields_ = [
+        ("tokens", C.c_void_p), ("capacity", C.c_int64), ("lengths", C.c_void_p), ("n_new", C.c_void_p),
+        ("cache_len", C.c_void_p), ("done", C.c_void_p), ("next_input", C.c_void_p), ("window_start", C.c_void_p),
+        ("live_count", C.c_void_p), ("stop_tokens", C.c_int32 * GEN_MAX_STOPS), ("n_stop", C.c_int32),
+        ("max_new", C.c_int32), ("max_seq", C.c_int32), ("cached", C.c_int32),
+    ]
 
 
 class Counters(C.Structure):
@@ -72,6 +86,8 @@ def load() -> C.CDLL:
         "gorch_cuda_vocab_merge_dev": (i32, [p, p, i32, i64, i64, p, p, p, p, err]),
         "gorch_cuda_topk_dev": (i32, [p, p, i32, i64, i64, i64, i64, p, p, p, err]),
         "gorch_cuda_multinomial_dev": (i32, [p, p, i64, i64, i64, p, p, p, err]),
+        "gorch_cuda_generate_control_dev": (i32, [p, p, p, C.POINTER(GenControl), i64, err]),
+        "gorch_cuda_generate_step_dev": (i32, [p, p, i32, i64, i64, i64, p, p, p, p, C.POINTER(GenControl), err]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)

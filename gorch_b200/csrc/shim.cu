@@ -24,6 +24,7 @@
 #include "sample_wide.cuh"      // gs::w1024: 1024 threads, one CTA per SM (latency)
 #include "sample_vocab.cuh"
 #include "index_ops.cuh"
+#include "generate_control.cuh"
 
 namespace {
 
@@ -737,6 +738,57 @@ int gorch_cuda_multinomial_dev(GorchCudaCtxRef ctx, const float* probs, int64_t 
   CUDA_TRY(cudaGetLastError(), errOut);
   c->counters.kernel_launches += 1;
   return GORCH_CUDA_OK;
+}
+
+static int launch_generate_control(Ctx* c, const int32_t* ids, const uint32_t* flags,
+                                   const GorchGenControl* gc, int64_t B, char** errOut) {
+  static_assert(GORCH_GEN_MAX_STOPS == gs::GC_MAX_STOPS && GORCH_GEN_STOP == gs::GC_STOP &&
+                GORCH_GEN_MAX_NEW == gs::GC_MAX_NEW && GORCH_GEN_MAX_SEQ == gs::GC_MAX_SEQ &&
+                GORCH_GEN_ERROR == gs::GC_ERROR, "generate-control codes");
+  if (!gc) { set_err(errOut, "gorch_cuda: null generate-control record"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if (B < 0 || B > 0x7fffffffll) { set_err(errOut, "gorch_cuda: bad batch size %lld", (long long)B); return GORCH_CUDA_ERR_BAD_ARG; }
+  if (gc->n_stop < 0 || gc->n_stop > GORCH_GEN_MAX_STOPS) {
+    set_err(errOut, "gorch_cuda: n_stop %d outside 0..%d", gc->n_stop, GORCH_GEN_MAX_STOPS);
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  if (gc->capacity < 0 || gc->max_seq < 0) { set_err(errOut, "gorch_cuda: negative capacity or max_seq"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!ids || !gc->tokens || !gc->lengths || !gc->n_new || !gc->done || !gc->next_input || !gc->live_count ||
+      (gc->cached && !gc->cache_len)) {
+    set_err(errOut, "gorch_cuda: null pointer in the generate-control record");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  gs::GenControlArgs a;
+  a.ids = ids; a.flags = flags;
+  a.tokens = gc->tokens; a.capacity = gc->capacity; a.lengths = gc->lengths; a.n_new = gc->n_new;
+  a.cache_len = gc->cache_len; a.done = gc->done; a.next_input = gc->next_input;
+  a.window_start = gc->window_start; a.live_count = gc->live_count;
+  for (int i = 0; i < GORCH_GEN_MAX_STOPS; i++) a.stops[i] = (i < gc->n_stop && gc->stop_tokens[i] >= 0) ? gc->stop_tokens[i] : -1;
+  a.n_stop = gc->n_stop; a.max_new = gc->max_new; a.max_seq = gc->max_seq; a.cached = gc->cached ? 1 : 0;
+  a.bad_flags = GORCH_FLAG_INTERNAL | GORCH_FLAG_BAD_CFG | GORCH_FLAG_TIMEOUT;
+  a.B = static_cast<int>(B);
+  gs::generate_control_kernel<<<1, gs::GC_NT, 0, c->stream>>>(a);
+  CUDA_TRY(cudaGetLastError(), errOut);
+  c->counters.kernel_launches += 1;
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_generate_control_dev(GorchCudaCtxRef ctx, const int32_t* ids, const uint32_t* flags,
+                                    const GorchGenControl* gc, int64_t B, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  return launch_generate_control(c, ids, flags, gc, B, errOut);
+}
+
+int gorch_cuda_generate_step_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                                 int64_t V, int64_t row_stride, const GorchSampleCfg* cfgs,
+                                 const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
+                                 const GorchGenControl* gc, char** errOut) {
+  int rc = gorch_cuda_sample_dev(ctx, logits, dtype, B, V, row_stride, cfgs, uniforms, out_ids, out_flags,
+                                 nullptr, nullptr, errOut);
+  if (rc) return rc;
+  return launch_generate_control(static_cast<Ctx*>(ctx), out_ids, out_flags, gc, B, errOut);
 }
 
 int64_t gorch_cuda_sample_row(GorchCudaCtxRef ctx, const float* logits, int64_t n,

@@ -213,6 +213,58 @@ int gorch_cuda_multinomial_dev(GorchCudaCtxRef ctx, const float* probs, int64_t 
                                int64_t row_stride, const double* uniforms, int32_t* out_ids,
                                uint32_t* out_flags, char** errOut);
 
+/* The bookkeeping of the reference's generate loops for a batch of sequences, on the device: the
+ * token ids stay in device memory between decode steps and the host no longer has to read each
+ * step's id back to decide whether to go on (model/generate.go:60-88 uncached, :107-129 cached;
+ * model/qwen/generate.go:47-61). All pointers are device pointers owned by the caller.
+ *
+ * For every row with done[b] == GORCH_GEN_LIVE, one loop iteration in the reference's order:
+ * the iteration limit (n_new[b] >= max_new => GORCH_GEN_MAX_NEW); the stop test, the stop token
+ * NOT appended (=> GORCH_GEN_STOP; stop_tokens entries < 0 never match, which is StopToken = -1 of
+ * generate.go:82); the append to tokens[b, lengths[b]]; then, cached != 0: cache_len[b] >= max_seq
+ * => GORCH_GEN_MAX_SEQ (generate.go:121-123), else next_input[b] = id and cache_len[b]++;
+ * cached == 0: next_input[b] = id and window_start[b] (may be NULL) = start of the last max_seq
+ * tokens of the row (generate.go:62-65). A row whose max_new-th token was just appended becomes
+ * GORCH_GEN_MAX_NEW at once. An id < 0, a sampler flag in GORCH_FLAG_INTERNAL | GORCH_FLAG_BAD_CFG |
+ * GORCH_FLAG_TIMEOUT (flags may be NULL) or a full token buffer => GORCH_GEN_ERROR, nothing appended.
+ * live_count[0] = rows still live after the step.
+ *
+ * Before the first step the caller fills tokens/lengths with the prompts (cached loops of
+ * generate.go: truncated to their last max_seq tokens, :101-103), n_new = 0, done = 0 and
+ * cache_len = prompt length after the prefill. */
+#define GORCH_GEN_LIVE 0
+#define GORCH_GEN_STOP 1
+#define GORCH_GEN_MAX_NEW 2
+#define GORCH_GEN_MAX_SEQ 3
+#define GORCH_GEN_ERROR 4
+#define GORCH_GEN_MAX_STOPS 16
+typedef struct {
+  int32_t* tokens;       /* [B, capacity] */
+  int64_t capacity;      /* >= prompt length + max_new */
+  int32_t* lengths;      /* [B] */
+  int32_t* n_new;        /* [B] */
+  int32_t* cache_len;    /* [B]; read and written only when cached != 0 */
+  int32_t* done;         /* [B] GORCH_GEN_* */
+  int32_t* next_input;   /* [B] */
+  int32_t* window_start; /* [B] or NULL; written only when cached == 0 */
+  int32_t* live_count;   /* [1] */
+  int32_t stop_tokens[GORCH_GEN_MAX_STOPS];
+  int32_t n_stop;        /* 0..GORCH_GEN_MAX_STOPS */
+  int32_t max_new;       /* MaxNewTokens */
+  int32_t max_seq;       /* MaxSeq */
+  int32_t cached;        /* 0: GenerateWithConfig without KV cache; else the cached loops */
+} GorchGenControl;
+/* The control step alone, over ids (and flags, may be NULL) that a sampling call on the same
+ * context has written. One launch, asynchronous on the context's stream. */
+int gorch_cuda_generate_control_dev(GorchCudaCtxRef ctx, const int32_t* ids, const uint32_t* flags,
+                                    const GorchGenControl* gc, int64_t B, char** errOut);
+/* gorch_cuda_sample_dev followed by the control step in one call: out_ids / out_flags receive the
+ * sampled ids as usual (rows that are no longer live are sampled too and ignored). */
+int gorch_cuda_generate_step_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                                 int64_t V, int64_t row_stride, const GorchSampleCfg* cfgs,
+                                 const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
+                                 const GorchGenControl* gc, char** errOut);
+
 /* One row, the exact shape of the reference's calls: sample(logits,
  * temperature, topK, topP) (generate.go:147) with the uniform passed in, and
  * argmax when temperature == 0. Returns the token id, or -1 with *errOut set. */

@@ -360,6 +360,63 @@ void gorch_oracle_multinomial_f32(const float* probs, int64_t B, int64_t V,
   }
 }
 
+// The control flow of the reference's three generate loops, with the sampler's answers scripted:
+// script[i] is what argmax / sample returns in iteration i, so the loop's own rules (prompt
+// truncation, the stop test before the append, the MaxSeq test after it, the iteration limit)
+// are all that is exercised.
+//   loop 0: GenerateWithConfig, uncached (model/generate.go:57-88); one stop token, off when < 0
+//   loop 1: generateCached (model/generate.go:93-131)
+//   loop 2: qwen.Generate (model/qwen/generate.go:35-62); a list of stop tokens (isStop, :64-71)
+// out_tokens holds n_prompt + max_new entries; returns the result's length. reason: 1 the stop
+// token came, 2 the iteration limit, 3 the cache reached MaxSeq. sampler_calls: iterations that
+// asked the sampler (= uniforms drawn when temperature != 0). fed: for loops 1 and 2 the tokens
+// given to the incremental forward, in order (up to max_new entries); n_fed their count. For
+// loop 0, fed[i] is the start of the input window of iteration i (len(result) - MaxSeq, or 0).
+int64_t gorch_oracle_generate_scripted(int32_t loop, const int64_t* prompt, int64_t n_prompt,
+                                       const int64_t* script, int64_t max_new, int64_t max_seq,
+                                       const int64_t* stops, int64_t n_stops,
+                                       int64_t* out_tokens, int32_t* reason,
+                                       int64_t* sampler_calls, int64_t* fed, int64_t* n_fed) {
+  std::vector<int64_t> result(prompt, prompt + n_prompt);
+  int64_t calls = 0, nf = 0;
+  int32_t why = 2;
+  auto is_stop = [&](int64_t tok) {
+    if (loop == 2) {
+      for (int64_t i = 0; i < n_stops; i++) if (tok == stops[i]) return true;
+      return false;
+    }
+    return n_stops > 0 && stops[0] >= 0 && tok == stops[0];
+  };
+  if (loop == 0) {
+    for (int64_t i = 0; i < max_new; i++) {
+      int64_t start = 0;
+      if (static_cast<int64_t>(result.size()) > max_seq) start = static_cast<int64_t>(result.size()) - max_seq;
+      fed[nf++] = start;
+      const int64_t next = script[calls++];
+      if (is_stop(next)) { why = 1; break; }
+      result.push_back(next);
+    }
+  } else {
+    if (loop == 1 && static_cast<int64_t>(result.size()) > max_seq) {
+      result.erase(result.begin(), result.end() - max_seq);     // generate.go:101-103
+    }
+    int64_t cache_len = static_cast<int64_t>(result.size());    // prefill of the whole prompt
+    for (int64_t i = 0; i < max_new; i++) {
+      const int64_t next = script[calls++];
+      if (is_stop(next)) { why = 1; break; }
+      result.push_back(next);
+      if (cache_len >= max_seq) { why = 3; break; }
+      fed[nf++] = next;
+      cache_len++;
+    }
+  }
+  for (size_t i = 0; i < result.size(); i++) out_tokens[i] = result[i];
+  *reason = why;
+  *sampler_calls = calls;
+  *n_fed = nf;
+  return static_cast<int64_t>(result.size());
+}
+
 float gorch_oracle_bf16_to_f32(uint16_t v) { return bf16_to_f32(v); }
 
 // tensor.go:85-94: round-to-nearest-even, quiet NaN preserved.

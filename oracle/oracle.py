@@ -82,6 +82,11 @@ def lib() -> C.CDLL:
         L.gorch_oracle_multinomial_f32.argtypes = [
             C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
         ]
+        L.gorch_oracle_generate_scripted.restype = C.c_int64
+        L.gorch_oracle_generate_scripted.argtypes = [
+            C.c_int32, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64,
+            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+        ]
         L.gorch_oracle_bf16_to_f32.restype = C.c_float
         L.gorch_oracle_bf16_to_f32.argtypes = [C.c_uint16]
         L.gorch_oracle_f32_to_bf16.restype = C.c_uint16
@@ -176,6 +181,25 @@ def multinomial(probs, uniforms) -> np.ndarray:
     out = np.empty(B, dtype=np.int64)
     lib().gorch_oracle_multinomial_f32(p.ctypes.data, B, V, u.ctypes.data, out.ctypes.data)
     return out
+
+
+def generate_scripted(loop: int, prompt, script, max_new: int, max_seq: int, stops=()) -> dict:
+    """The reference's generate loop `loop` (0 GenerateWithConfig uncached, 1 generateCached,
+    2 qwen.Generate) with the sampler's answers taken from `script`."""
+    pr = np.ascontiguousarray(prompt, dtype=np.int64)
+    sc = np.full(max(int(max_new), 1), -1, dtype=np.int64)    # a script that ends early reads -1
+    sc[: min(len(script), sc.size)] = np.asarray(script, dtype=np.int64)[: sc.size]
+    st = np.ascontiguousarray(list(stops), dtype=np.int64)
+    out = np.empty(pr.size + max(int(max_new), 0), dtype=np.int64)
+    fed = np.empty(max(int(max_new), 1), dtype=np.int64)
+    reason = C.c_int32(0)
+    calls = C.c_int64(0)
+    n_fed = C.c_int64(0)
+    n = lib().gorch_oracle_generate_scripted(
+        int(loop), pr.ctypes.data, pr.size, sc.ctypes.data, int(max_new), int(max_seq), st.ctypes.data, st.size,
+        out.ctypes.data, C.byref(reason), C.byref(calls), fed.ctypes.data, C.byref(n_fed))
+    return {"tokens": out[:n].tolist(), "reason": int(reason.value), "sampler_calls": int(calls.value),
+            "fed": fed[: n_fed.value].tolist()}
 
 
 def f32_to_bf16_bits(a) -> np.ndarray:
