@@ -22,6 +22,7 @@ EXPORTS = [
     "gorch_cuda_vocab_local_dev", "gorch_cuda_vocab_merge_dev",
     "gorch_cuda_topk_dev", "gorch_cuda_multinomial_dev",
     "gorch_cuda_generate_control_dev", "gorch_cuda_generate_step_dev",
+    "gorch_cuda_softmax_dev", "gorch_cuda_cross_entropy_fwd_dev", "gorch_cuda_cross_entropy_bwd_dev",
 ]
 
 
@@ -86,6 +87,9 @@ def load() -> C.CDLL:
         "gorch_cuda_vocab_merge_dev": (i32, [p, p, i32, i64, i64, p, p, p, p, err]),
         "gorch_cuda_topk_dev": (i32, [p, p, i32, i64, i64, i64, i64, p, p, p, err]),
         "gorch_cuda_multinomial_dev": (i32, [p, p, i64, i64, i64, p, p, p, err]),
+        "gorch_cuda_softmax_dev": (i32, [p, p, i32, i64, i64, i64, p, i64, i32, err]),
+        "gorch_cuda_cross_entropy_fwd_dev": (i32, [p, p, i32, i64, i64, i64, p, p, p, p, err]),
+        "gorch_cuda_cross_entropy_bwd_dev": (i32, [p, p, i32, i64, i64, i64, p, p, f32, p, i64, err]),
         "gorch_cuda_generate_control_dev": (i32, [p, p, p, C.POINTER(GenControl), i64, err]),
         "gorch_cuda_generate_step_dev": (i32, [p, p, i32, i64, i64, i64, p, p, p, p, C.POINTER(GenControl), err]),
     }

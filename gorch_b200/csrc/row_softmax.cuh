@@ -1,0 +1,227 @@
+// Row softmax, log-softmax and cross-entropy over [B, V] logits at vocabulary scale
+// (ops.go:527-563 Softmax, :566-603 LogSoftmax; loss.go:55-124 CrossEntropyLoss forward,
+// :128-141 its backward; the Metal kernels they replace: metal/kernels.go:348-432).
+//
+// One 1024-thread CTA per SM, one row at a time per CTA. With one row per SM in flight the rows
+// being worked on (148 x 608 KB for the largest vocabulary) stay in L2, so the second pass of
+// the ops that write [B, V] re-reads its row from L2 and HBM sees each logit once and each
+// output once.
+//   pass 1   one read of the row: every thread keeps a running maximum m and the sum s of
+//            exp(x - m) over its own elements (rescaled when m grows), then the block combines
+//            them: M = max m, S = sum s * exp(m - M) in f64.
+//   pass 2   softmax: exp(x - M) / S; log-softmax: (x - M) - log S; cross-entropy backward:
+//            exp(x - lse) * scale, minus scale at the target. Written with streaming stores.
+// Cross-entropy forward needs pass 1 only: lse = M + log S, loss = lse - x[target].
+//
+// Values follow the reference's expressions with its f32 roundings (x - M in f32, the result of
+// exp rounded to f32, lse = M + f32(log(f64(S)))); the sum itself is formed in a different order
+// and in higher precision than the reference's sequential f32 loop. NaN and infinities come out
+// as upstream: a NaN anywhere, a +Inf, or a row of -Inf only makes the whole row NaN.
+#pragma once
+
+#include <cstdint>
+
+#include "block_util.cuh"
+#include "sample_common.cuh"
+#include "sample_kernel.cuh"   // Elem, RowView
+
+namespace gs {
+
+constexpr int RS_NT = 1024;
+constexpr int RS_NW = RS_NT / 32;
+constexpr int RS_UNROLL = 4;      // 16-byte loads in flight per thread
+
+constexpr int RS_SOFTMAX = 0;
+constexpr int RS_LOG_SOFTMAX = 1;
+constexpr int RS_CE_FWD = 2;
+constexpr int RS_CE_BWD = 3;
+
+struct RowSoftmaxArgs {
+  const void* x;            // [B, row_stride] f32 or bf16
+  int64_t row_stride;
+  int32_t V;
+  int64_t B;
+  int32_t mode;
+  void* out;                // softmax / log-softmax: [B, out_stride] in x's type; CE backward: f32 dx
+  int64_t out_stride;
+  const int32_t* targets;   // CE: [B]
+  float* row_loss;          // CE forward: [B]
+  float* row_lse;           // CE forward: [B] written; CE backward: [B] read
+  float scale;              // CE backward: grad / batch
+};
+
+// f32 -> bf16 bits, round to nearest even, NaN kept quiet (tensor.go:85-94)
+__device__ __forceinline__ uint32_t bf16_bits_rne(float v) {
+  const uint32_t b = __float_as_uint(v);
+  if (((b >> 23) & 0xffu) == 0xffu && (b & 0x7fffffu) != 0u) return (b >> 16) | 0x40u;
+  return (b + 0x7fffu + ((b >> 16) & 1u)) >> 16;
+}
+
+// the elements of vector v of the row; those outside the row read -Inf
+template <typename T>
+__device__ __forceinline__ void rs_unpack(const RowView<T>& rv, int v, const uint4& raw, float* x) {
+  constexpr int VEC = Elem<T>::VEC;
+  Elem<T>::unpack(raw, x);
+  if (v == 0 || v >= rv.nvec - 1) {
+    const int i0 = v * VEC - rv.shift;
+#pragma unroll
+    for (int c = 0; c < VEC; c++) if (i0 + c < 0 || i0 + c >= rv.V) x[c] = -INFINITY;
+  }
+}
+
+// Pass 1. Returns the row's maximum M (NaNs ignored) and S = sum exp(x - M) to every thread.
+template <typename T>
+__device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, bu::Scratch& sc, int tid, float& M, double& S) {
+  constexpr int VEC = Elem<T>::VEC;
+  float m = -INFINITY, s = 0.0f;
+  auto take = [&](int v, const uint4& raw) {
+    float x[VEC];
+    rs_unpack<T>(rv, v, raw, x);
+    float vm = x[0];
+#pragma unroll
+    for (int c = 1; c < VEC; c++) vm = fmaxf(vm, x[c]);
+    if (vm > m) { s *= expf(m - vm); m = vm; }               // m = -Inf before: s is 0 (or NaN) and stays so
+    if (m > -INFINITY) {
+#pragma unroll
+      for (int c = 0; c < VEC; c++) s += expf(x[c] - m);       // a NaN logit turns s NaN
+    } else {
+      // only -Inf and NaN so far: exp(-Inf - -Inf) must not poison the sum, a NaN logit must
+      float t = x[0];
+#pragma unroll
+      for (int c = 1; c < VEC; c++) t += x[c];
+      if (t != t) s = t;
+    }
+  };
+  int v = tid;
+  for (; v + (RS_UNROLL - 1) * RS_NT < rv.nvec; v += RS_UNROLL * RS_NT) {
+    uint4 r[RS_UNROLL];
+#pragma unroll
+    for (int q = 0; q < RS_UNROLL; q++) r[q] = __ldg(rv.vbase + v + q * RS_NT);
+#pragma unroll
+    for (int q = 0; q < RS_UNROLL; q++) take(v + q * RS_NT, r[q]);
+  }
+  for (; v < rv.nvec; v += RS_NT) take(v, __ldg(rv.vbase + v));
+  M = okey_to_float(static_cast<uint32_t>(bu::max_u64<RS_NW>(static_cast<unsigned long long>(okey(m)), sc, tid)));
+  // s NaN: NaN * anything stays NaN; m = -Inf with s = 0: the thread adds nothing
+  const double part = (m > -INFINITY || s != s) ? static_cast<double>(s) * static_cast<double>(expf(m - M)) : 0.0;
+  S = bu::sum_d<RS_NW>(part, sc, tid);
+  if (!(M > -INFINITY)) S = __longlong_as_double(0x7ff8000000000000ll);   // a row of -Inf only: upstream's -Inf - -Inf
+}
+
+// The N results of one input vector (elements i0 .. i0+N-1 of the row) into the output row:
+// 16-byte streaming stores where the output is aligned like the input (vec_ok) and the vector
+// lies inside the row, element by element otherwise.
+template <typename TO, int N>
+__device__ __forceinline__ void rs_store(TO* orow, bool vec_ok, int V, int i0, const float* y) {
+  static_assert((sizeof(TO) == 4 && (N == 4 || N == 8)) || (sizeof(TO) == 2 && N == 8), "f32 out of f32/bf16 in, bf16 out of bf16 in");
+  if (vec_ok && i0 >= 0 && i0 + N <= V) {
+    if (sizeof(TO) == 4) {
+#pragma unroll
+      for (int h = 0; h < N / 4; h++) {
+        uint4 o;
+        o.x = __float_as_uint(y[4 * h]); o.y = __float_as_uint(y[4 * h + 1]);
+        o.z = __float_as_uint(y[4 * h + 2]); o.w = __float_as_uint(y[4 * h + 3]);
+        __stcs(reinterpret_cast<uint4*>(orow + i0) + h, o);
+      }
+    } else {
+      uint4 o;
+      o.x = bf16_bits_rne(y[0]) | (bf16_bits_rne(y[1]) << 16);
+      o.y = bf16_bits_rne(y[2]) | (bf16_bits_rne(y[3]) << 16);
+      o.z = bf16_bits_rne(y[N - 4]) | (bf16_bits_rne(y[N - 3]) << 16);
+      o.w = bf16_bits_rne(y[N - 2]) | (bf16_bits_rne(y[N - 1]) << 16);
+      __stcs(reinterpret_cast<uint4*>(orow + i0), o);
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < N; c++) {
+      const int i = i0 + c;
+      if (i >= 0 && i < V) {
+        if (sizeof(TO) == 4) reinterpret_cast<float*>(orow)[i] = y[c];
+        else reinterpret_cast<uint16_t*>(orow)[i] = static_cast<uint16_t>(bf16_bits_rne(y[c]));
+      }
+    }
+  }
+}
+
+// Pass 2: y = f(x) for every element of the row, written to orow.
+template <typename T, typename TO, typename F>
+__device__ __forceinline__ void rs_map(const RowView<T>& rv, TO* orow, int tid, F&& f) {
+  constexpr int VEC = Elem<T>::VEC;
+  // orow + (v * VEC - shift) is 16-byte aligned for every v, or for none
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(orow) - static_cast<uintptr_t>(rv.shift) * sizeof(TO)) & 15u) == 0;
+  auto put = [&](int v, const uint4& raw) {
+    float x[VEC], y[VEC];
+    Elem<T>::unpack(raw, x);
+    const int i0 = v * VEC - rv.shift;
+#pragma unroll
+    for (int c = 0; c < VEC; c++) y[c] = f(x[c], i0 + c);
+    rs_store<TO, VEC>(orow, vec_ok, rv.V, i0, y);
+  };
+  int v = tid;
+  for (; v + (RS_UNROLL - 1) * RS_NT < rv.nvec; v += RS_UNROLL * RS_NT) {
+    uint4 r[RS_UNROLL];
+#pragma unroll
+    for (int q = 0; q < RS_UNROLL; q++) r[q] = __ldg(rv.vbase + v + q * RS_NT);
+#pragma unroll
+    for (int q = 0; q < RS_UNROLL; q++) put(v + q * RS_NT, r[q]);
+  }
+  for (; v < rv.nvec; v += RS_NT) put(v, __ldg(rv.vbase + v));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RS_NT, 1) row_softmax_kernel(const RowSoftmaxArgs A) {
+  __shared__ bu::Scratch sc;
+  const int tid = threadIdx.x;
+  const T* x = static_cast<const T*>(A.x);
+  for (int64_t row = blockIdx.x; row < A.B; row += gridDim.x) {
+    RowView<T> rv;
+    rv.init(x + row * A.row_stride, A.V);
+    if (A.mode == RS_CE_BWD) {
+      // loss.go:128-141: dx = exp(x - lse) * scale, minus scale at the target
+      const float lse = A.row_lse[row], scale = A.scale;
+      const int t = A.targets[row];
+      rs_map<T, float>(rv, static_cast<float*>(A.out) + row * A.out_stride, tid, [&](float xv, int i) {
+        float d = expf(xv - lse) * scale;
+        if (i == t) d -= scale;
+        return d;
+      });
+      continue;
+    }
+    float M;
+    double S;
+    rs_max_sum<T>(rv, sc, tid, M, S);
+    const float Sf = static_cast<float>(S);                  // the reference's f32 sum
+    if (A.mode == RS_CE_FWD) {
+      if (tid == 0) {
+        // loss.go:118-120: l = rowMax + f32(log(f64(sumExp))); loss = l - row[target]
+        const float lse = M + static_cast<float>(log(static_cast<double>(Sf)));
+        const int t = A.targets[row];
+        float xt = __int_as_float(0x7fc00000);               // a target outside the row: upstream panics; NaN here
+        if (t >= 0 && t < A.V) {
+          if (sizeof(T) == 4) xt = reinterpret_cast<const float*>(x)[row * A.row_stride + t];
+          else xt = __uint_as_float(static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(x)[row * A.row_stride + t]) << 16);
+        }
+        A.row_lse[row] = lse;
+        A.row_loss[row] = lse - xt;
+      }
+    } else if (A.mode == RS_SOFTMAX) {
+      // ops.go:544-550: f32(exp(f64(x - max))) / sum
+      rs_map<T, T>(rv, static_cast<T*>(A.out) + row * A.out_stride, tid, [&](float xv, int) { return expf(xv - M) / Sf; });
+    } else {
+      // ops.go:589-592: x - max - f32(log(f64(sumExp)))
+      const float logS = static_cast<float>(log(static_cast<double>(Sf)));
+      rs_map<T, T>(rv, static_cast<T*>(A.out) + row * A.out_stride, tid, [&](float xv, int) { return xv - M - logS; });
+    }
+  }
+}
+
+// Mean of the row losses in row order (loss.go:83: total / batch), one warp-sized CTA.
+__global__ void __launch_bounds__(256) mean_loss_kernel(const float* row_loss, int64_t B, float* out) {
+  __shared__ bu::Scratch sc;
+  double acc = 0.0;
+  for (int64_t i = threadIdx.x; i < B; i += 256) acc += static_cast<double>(row_loss[i]);
+  acc = bu::sum_d<8>(acc, sc, threadIdx.x);
+  if (threadIdx.x == 0) *out = static_cast<float>(acc / static_cast<double>(B));
+}
+
+}  // namespace gs

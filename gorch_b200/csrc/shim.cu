@@ -25,6 +25,7 @@
 #include "sample_vocab.cuh"
 #include "index_ops.cuh"
 #include "generate_control.cuh"
+#include "row_softmax.cuh"
 
 namespace {
 
@@ -789,6 +790,87 @@ int gorch_cuda_generate_step_dev(GorchCudaCtxRef ctx, const void* logits, int dt
                                  nullptr, nullptr, errOut);
   if (rc) return rc;
   return launch_generate_control(static_cast<Ctx*>(ctx), out_ids, out_flags, gc, B, errOut);
+}
+
+static int launch_row_softmax(Ctx* c, int dtype, const gs::RowSoftmaxArgs& a, char** errOut) {
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  const unsigned g = static_cast<unsigned>(a.B < c->sm_count ? a.B : c->sm_count);
+  if (dtype == GORCH_CUDA_F32) gs::row_softmax_kernel<float><<<g, gs::RS_NT, 0, c->stream>>>(a);
+  else gs::row_softmax_kernel<uint16_t><<<g, gs::RS_NT, 0, c->stream>>>(a);
+  CUDA_TRY(cudaGetLastError(), errOut);
+  c->counters.kernel_launches += 1;
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_softmax_dev(GorchCudaCtxRef ctx, const void* x, int dtype, int64_t B, int64_t V,
+                           int64_t row_stride, void* out, int64_t out_stride, int log_softmax,
+                           char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = check_shape(dtype, B, V, row_stride, errOut);
+  if (rc) return rc;
+  if (out_stride < V) { set_err(errOut, "gorch_cuda: out_stride %lld below V", (long long)out_stride); return GORCH_CUDA_ERR_BAD_ARG; }
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!x || !out) { set_err(errOut, "gorch_cuda: null pointer argument"); return GORCH_CUDA_ERR_BAD_ARG; }
+  const size_t es = elem_size(dtype);
+  if ((reinterpret_cast<uintptr_t>(x) % es) != 0 || (reinterpret_cast<uintptr_t>(out) % es) != 0) {
+    set_err(errOut, "gorch_cuda: pointer not aligned to its element type");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  gs::RowSoftmaxArgs a{};
+  a.x = x; a.row_stride = row_stride; a.V = static_cast<int32_t>(V); a.B = B;
+  a.mode = log_softmax ? gs::RS_LOG_SOFTMAX : gs::RS_SOFTMAX;
+  a.out = out; a.out_stride = out_stride;
+  return launch_row_softmax(c, dtype, a, errOut);
+}
+
+int gorch_cuda_cross_entropy_fwd_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                                     int64_t V, int64_t row_stride, const int32_t* targets,
+                                     float* row_loss, float* row_lse, float* mean_loss,
+                                     char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = check_shape(dtype, B, V, row_stride, errOut);
+  if (rc) return rc;
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!logits || !targets || !row_loss || !row_lse) { set_err(errOut, "gorch_cuda: null pointer argument"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if ((reinterpret_cast<uintptr_t>(logits) % elem_size(dtype)) != 0) {
+    set_err(errOut, "gorch_cuda: pointer not aligned to its element type");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  gs::RowSoftmaxArgs a{};
+  a.x = logits; a.row_stride = row_stride; a.V = static_cast<int32_t>(V); a.B = B;
+  a.mode = gs::RS_CE_FWD; a.targets = targets; a.row_loss = row_loss; a.row_lse = row_lse;
+  rc = launch_row_softmax(c, dtype, a, errOut);
+  if (rc) return rc;
+  if (mean_loss) {
+    gs::mean_loss_kernel<<<1, 256, 0, c->stream>>>(row_loss, B, mean_loss);
+    CUDA_TRY(cudaGetLastError(), errOut);
+    c->counters.kernel_launches += 1;
+  }
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_cross_entropy_bwd_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                                     int64_t V, int64_t row_stride, const int32_t* targets,
+                                     const float* row_lse, float scale, float* dx,
+                                     int64_t dx_stride, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = check_shape(dtype, B, V, row_stride, errOut);
+  if (rc) return rc;
+  if (dx_stride < V) { set_err(errOut, "gorch_cuda: dx_stride %lld below V", (long long)dx_stride); return GORCH_CUDA_ERR_BAD_ARG; }
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!logits || !targets || !row_lse || !dx) { set_err(errOut, "gorch_cuda: null pointer argument"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if ((reinterpret_cast<uintptr_t>(logits) % elem_size(dtype)) != 0 || (reinterpret_cast<uintptr_t>(dx) % 4) != 0) {
+    set_err(errOut, "gorch_cuda: pointer not aligned to its element type");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  gs::RowSoftmaxArgs a{};
+  a.x = logits; a.row_stride = row_stride; a.V = static_cast<int32_t>(V); a.B = B;
+  a.mode = gs::RS_CE_BWD; a.targets = targets; a.row_lse = const_cast<float*>(row_lse);
+  a.scale = scale; a.out = dx; a.out_stride = dx_stride;
+  return launch_row_softmax(c, dtype, a, errOut);
 }
 
 int64_t gorch_cuda_sample_row(GorchCudaCtxRef ctx, const float* logits, int64_t n,

@@ -265,6 +265,30 @@ int gorch_cuda_generate_step_dev(GorchCudaCtxRef ctx, const void* logits, int dt
                                  const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
                                  const GorchGenControl* gc, char** errOut);
 
+/* Row softmax, log-softmax and cross-entropy over x [B,V] (f32, or bf16 upcast) at vocabulary
+ * scale, as device ops (device pointers, asynchronous on the context's stream).
+ * gorch_cuda_softmax_dev: log_softmax == 0: gorch.Softmax (ops.go:527-563), out = exp(x - max) /
+ * sum; else gorch.LogSoftmax (ops.go:566-603), out = x - max - log(sum). out [B,out_stride] has
+ * x's type (bf16: rounded to nearest even, as downcastToBF16). out may not overlap x.
+ * gorch_cuda_cross_entropy_fwd_dev (loss.go:55-124): row_lse[b] = max + log(sum exp(x - max)),
+ * row_loss[b] = row_lse[b] - x[b, targets[b]], mean_loss[0] = sum(row_loss) / B (may be NULL). A
+ * target outside [0,V) makes that row's loss NaN (upstream panics).
+ * gorch_cuda_cross_entropy_bwd_dev (loss.go:128-141): dx[b,j] = exp(x[b,j] - row_lse[b]) * scale,
+ * minus scale at j = targets[b]; dx is f32 [B,dx_stride]; scale = upstream grad / batch.
+ * The row sum is formed in another order and a higher precision than upstream's sequential f32
+ * loop; everything else keeps upstream's f32 roundings. */
+int gorch_cuda_softmax_dev(GorchCudaCtxRef ctx, const void* x, int dtype, int64_t B, int64_t V,
+                           int64_t row_stride, void* out, int64_t out_stride, int log_softmax,
+                           char** errOut);
+int gorch_cuda_cross_entropy_fwd_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                                     int64_t V, int64_t row_stride, const int32_t* targets,
+                                     float* row_loss, float* row_lse, float* mean_loss,
+                                     char** errOut);
+int gorch_cuda_cross_entropy_bwd_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                                     int64_t V, int64_t row_stride, const int32_t* targets,
+                                     const float* row_lse, float scale, float* dx,
+                                     int64_t dx_stride, char** errOut);
+
 /* One row, the exact shape of the reference's calls: sample(logits,
  * temperature, topK, topP) (generate.go:147) with the uniform passed in, and
  * argmax when temperature == 0. Returns the token id, or -1 with *errOut set. */

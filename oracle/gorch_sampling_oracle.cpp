@@ -417,6 +417,69 @@ int64_t gorch_oracle_generate_scripted(int32_t loop, const int64_t* prompt, int6
   return static_cast<int64_t>(result.size());
 }
 
+// ops.go:527-551: Softmax forward over a (batch, classes) f32 tensor, loop for loop: the row
+// maximum by strict `>` from element 0, f32(exp(f64(x - max))) summed sequentially in f32, then
+// an f32 division.
+void gorch_oracle_softmax_f32(const float* x, int64_t B, int64_t V, float* out) {
+  for (int64_t i = 0; i < B; i++) {
+    const float* row = x + i * V;
+    float* o = out + i * V;
+    float row_max = row[0];
+    for (int64_t j = 1; j < V; j++) if (row[j] > row_max) row_max = row[j];
+    float sum = 0.0f;
+    for (int64_t j = 0; j < V; j++) {
+      o[j] = static_cast<float>(std::exp(static_cast<double>(row[j] - row_max)));
+      sum += o[j];
+    }
+    for (int64_t j = 0; j < V; j++) o[j] /= sum;
+  }
+}
+
+// ops.go:566-593: LogSoftmax forward: x - max - f32(log(f64(sumExp))), two f32 subtractions.
+void gorch_oracle_log_softmax_f32(const float* x, int64_t B, int64_t V, float* out) {
+  for (int64_t i = 0; i < B; i++) {
+    const float* row = x + i * V;
+    float* o = out + i * V;
+    float row_max = row[0];
+    for (int64_t j = 1; j < V; j++) if (row[j] > row_max) row_max = row[j];
+    float sum_exp = 0.0f;
+    for (int64_t j = 0; j < V; j++) sum_exp += static_cast<float>(std::exp(static_cast<double>(row[j] - row_max)));
+    const float log_sum_exp = static_cast<float>(std::log(static_cast<double>(sum_exp)));
+    for (int64_t j = 0; j < V; j++) o[j] = row[j] - row_max - log_sum_exp;
+  }
+}
+
+// loss.go:108-124 (ceForwardCPU) and :83: per-row logsumexp and the mean loss. Upstream's row
+// passes go through Accelerate (vDSP/vForce, not part of the reference's tree): maximum, x - max,
+// elementwise f32 exp, f32 sum; they are restated here as scalar f32 loops.
+float gorch_oracle_cross_entropy_fwd_f32(const float* x, const int32_t* targets, int64_t B, int64_t V,
+                                         float* row_loss, float* row_lse) {
+  float total = 0.0f;
+  for (int64_t i = 0; i < B; i++) {
+    const float* row = x + i * V;
+    float row_max = row[0];
+    for (int64_t j = 1; j < V; j++) if (row[j] > row_max) row_max = row[j];
+    float sum_exp = 0.0f;
+    for (int64_t j = 0; j < V; j++) sum_exp += static_cast<float>(std::exp(static_cast<double>(row[j] - row_max)));
+    const float l = row_max + static_cast<float>(std::log(static_cast<double>(sum_exp)));
+    row_lse[i] = l;
+    row_loss[i] = l - row[targets[i]];
+    total += row_loss[i];
+  }
+  return total / static_cast<float>(B);
+}
+
+// loss.go:128-141 (ceBackwardCPU): dx = exp(x - lse) * scale, then dx[target] -= scale.
+void gorch_oracle_cross_entropy_bwd_f32(const float* x, const int32_t* targets, const float* row_lse,
+                                        int64_t B, int64_t V, float scale, float* dx) {
+  for (int64_t i = 0; i < B; i++) {
+    const float* row = x + i * V;
+    float* d = dx + i * V;
+    for (int64_t j = 0; j < V; j++) d[j] = static_cast<float>(std::exp(static_cast<double>(row[j] - row_lse[i]))) * scale;
+    d[targets[i]] -= scale;
+  }
+}
+
 float gorch_oracle_bf16_to_f32(uint16_t v) { return bf16_to_f32(v); }
 
 // tensor.go:85-94: round-to-nearest-even, quiet NaN preserved.

@@ -87,6 +87,14 @@ def lib() -> C.CDLL:
             C.c_int32, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64,
             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
         ]
+        L.gorch_oracle_softmax_f32.restype = None
+        L.gorch_oracle_softmax_f32.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+        L.gorch_oracle_log_softmax_f32.restype = None
+        L.gorch_oracle_log_softmax_f32.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+        L.gorch_oracle_cross_entropy_fwd_f32.restype = C.c_float
+        L.gorch_oracle_cross_entropy_fwd_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
+        L.gorch_oracle_cross_entropy_bwd_f32.restype = None
+        L.gorch_oracle_cross_entropy_bwd_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_void_p]
         L.gorch_oracle_bf16_to_f32.restype = C.c_float
         L.gorch_oracle_bf16_to_f32.argtypes = [C.c_uint16]
         L.gorch_oracle_f32_to_bf16.restype = C.c_uint16
@@ -200,6 +208,39 @@ def generate_scripted(loop: int, prompt, script, max_new: int, max_seq: int, sto
         out.ctypes.data, C.byref(reason), C.byref(calls), fed.ctypes.data, C.byref(n_fed))
     return {"tokens": out[:n].tolist(), "reason": int(reason.value), "sampler_calls": int(calls.value),
             "fed": fed[: n_fed.value].tolist()}
+
+
+def softmax(x, log: bool = False) -> np.ndarray:
+    """gorch.Softmax / gorch.LogSoftmax forward over f32 [B,V] (ops.go:527-551, :566-593)."""
+    a = _f32(x)
+    B, V = a.shape
+    out = np.empty_like(a)
+    fn = lib().gorch_oracle_log_softmax_f32 if log else lib().gorch_oracle_softmax_f32
+    fn(a.ctypes.data, B, V, out.ctypes.data)
+    return out
+
+
+def cross_entropy_fwd(x, targets):
+    """ceForwardCPU + the mean (loss.go:83, :108-124): (mean loss, row_loss [B], row_lse [B])."""
+    a = _f32(x)
+    B, V = a.shape
+    t = np.ascontiguousarray(targets, dtype=np.int32)
+    assert t.shape == (B,) and t.min() >= 0 and t.max() < V
+    row_loss = np.empty(B, dtype=np.float32)
+    row_lse = np.empty(B, dtype=np.float32)
+    mean = lib().gorch_oracle_cross_entropy_fwd_f32(a.ctypes.data, t.ctypes.data, B, V, row_loss.ctypes.data, row_lse.ctypes.data)
+    return float(mean), row_loss, row_lse
+
+
+def cross_entropy_bwd(x, targets, row_lse, scale: float) -> np.ndarray:
+    """ceBackwardCPU (loss.go:128-141)."""
+    a = _f32(x)
+    B, V = a.shape
+    t = np.ascontiguousarray(targets, dtype=np.int32)
+    lse = _f32(row_lse)
+    dx = np.empty_like(a)
+    lib().gorch_oracle_cross_entropy_bwd_f32(a.ctypes.data, t.ctypes.data, lse.ctypes.data, B, V, float(scale), dx.ctypes.data)
+    return dx
 
 
 def f32_to_bf16_bits(a) -> np.ndarray:
