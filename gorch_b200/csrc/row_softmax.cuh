@@ -57,6 +57,38 @@ __device__ __forceinline__ uint32_t bf16_bits_rne(float v) {
   return (b + 0x7fffu + ((b >> 16) & 1u)) >> 16;
 }
 
+// Two f32 in one 64-bit register for the packed FMA pipe (half the issue slots per element).
+typedef unsigned long long rs_f2;
+__device__ __forceinline__ rs_f2 rs_pk(float a, float b) { rs_f2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ void rs_upk(rs_f2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ rs_f2 rs_fma2(rs_f2 a, rs_f2 b, rs_f2 c) { rs_f2 d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ rs_f2 rs_add2(rs_f2 a, rs_f2 b) { rs_f2 d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ rs_f2 rs_mul2(rs_f2 a, rs_f2 b) { rs_f2 d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ float rs_maxnan(float a, float b) { float d; asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b)); return d; }
+__device__ __forceinline__ float rs_ex2(float t) { float e; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t)); return e; }
+
+// exp of two f32 arguments, each result within about 3e-7 relative of the correctly rounded one
+// (the reference rounds a double exp to f32). exp(d) = 2^t (1 + r ln 2) with t = rn(d log2 e) and
+// r = d log2 e - t recovered exactly by an FMA plus the low part of log2 e; 2^t from the special
+// function unit (2 ulp). Arguments below -200 give 0 like everything below -104 does in f32 (the
+// clamp keeps -Inf from turning into Inf - Inf); a NaN stays a NaN.
+__device__ __forceinline__ rs_f2 rs_exp2(float d0, float d1) {
+  constexpr float L2E = 1.44269502162933349609375f, L2E_LO = 1.925963033500011e-8f, LN2 = 0.693147182464599609375f;
+  const rs_f2 D = rs_pk(rs_maxnan(d0, -200.0f), rs_maxnan(d1, -200.0f));
+  const rs_f2 NT = rs_mul2(D, rs_pk(-L2E, -L2E));                       // -t, exactly
+  rs_f2 R = rs_fma2(D, rs_pk(L2E, L2E), NT);
+  R = rs_fma2(D, rs_pk(L2E_LO, L2E_LO), R);
+  float n0, n1;
+  rs_upk(NT, n0, n1);
+  const rs_f2 P = rs_pk(rs_ex2(-n0), rs_ex2(-n1));
+  return rs_fma2(P, rs_mul2(R, rs_pk(LN2, LN2)), P);
+}
+__device__ __forceinline__ float rs_exp1(float d) {
+  float a, b;
+  rs_upk(rs_exp2(d, d), a, b);
+  return a;
+}
+
 // the elements of vector v of the row; those outside the row read -Inf
 template <typename T>
 __device__ __forceinline__ void rs_unpack(const RowView<T>& rv, int v, const uint4& raw, float* x) {
@@ -73,23 +105,28 @@ __device__ __forceinline__ void rs_unpack(const RowView<T>& rv, int v, const uin
 template <typename T>
 __device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, bu::Scratch& sc, int tid, float& M, double& S) {
   constexpr int VEC = Elem<T>::VEC;
-  float m = -INFINITY, s = 0.0f;
+  float m = -INFINITY;
+  rs_f2 s2 = rs_pk(0.0f, 0.0f);                                // two running sums (even and odd elements)
   auto take = [&](int v, const uint4& raw) {
     float x[VEC];
     rs_unpack<T>(rv, v, raw, x);
     float vm = x[0];
 #pragma unroll
     for (int c = 1; c < VEC; c++) vm = fmaxf(vm, x[c]);
-    if (vm > m) { s *= expf(m - vm); m = vm; }               // m = -Inf before: s is 0 (or NaN) and stays so
+    if (vm > m) {                                              // m = -Inf before: the sums are 0 (or NaN) and stay so
+      const float f = rs_exp1(m - vm);
+      s2 = rs_mul2(s2, rs_pk(f, f));
+      m = vm;
+    }
     if (m > -INFINITY) {
 #pragma unroll
-      for (int c = 0; c < VEC; c++) s += expf(x[c] - m);       // a NaN logit turns s NaN
+      for (int c = 0; c < VEC; c += 2) s2 = rs_add2(s2, rs_exp2(x[c] - m, x[c + 1] - m));   // a NaN logit turns the sum NaN
     } else {
       // only -Inf and NaN so far: exp(-Inf - -Inf) must not poison the sum, a NaN logit must
       float t = x[0];
 #pragma unroll
       for (int c = 1; c < VEC; c++) t += x[c];
-      if (t != t) s = t;
+      if (t != t) s2 = rs_pk(t, t);
     }
   };
   int v = tid;
@@ -103,6 +140,9 @@ __device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, bu::Scratch& sc
   for (; v < rv.nvec; v += RS_NT) take(v, __ldg(rv.vbase + v));
   M = okey_to_float(static_cast<uint32_t>(bu::max_u64<RS_NW>(static_cast<unsigned long long>(okey(m)), sc, tid)));
   // s NaN: NaN * anything stays NaN; m = -Inf with s = 0: the thread adds nothing
+  float sa, sb;
+  rs_upk(s2, sa, sb);
+  const float s = sa + sb;
   const double part = (m > -INFINITY || s != s) ? static_cast<double>(s) * static_cast<double>(expf(m - M)) : 0.0;
   S = bu::sum_d<RS_NW>(part, sc, tid);
   if (!(M > -INFINITY)) S = __longlong_as_double(0x7ff8000000000000ll);   // a row of -Inf only: upstream's -Inf - -Inf
@@ -143,7 +183,7 @@ __device__ __forceinline__ void rs_store(TO* orow, bool vec_ok, int V, int i0, c
   }
 }
 
-// Pass 2: y = f(x) for every element of the row, written to orow.
+// Pass 2: f(xa, xb, i, ya, yb) maps elements i and i+1 of the row; the results go to orow.
 template <typename T, typename TO, typename F>
 __device__ __forceinline__ void rs_map(const RowView<T>& rv, TO* orow, int tid, F&& f) {
   constexpr int VEC = Elem<T>::VEC;
@@ -154,7 +194,7 @@ __device__ __forceinline__ void rs_map(const RowView<T>& rv, TO* orow, int tid, 
     Elem<T>::unpack(raw, x);
     const int i0 = v * VEC - rv.shift;
 #pragma unroll
-    for (int c = 0; c < VEC; c++) y[c] = f(x[c], i0 + c);
+    for (int c = 0; c < VEC; c += 2) f(x[c], x[c + 1], i0 + c, y[c], y[c + 1]);
     rs_store<TO, VEC>(orow, vec_ok, rv.V, i0, y);
   };
   int v = tid;
@@ -180,10 +220,10 @@ __global__ void __launch_bounds__(RS_NT, 1) row_softmax_kernel(const RowSoftmaxA
       // loss.go:128-141: dx = exp(x - lse) * scale, minus scale at the target
       const float lse = A.row_lse[row], scale = A.scale;
       const int t = A.targets[row];
-      rs_map<T, float>(rv, static_cast<float*>(A.out) + row * A.out_stride, tid, [&](float xv, int i) {
-        float d = expf(xv - lse) * scale;
-        if (i == t) d -= scale;
-        return d;
+      rs_map<T, float>(rv, static_cast<float*>(A.out) + row * A.out_stride, tid, [&](float xa, float xb, int i, float& ya, float& yb) {
+        rs_upk(rs_mul2(rs_exp2(xa - lse, xb - lse), rs_pk(scale, scale)), ya, yb);
+        if (i == t) ya -= scale;
+        if (i + 1 == t) yb -= scale;
       });
       continue;
     }
@@ -205,12 +245,18 @@ __global__ void __launch_bounds__(RS_NT, 1) row_softmax_kernel(const RowSoftmaxA
         A.row_loss[row] = lse - xt;
       }
     } else if (A.mode == RS_SOFTMAX) {
-      // ops.go:544-550: f32(exp(f64(x - max))) / sum
-      rs_map<T, T>(rv, static_cast<T*>(A.out) + row * A.out_stride, tid, [&](float xv, int) { return expf(xv - M) / Sf; });
+      // ops.go:544-550: f32(exp(f64(x - max))) / sum; the quotient as a product with 1 / sum (within 1 ulp of it)
+      const float inv = 1.0f / Sf;
+      rs_map<T, T>(rv, static_cast<T*>(A.out) + row * A.out_stride, tid, [&](float xa, float xb, int, float& ya, float& yb) {
+        rs_upk(rs_mul2(rs_exp2(xa - M, xb - M), rs_pk(inv, inv)), ya, yb);
+      });
     } else {
       // ops.go:589-592: x - max - f32(log(f64(sumExp)))
       const float logS = static_cast<float>(log(static_cast<double>(Sf)));
-      rs_map<T, T>(rv, static_cast<T*>(A.out) + row * A.out_stride, tid, [&](float xv, int) { return xv - M - logS; });
+      rs_map<T, T>(rv, static_cast<T*>(A.out) + row * A.out_stride, tid, [&](float xa, float xb, int, float& ya, float& yb) {
+        ya = xa - M - logS;
+        yb = xb - M - logS;
+      });
     }
   }
 }
