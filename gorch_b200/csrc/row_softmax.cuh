@@ -29,7 +29,9 @@ namespace gs {
 
 constexpr int RS_NT = 1024;
 constexpr int RS_NW = RS_NT / 32;
-constexpr int RS_UNROLL = 4;      // 16-byte loads in flight per thread
+constexpr int RS_UNROLL = 4;      // 16-byte loads per thread and loop iteration
+constexpr int RS_STAGES = 3;      // pass 1: iterations staged in shared memory (two in flight while one is consumed)
+constexpr int RS_DYN_BYTES = RS_STAGES * RS_UNROLL * RS_NT * 16;   // 192 KB
 
 constexpr int RS_SOFTMAX = 0;
 constexpr int RS_LOG_SOFTMAX = 1;
@@ -103,8 +105,9 @@ __device__ __forceinline__ void rs_unpack(const RowView<T>& rv, int v, const uin
 
 // Pass 1. Returns the row's maximum M (NaNs ignored) and S = sum exp(x - M) to every thread.
 template <typename T>
-__device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, bu::Scratch& sc, int tid, float& M, double& S) {
+__device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, const uint4* ring, bu::Scratch& sc, int tid, float& M, double& S) {
   constexpr int VEC = Elem<T>::VEC;
+  const uint32_t ring_addr = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
   float m = -INFINITY;
   rs_f2 s2 = rs_pk(0.0f, 0.0f);                                // two running sums (even and odd elements)
   auto take = [&](int v, const uint4& raw) {
@@ -129,15 +132,36 @@ __device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, bu::Scratch& sc
       if (t != t) s2 = rs_pk(t, t);
     }
   };
-  int v = tid;
-  for (; v + (RS_UNROLL - 1) * RS_NT < rv.nvec; v += RS_UNROLL * RS_NT) {
-    uint4 r[RS_UNROLL];
+  // Registers could hold 64 KB of loads in flight per SM, which at HBM latency is about half of
+  // an SM's share of the bandwidth. So the row is staged through shared memory by asynchronous
+  // 16-byte copies: a thread copies the vectors it will consume itself (no barrier, it only waits
+  // for its own copy groups), RS_STAGES - 1 iterations (128 KB per SM) ahead of their use.
+  const int n_it = (rv.nvec + RS_UNROLL * RS_NT - 1) / (RS_UNROLL * RS_NT);
+  auto issue = [&](int it) {
+    if (it < n_it) {
+      const int base = it * RS_UNROLL * RS_NT + tid;
+      const uint32_t dst = ring_addr + static_cast<uint32_t>(((it % RS_STAGES) * RS_UNROLL * RS_NT + tid) * 16);
 #pragma unroll
-    for (int q = 0; q < RS_UNROLL; q++) r[q] = __ldg(rv.vbase + v + q * RS_NT);
+      for (int q = 0; q < RS_UNROLL; q++) {
+        if (base + q * RS_NT < rv.nvec)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst + q * RS_NT * 16), "l"(rv.vbase + base + q * RS_NT) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
 #pragma unroll
-    for (int q = 0; q < RS_UNROLL; q++) take(v + q * RS_NT, r[q]);
+  for (int st = 0; st < RS_STAGES - 1; st++) issue(st);
+  for (int it = 0; it < n_it; it++) {
+    issue(it + RS_STAGES - 1);
+    asm volatile("cp.async.wait_group %0;" :: "n"(RS_STAGES - 1) : "memory");
+    const int base = it * RS_UNROLL * RS_NT + tid;
+    const uint4* src = ring + (it % RS_STAGES) * RS_UNROLL * RS_NT + tid;
+#pragma unroll
+    for (int q = 0; q < RS_UNROLL; q++) {
+      if (base + q * RS_NT < rv.nvec) take(base + q * RS_NT, src[q * RS_NT]);
+    }
   }
-  for (; v < rv.nvec; v += RS_NT) take(v, __ldg(rv.vbase + v));
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   M = okey_to_float(static_cast<uint32_t>(bu::max_u64<RS_NW>(static_cast<unsigned long long>(okey(m)), sc, tid)));
   // s NaN: NaN * anything stays NaN; m = -Inf with s = 0: the thread adds nothing
   float sa, sb;
@@ -210,7 +234,9 @@ __device__ __forceinline__ void rs_map(const RowView<T>& rv, TO* orow, int tid, 
 
 template <typename T>
 __global__ void __launch_bounds__(RS_NT, 1) row_softmax_kernel(const RowSoftmaxArgs A) {
+  extern __shared__ __align__(16) unsigned char rs_dyn[];
   __shared__ bu::Scratch sc;
+  const uint4* ring = reinterpret_cast<const uint4*>(rs_dyn);
   const int tid = threadIdx.x;
   const T* x = static_cast<const T*>(A.x);
   for (int64_t row = blockIdx.x; row < A.B; row += gridDim.x) {
@@ -229,7 +255,7 @@ __global__ void __launch_bounds__(RS_NT, 1) row_softmax_kernel(const RowSoftmaxA
     }
     float M;
     double S;
-    rs_max_sum<T>(rv, sc, tid, M, S);
+    rs_max_sum<T>(rv, ring, sc, tid, M, S);
     const float Sf = static_cast<float>(S);                  // the reference's f32 sum
     if (A.mode == RS_CE_FWD) {
       if (tid == 0) {

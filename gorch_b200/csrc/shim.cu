@@ -447,6 +447,8 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   if ((e = cudaFuncSetAttribute(gs::multinomial_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::MN_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::vocab_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::VM_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::w256::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w256::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::row_softmax_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::RS_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::row_softmax_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::RS_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::w1024::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w1024::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::w256::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w256::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::w1024::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w1024::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
@@ -795,8 +797,8 @@ int gorch_cuda_generate_step_dev(GorchCudaCtxRef ctx, const void* logits, int dt
 static int launch_row_softmax(Ctx* c, int dtype, const gs::RowSoftmaxArgs& a, char** errOut) {
   CUDA_TRY(cudaSetDevice(c->device), errOut);
   const unsigned g = static_cast<unsigned>(a.B < c->sm_count ? a.B : c->sm_count);
-  if (dtype == GORCH_CUDA_F32) gs::row_softmax_kernel<float><<<g, gs::RS_NT, 0, c->stream>>>(a);
-  else gs::row_softmax_kernel<uint16_t><<<g, gs::RS_NT, 0, c->stream>>>(a);
+  if (dtype == GORCH_CUDA_F32) gs::row_softmax_kernel<float><<<g, gs::RS_NT, gs::RS_DYN_BYTES, c->stream>>>(a);
+  else gs::row_softmax_kernel<uint16_t><<<g, gs::RS_NT, gs::RS_DYN_BYTES, c->stream>>>(a);
   CUDA_TRY(cudaGetLastError(), errOut);
   c->counters.kernel_launches += 1;
   return GORCH_CUDA_OK;
