@@ -59,6 +59,7 @@ struct Scratch {  // grow-only device allocation
 struct Ctx {
   int device = 0;
   int sm_count = 148;
+  int64_t l2_bytes = 126ll << 20;
   cudaStream_t own_stream = nullptr;
   cudaStream_t stream = nullptr;
   cudaStream_t side_stream = nullptr;     // the wide kernel of a mixed batch runs here, beside the narrow one
@@ -423,6 +424,7 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
     return nullptr;
   }
   c->sm_count = prop.multiProcessorCount;
+  if (prop.l2CacheSize > 0) c->l2_bytes = prop.l2CacheSize;
   if ((e = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking)) != cudaSuccess) return fail("cudaStreamCreate", e);
   c->stream = c->own_stream;
   if ((e = cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking)) != cudaSuccess) return fail("cudaStreamCreate", e);
@@ -796,9 +798,30 @@ int gorch_cuda_generate_step_dev(GorchCudaCtxRef ctx, const void* logits, int dt
 
 static int launch_row_softmax(Ctx* c, int dtype, const gs::RowSoftmaxArgs& a, char** errOut) {
   CUDA_TRY(cudaSetDevice(c->device), errOut);
-  const unsigned g = static_cast<unsigned>(a.B < c->sm_count ? a.B : c->sm_count);
-  if (dtype == GORCH_CUDA_F32) gs::row_softmax_kernel<float><<<g, gs::RS_NT, gs::RS_DYN_BYTES, c->stream>>>(a);
-  else gs::row_softmax_kernel<uint16_t><<<g, gs::RS_NT, gs::RS_DYN_BYTES, c->stream>>>(a);
+  // A pair of CTAs per row where it was measured to pay: the two-pass ops when one row per SM in
+  // flight would not fit in half of L2 (each pass-2 read then came from HBM again), and the
+  // cross-entropy backward (no exchange, only finer work units) for rows of 256 KB and more. The
+  // cross-entropy forward is one pass: the pair's barrier per row only costs there.
+  const int64_t row_bytes = static_cast<int64_t>(a.V) * static_cast<int64_t>(elem_size(dtype));
+  bool pair = false;
+  if (a.mode == gs::RS_SOFTMAX || a.mode == gs::RS_LOG_SOFTMAX) pair = row_bytes * c->sm_count > (static_cast<int64_t>(c->l2_bytes) / 2);
+  else if (a.mode == gs::RS_CE_BWD) pair = row_bytes >= 262144;
+  const int C = (pair && c->sm_count >= 2) ? 2 : 1;
+  const int64_t clusters = a.B < c->sm_count / C ? a.B : c->sm_count / C;
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(static_cast<unsigned>(clusters * C));
+  lc.blockDim = dim3(gs::RS_NT);
+  lc.dynamicSmemBytes = gs::RS_DYN_BYTES;
+  lc.stream = c->stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = static_cast<unsigned>(C);
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  lc.attrs = at;
+  lc.numAttrs = 1;
+  if (dtype == GORCH_CUDA_F32) { CUDA_TRY(cudaLaunchKernelEx(&lc, gs::row_softmax_kernel<float>, a), errOut); }
+  else { CUDA_TRY(cudaLaunchKernelEx(&lc, gs::row_softmax_kernel<uint16_t>, a), errOut); }
   CUDA_TRY(cudaGetLastError(), errOut);
   c->counters.kernel_launches += 1;
   return GORCH_CUDA_OK;
