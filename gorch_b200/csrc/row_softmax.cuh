@@ -107,8 +107,8 @@ __device__ __forceinline__ void rs_unpack(const RowView<T>& rv, int v, const uin
 // Pass 1 over the vectors [v0, v1) of the row. Returns their maximum M (NaNs ignored; -Inf when
 // there is none) and S = sum exp(x - M) (0 when M is -Inf, NaN when a NaN was seen) to every thread.
 template <typename T>
-__device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, int v0, int v1, const uint4* ring, bu::Scratch& sc, int tid,
-                                           float& M, double& S) {
+__device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, int v0, int v1, bool primed, const RowView<T>* nrv, int nv0, int nv1,
+                                           const uint4* ring, bu::Scratch& sc, int tid, float& M, double& S) {
   constexpr int VEC = Elem<T>::VEC;
   const uint32_t ring_addr = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
   float m = -INFINITY;
@@ -139,23 +139,26 @@ __device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, int v0, int v1,
   // an SM's share of the bandwidth. So the row is staged through shared memory by asynchronous
   // 16-byte copies: a thread copies the vectors it will consume itself (no barrier, it only waits
   // for its own copy groups), RS_STAGES - 1 iterations (128 KB per SM) ahead of their use.
-  const int n_it = (v1 - v0 + RS_UNROLL * RS_NT - 1) / (RS_UNROLL * RS_NT);
-  auto issue = [&](int it) {
-    if (it < n_it) {
-      const int base = v0 + it * RS_UNROLL * RS_NT + tid;
-      const uint32_t dst = ring_addr + static_cast<uint32_t>(((it % RS_STAGES) * RS_UNROLL * RS_NT + tid) * 16);
+  // `primed`: the first RS_STAGES - 1 iterations of this range were issued already, at the end of
+  // the previous row's pass 1 (they arrived while that row's reduction and second pass ran). At the
+  // end of this pass the same is done for the range [nv0, nv1) of the CTA's next row, if any.
+  auto issue = [&](const RowView<T>& r, int a0, int a1, int it) {
+    const int base = a0 + it * RS_UNROLL * RS_NT + tid;
+    const uint32_t dst = ring_addr + static_cast<uint32_t>(((it % RS_STAGES) * RS_UNROLL * RS_NT + tid) * 16);
 #pragma unroll
-      for (int q = 0; q < RS_UNROLL; q++) {
-        if (base + q * RS_NT < v1)
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst + q * RS_NT * 16), "l"(rv.vbase + base + q * RS_NT) : "memory");
-      }
+    for (int q = 0; q < RS_UNROLL; q++) {
+      if (base + q * RS_NT < a1)                               // also false for every iteration past the range
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst + q * RS_NT * 16), "l"(r.vbase + base + q * RS_NT) : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
+  const int n_it = (v1 - v0 + RS_UNROLL * RS_NT - 1) / (RS_UNROLL * RS_NT);
+  if (!primed) {
 #pragma unroll
-  for (int st = 0; st < RS_STAGES - 1; st++) issue(st);
+    for (int st = 0; st < RS_STAGES - 1; st++) issue(rv, v0, v1, st);
+  }
   for (int it = 0; it < n_it; it++) {
-    issue(it + RS_STAGES - 1);
+    issue(rv, v0, v1, it + RS_STAGES - 1);
     asm volatile("cp.async.wait_group %0;" :: "n"(RS_STAGES - 1) : "memory");
     const int base = v0 + it * RS_UNROLL * RS_NT + tid;
     const uint4* src = ring + (it % RS_STAGES) * RS_UNROLL * RS_NT + tid;
@@ -164,7 +167,12 @@ __device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, int v0, int v1,
       if (base + q * RS_NT < v1) take(base + q * RS_NT, src[q * RS_NT]);
     }
   }
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  // every copy of this row has been waited for (the groups still pending are empty); this thread
+  // has consumed its part of every stage, so the next row's first stages can start now
+  if (nrv != nullptr) {
+#pragma unroll
+    for (int st = 0; st < RS_STAGES - 1; st++) issue(*nrv, nv0, nv1, st);
+  }
   M = okey_to_float(static_cast<uint32_t>(bu::max_u64<RS_NW>(static_cast<unsigned long long>(okey(m)), sc, tid)));
   // s NaN: NaN * anything stays NaN; m = -Inf with s = 0: the thread adds nothing
   float sa, sb;
@@ -260,12 +268,25 @@ __global__ void __launch_bounds__(RS_NT, 1) row_softmax_kernel(const RowSoftmaxA
   const int rank = static_cast<int>(cluster.block_rank());
   const int64_t ncl = gridDim.x / C;
   int k = 0;
+  bool primed = false;
+  // this CTA's vectors of a row: halves cut at a 128-byte line
+  auto range = [&](const RowView<T>& r, int& a0, int& a1) {
+    const int per = (C == 1) ? r.nvec : (((r.nvec + 1) / 2 + 7) & ~7);
+    a0 = min(rank * per, r.nvec);
+    a1 = min(a0 + per, r.nvec);
+  };
   for (int64_t row = blockIdx.x / C; row < A.B; row += ncl, k++) {
-    RowView<T> rv;
+    RowView<T> rv, nx;
     rv.init(x + row * A.row_stride, A.V);
-    // this CTA's vectors: halves cut at a 128-byte line
-    const int per = (C == 1) ? rv.nvec : (((rv.nvec + 1) / 2 + 7) & ~7);
-    const int v0 = min(rank * per, rv.nvec), v1 = min(v0 + per, rv.nvec);
+    int v0, v1, nv0 = 0, nv1 = 0;
+    range(rv, v0, v1);
+    // only the one-pass op runs its copies on into the next row: behind a second pass the early
+    // copies competed with that pass's L2 reads and stores and cost more than they saved (measured)
+    const bool has_next = A.mode == RS_CE_FWD && row + ncl < A.B;
+    if (has_next) {
+      nx.init(x + (row + ncl) * A.row_stride, A.V);
+      range(nx, nv0, nv1);
+    }
     if (A.mode == RS_CE_BWD) {
       // loss.go:128-141: dx = exp(x - lse) * scale, minus scale at the target
       const float lse = A.row_lse[row], scale = A.scale;
@@ -280,7 +301,8 @@ __global__ void __launch_bounds__(RS_NT, 1) row_softmax_kernel(const RowSoftmaxA
     }
     float M;
     double S;
-    rs_max_sum<T>(rv, v0, v1, ring, sc, tid, M, S);
+    rs_max_sum<T>(rv, v0, v1, primed, has_next ? &nx : nullptr, nv0, nv1, ring, sc, tid, M, S);
+    primed = has_next;
     if (C > 1) {
       if (tid == 0) { xch[k & 1].m = M; xch[k & 1].s = S; }
       cluster.sync();                                        // both halves published (release / acquire)
