@@ -1,4 +1,5 @@
-"""Times the row softmax / log-softmax / cross-entropy ops on one GPU.
+"""Times the row ops beside the sampling step on one GPU: softmax / log-softmax / cross-entropy
+and the tensor-level TopK / Multinomial.
 
     python -m gorch_b200.row_ops_bench                       # 512 x 151,936 f32, every op
     python -m gorch_b200.row_ops_bench --rows 1500 --vocab 168320 --op ce_fwd
@@ -8,7 +9,8 @@ Synthetic normal logits x 2 (the distribution of the reference's cross-entropy t
 ce_metal_test.go:44-54). Device time by CUDA events on the launching stream, median over the
 iterations, a buffer larger than L2 rewritten between launches. GB/s = algorithmic bytes / time:
 softmax and log-softmax read and write the tensor once, the cross-entropy forward reads it once,
-the backward reads it and writes f32. One JSON line per op."""
+the backward reads it and writes f32, TopK (k = 64; moe-style k = 8 with --topk 8) and Multinomial
+(over the softmax output, f32) read it once. One JSON line per op."""
 from __future__ import annotations
 
 import argparse
@@ -22,10 +24,13 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=512)
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
-    ap.add_argument("--op", default="all", choices=["all", "softmax", "log_softmax", "ce_fwd", "ce_bwd"])
+    ap.add_argument("--op", default="all", choices=["all", "softmax", "log_softmax", "ce_fwd", "ce_bwd", "topk", "multinomial"])
+    ap.add_argument("--topk", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
+
+    import ctypes as C
 
     import torch
 
@@ -56,6 +61,28 @@ def main() -> None:
         "ce_bwd": (lambda: row_ops.cross_entropy_bwd_ptrs(s, x.data_ptr(), code, B, V, V, tgt.data_ptr(), row_lse.data_ptr(),
                                                           1.0 / B, dx.data_ptr(), V), es + 4),
     }
+    k = a.topk
+    tk_val = torch.empty(B, k, device="cuda", dtype=torch.float32)
+    tk_idx = torch.empty(B, k, device="cuda", dtype=torch.int32)
+    probs = torch.softmax(x.float(), dim=1)
+    uni = torch.rand(B, device="cuda", dtype=torch.float64, generator=gen)
+    ids = torch.empty(B, device="cuda", dtype=torch.int32)
+    flags = torch.empty(B, device="cuda", dtype=torch.int32)
+
+    def run_topk():
+        err = C.c_void_p()
+        rc = s._lib.gorch_cuda_topk_dev(s._ctx, x.data_ptr(), code, B, V, V, k, tk_val.data_ptr(), tk_idx.data_ptr(),
+                                        flags.data_ptr(), C.byref(err))
+        sampling._check(s._lib, rc, err)
+
+    def run_multinomial():
+        err = C.c_void_p()
+        rc = s._lib.gorch_cuda_multinomial_dev(s._ctx, probs.data_ptr(), B, V, V, uni.data_ptr(), ids.data_ptr(),
+                                               flags.data_ptr(), C.byref(err))
+        sampling._check(s._lib, rc, err)
+
+    ops["topk"] = (run_topk, es)
+    ops["multinomial"] = (run_multinomial, 4)
     # the backward needs a logsumexp to read
     ops["ce_fwd"][0]()
     torch.cuda.synchronize()
