@@ -113,9 +113,30 @@ __device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, int v0, int v1,
   const uint32_t ring_addr = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
   float m = -INFINITY;
   rs_f2 s2 = rs_pk(0.0f, 0.0f);                                // two running sums (even and odd elements)
-  auto take = [&](int v, const uint4& raw) {
+  // The terms of the sum need no compensated exponential: a term's error from rounding t = d log2 e
+  // grows with |t| while the term shrinks as 2^t, and the errors of different terms are independent,
+  // so the sum stays within about 1e-7 relative. exp(-Inf) is 0 and a NaN stays NaN without a clamp.
+  auto accumulate = [&](const float* x) {
+    if (m > -INFINITY) {
+      const rs_f2 NM = rs_pk(-m, -m), L = rs_pk(1.44269502162933349609375f, 1.44269502162933349609375f);
+#pragma unroll
+      for (int c = 0; c < VEC; c += 2) {
+        float t0, t1;
+        rs_upk(rs_mul2(rs_add2(rs_pk(x[c], x[c + 1]), NM), L), t0, t1);
+        s2 = rs_add2(s2, rs_pk(rs_ex2(t0), rs_ex2(t1)));       // a NaN logit turns the sum NaN
+      }
+    } else {
+      // only -Inf and NaN so far: exp(-Inf - -Inf) must not poison the sum, a NaN logit must
+      float t = x[0];
+#pragma unroll
+      for (int c = 1; c < VEC; c++) t += x[c];
+      if (t != t) s2 = rs_pk(t, t);
+    }
+  };
+  auto take = [&](int v, const uint4& raw, bool interior) {
     float x[VEC];
-    rs_unpack<T>(rv, v, raw, x);
+    if (interior) Elem<T>::unpack(raw, x);
+    else rs_unpack<T>(rv, v, raw, x);
     float vm = x[0];
 #pragma unroll
     for (int c = 1; c < VEC; c++) vm = fmaxf(vm, x[c]);
@@ -124,16 +145,7 @@ __device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, int v0, int v1,
       s2 = rs_mul2(s2, rs_pk(f, f));
       m = vm;
     }
-    if (m > -INFINITY) {
-#pragma unroll
-      for (int c = 0; c < VEC; c += 2) s2 = rs_add2(s2, rs_exp2(x[c] - m, x[c + 1] - m));   // a NaN logit turns the sum NaN
-    } else {
-      // only -Inf and NaN so far: exp(-Inf - -Inf) must not poison the sum, a NaN logit must
-      float t = x[0];
-#pragma unroll
-      for (int c = 1; c < VEC; c++) t += x[c];
-      if (t != t) s2 = rs_pk(t, t);
-    }
+    accumulate(x);
   };
   // Registers could hold 64 KB of loads in flight per SM, which at HBM latency is about half of
   // an SM's share of the bandwidth. So the row is staged through shared memory by asynchronous
@@ -160,11 +172,18 @@ __device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, int v0, int v1,
   for (int it = 0; it < n_it; it++) {
     issue(rv, v0, v1, it + RS_STAGES - 1);
     asm volatile("cp.async.wait_group %0;" :: "n"(RS_STAGES - 1) : "memory");
-    const int base = v0 + it * RS_UNROLL * RS_NT + tid;
+    const int first = v0 + it * RS_UNROLL * RS_NT;
+    const int base = first + tid;
     const uint4* src = ring + (it % RS_STAGES) * RS_UNROLL * RS_NT + tid;
+    if (first > 0 && first + RS_UNROLL * RS_NT < min(v1, rv.nvec - 1)) {
+      // every vector of the iteration exists and is neither the row's first nor its last one
 #pragma unroll
-    for (int q = 0; q < RS_UNROLL; q++) {
-      if (base + q * RS_NT < v1) take(base + q * RS_NT, src[q * RS_NT]);
+      for (int q = 0; q < RS_UNROLL; q++) take(base + q * RS_NT, src[q * RS_NT], true);
+    } else {
+#pragma unroll
+      for (int q = 0; q < RS_UNROLL; q++) {
+        if (base + q * RS_NT < v1) take(base + q * RS_NT, src[q * RS_NT], false);
+      }
     }
   }
   // every copy of this row has been waited for (the groups still pending are empty); this thread
