@@ -224,8 +224,10 @@ __device__ __forceinline__ uint4 mask_edges(const RowView<T>& rv, int v, uint4 r
 // ---------------------------------------------------------------------------
 template <typename T>
 __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned char* dyn, bu::Scratch& sc,
-                           uint32_t* s_sel, int* s_bc, double* s_bcd, int* s_cnt, float* s_thr, int* s_flag) {
+                           uint32_t* s_sel, int* s_bc, double* s_bcd, int* s_cnt, float* s_thr, int* s_flag,
+                           const bool allow_tight, bool& redo) {
   const KernelArgs& A = BA.k;
+  redo = false;
   const int tid = threadIdx.x;
   const int V = A.V;
   constexpr int VEC = Elem<T>::VEC;
@@ -404,17 +406,43 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   // r-th largest logit of the warm-up chunk, with r chosen so that about four times top_k logits
   // of the whole row are expected above it. If the row ends with at least top_k candidates, its
   // top_k-th largest is among them and nothing was lost; if not (the chunk was not typical of
-  // the row), the row is redone by the single-CTA kernel. Not used for vocab-sharded slices.
+  // the row), the row is redone: by the single-CTA kernel when it is a sampling row, by this kernel
+  // without the estimate (`redo`) when it is a TopK row or a vocab-sharded slice, which that kernel
+  // does not serve.
   bool tight = false;
-  if (!A.vs_records && A.tk_k == 0 && rv.nvec > warm) {
+  if (allow_tight && rv.nvec > warm) {
     const int cnt0 = *s_cnt;
     const long long welems = static_cast<long long>(warm) * VEC;
     const int r = static_cast<int>((4ll * topk * welems + V - 1) / V) + 4;
     if (r < cnt0) {                                          // uniform
       const uint32_t rkey = bu::select_kth<N_NT>(cand, cnt0, r, s_sel, s_bc, tid);
-      const float t = okey_to_float(rkey);
-      if (t > thr) { thr = t; tight = true; }
+      // lower edge of its class of equal quotients x / T, like every threshold here: whatever ties
+      // with the k-th largest after the division is then collected too
+      const float t = quotient_class_floor(okey_to_float(rkey), Tm);
       __syncthreads();
+      if (t > thr) {
+        // The list keeps only what passes the estimate, so that the count at the end of the row
+        // says whether top_k logits passed it (entries below it would hide a failed estimate, and
+        // a later prune would take its k-th largest from them).
+        uint2* tmp = reinterpret_cast<uint2*>(chunk);        // 2048 entries; the warm-up vectors are used up
+        if (tid == 0) *s_cnt = 0;
+        __syncthreads();
+        for (int j = tid; j < cnt0; j += N_NT) {
+          const uint2 e = cand[j];
+          if (__uint_as_float(e.x) >= t) { const int slot = atomicAdd(s_cnt, 1); if (slot < 2048) tmp[slot] = e; }
+        }
+        __syncthreads();
+        const int kept = *s_cnt;
+        __syncthreads();
+        if (kept <= 2048) {
+          for (int j = tid; j < kept; j += N_NT) cand[j] = tmp[j];
+          thr = t;
+          tight = true;
+        } else if (tid == 0) {
+          *s_cnt = cnt0;                                     // a long run of ties at the estimate: go on without it
+        }
+        __syncthreads();
+      }
     }
   }
   stamp(0);
@@ -514,7 +542,10 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   dbg.cycles[5] = static_cast<uint32_t>(*s_cnt);
   int nk = 0;
   if (!giveup && *s_cnt > N_CAP) giveup = true;
-  if (!giveup && tight && *s_cnt < topk) giveup = true;      // the estimated threshold was too tight for this row
+  if (!giveup && tight && *s_cnt < topk) {                   // the estimated threshold was too tight for this row
+    if (A.vs_records || A.tk_k > 0) { redo = true; return; } // uniform: *s_cnt is read after the loop's last barrier
+    giveup = true;
+  }
   if (!giveup) {
     nk = prune(*s_cnt);
     if (nk > KEEP_MAX) giveup = true;                        // long run of ties at the threshold
@@ -600,7 +631,13 @@ __global__ void __launch_bounds__(N_NT, 4) narrow_rows_kernel(BatchArgs BA) {
     __syncthreads();
     const int row = s_row;
     if (row < 0) break;
-    narrow_row<T>(BA, row, dyn, sc, s_sel, s_bc, s_bcd, &s_cnt, &s_thr, &s_flag);
+    bool redo, allow_tight = true;
+    for (;;) {                                               // at most twice: the second time without the estimate
+      narrow_row<T>(BA, row, dyn, sc, s_sel, s_bc, s_bcd, &s_cnt, &s_thr, &s_flag, allow_tight, redo);
+      if (!redo) break;
+      allow_tight = false;
+      __syncthreads();
+    }
   }
 }
 

@@ -1,0 +1,43 @@
+"""Rows whose largest logits sit at the start of the row (low token ids, as frequent tokens do in
+a BPE vocabulary), or whose start is unusually low: the streaming kernels guess a threshold from
+the first 4096 logits, and a guess that is too high must be noticed and the row done again.
+Checked through the C ABI against the oracle with the usual gates (tests/parity.py), every kernel
+variant, f32 and bf16, top-k with and without top-p, greedy."""
+import numpy as np
+import pytest
+
+from gorch_b200.config import CFG_DTYPE
+
+from tests.test_gpu_parity import run_both
+
+pytestmark = pytest.mark.gpu
+
+
+def _rows(V, seed):
+    rng = np.random.Generator(np.random.Philox(key=seed))
+    B = 24
+    x = (rng.standard_normal((B, V)) * 2.0).astype(np.float32)
+    x[0:6, :20] += 30.0                          # 20 dominant logits at the very start
+    x[6:10, :300] += 6.0                         # a few hundred raised ones
+    x[10:12, :4096] -= 50.0                      # a start far below the rest
+    x[12] = np.sort(x[12])[::-1]                 # descending row
+    x[13] = np.sort(x[13])                       # ascending row
+    x[14, :4096] = np.sort(x[14, :4096])[::-1]
+    x[15, 100:164] = 25.0                        # exactly 64 equal dominant logits
+    cfgs = np.zeros(B, dtype=CFG_DTYPE)
+    kinds = [(0.8, 40, 0.0, 0), (1.0, 64, 0.95, 1), (0.7, 64, 0.9, 0), (1.3, 200, 0.0, 0), (0.0, 0, 0.0, 0), (1.0, 5, 0.5, 1)]
+    for b in range(B):
+        cfgs[b] = kinds[b % len(kinds)]
+    return x, cfgs, rng.random(B)
+
+
+@pytest.mark.parametrize("V", [50257, 151936])
+def test_front_loaded_rows_f32(sampler, oracle, V):
+    x, cfgs, uniforms = _rows(V, 900 + V)
+    run_both(sampler, oracle, x, cfgs, uniforms, allow_tie_cut=True)
+
+
+def test_front_loaded_rows_bf16(sampler, oracle):
+    x, cfgs, uniforms = _rows(151936, 901)
+    bits = oracle.f32_to_bf16_bits(x)
+    run_both(sampler, oracle, bits, cfgs, uniforms, allow_tie_cut=True)

@@ -82,3 +82,25 @@ def test_multinomial_nan_row_falls_through(sampler, oracle):
     u = np.array([0.5, 0.5])
     ids, flags = sampler.multinomial(p, u)
     assert ids.tolist() == oracle.multinomial(p, u).tolist()
+
+
+def test_topk_rows_whose_start_is_not_typical(sampler, oracle):
+    """The streaming kernel guesses a threshold from the first 4096 logits of a row. Rows whose
+    largest values all sit there make the guess too high (fewer than k logits pass it) and are
+    done again without it; rows whose start is unusually low make it too generous. Both must
+    still return the exact top k."""
+    rng = np.random.Generator(np.random.Philox(key=77))
+    B, V, k = 12, 151936, 64
+    x = (rng.standard_normal((B, V)) * 2.0).astype(np.float32)
+    x[0:4, :20] += 100.0                      # 20 huge logits at the start, k = 64 wanted
+    x[4:6, :4096] -= 50.0                     # a start far below the rest
+    x[6, :4096] = np.sort(x[6, :4096])[::-1]  # descending start
+    x[7] = np.sort(x[7])[::-1]                # whole row descending
+    x[8] = np.sort(x[8])                      # whole row ascending
+    vals, idx = sampler.topk(x, k)
+    wv, wi = oracle.topk(x, k)
+    assert np.array_equal(vals, wv) and np.array_equal(idx.astype(np.int64), wi)
+    bits = oracle.f32_to_bf16_bits(x)
+    vals, idx = sampler.topk(bits, k)
+    wv, wi = oracle.topk(oracle.bf16_bits_to_f32(bits), k)
+    assert np.array_equal(vals, wv) and np.array_equal(idx.astype(np.int64), wi)

@@ -79,3 +79,22 @@ def test_rows_without_top_k_are_flagged(sampler):
     cfgs[1] = (1.0, 200, 0.9, 1)                       # above the record capacity
     ids, flags = run_sharded(sampler, logits, cfgs, np.full(B, 0.5), 2)
     assert ids.tolist() == [-1, -1] and np.all(flags & FLAG_INTERNAL)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_slices_whose_start_is_not_typical(sampler, oracle, world):
+    """A slice whose largest logits all sit in its first 4096 columns defeats the local pass's
+    estimated threshold (fewer than top_k logits pass it); the slice is then done again without
+    the estimate and the merged result must not change."""
+    rng = np.random.Generator(np.random.Philox(key=78 + world))
+    B, V = 10, 151936
+    logits = (rng.standard_normal((B, V)) * 2.0).astype(np.float32)
+    for r in range(world):
+        lo, _ = workloads.shard_vocab(V, r, world)
+        logits[0:5, lo:lo + 12] += 60.0 + r     # a dozen huge logits at the start of every slice
+    logits[5:7, :4096] -= 40.0
+    cfgs = np.zeros(B, dtype=CFG_DTYPE)
+    for b in range(B):
+        cfgs[b] = (0.9, 64, 0.95, 1) if b % 2 else (1.0, 40, 0.0, 0)
+    uniforms = rng.random(B)
+    check(sampler, oracle, logits, cfgs, uniforms, world)
