@@ -2,7 +2,8 @@
 a BPE vocabulary), or whose start is unusually low: the streaming kernels guess a threshold from
 the first 4096 logits, and a guess that is too high must be noticed and the row done again.
 Checked through the C ABI against the oracle with the usual gates (tests/parity.py), every kernel
-variant, f32 and bf16, top-k with and without top-p, greedy."""
+variant, f32 and bf16, top-k with and without top-p, greedy, and top-k off (the wide kernel's
+sampled anchor and bucket scale meet the same rows)."""
 import numpy as np
 import pytest
 
@@ -15,7 +16,7 @@ pytestmark = pytest.mark.gpu
 
 def _rows(V, seed):
     rng = np.random.Generator(np.random.Philox(key=seed))
-    B = 24
+    B = 36
     x = (rng.standard_normal((B, V)) * 2.0).astype(np.float32)
     x[0:6, :20] += 30.0                          # 20 dominant logits at the very start
     x[6:10, :300] += 6.0                         # a few hundred raised ones
@@ -24,10 +25,19 @@ def _rows(V, seed):
     x[13] = np.sort(x[13])                       # ascending row
     x[14, :4096] = np.sort(x[14, :4096])[::-1]
     x[15, 100:164] = 25.0                        # exactly 64 equal dominant logits
+    x[16:20, 5000:5020] += 30.0                  # dominant logits where no warp's first step looks
+    x[20:22, V // 2: V // 2 + 3] += 45.0         # three far outliers in the middle
+    x[22, -40:] += 25.0                          # dominant logits at the very end
+    x[23, :] = np.float32(1.5); x[23, 7] = 9.0   # flat row with one peak
     cfgs = np.zeros(B, dtype=CFG_DTYPE)
-    kinds = [(0.8, 40, 0.0, 0), (1.0, 64, 0.95, 1), (0.7, 64, 0.9, 0), (1.3, 200, 0.0, 0), (0.0, 0, 0.0, 0), (1.0, 5, 0.5, 1)]
+    kinds = [(0.8, 40, 0.0, 0), (1.0, 64, 0.95, 1), (0.7, 64, 0.9, 0), (1.3, 200, 0.0, 0), (0.0, 0, 0.0, 0), (1.0, 5, 0.5, 1),
+             (1.0, 0, 0.9, 0), (1.0, 0, 0.99, 1), (0.8, 0, 0.0, 0), (1.2, 0, 0.6, 1)]     # the last four: top-k off
     for b in range(B):
         cfgs[b] = kinds[b % len(kinds)]
+    # rows 24..35 repeat the shapes of rows 0..23 that the top-k-off kinds did not meet
+    x[24:36] = x[[0, 1, 6, 10, 12, 13, 15, 16, 17, 20, 22, 23]]
+    for b in range(24, 36):
+        cfgs[b] = kinds[6 + b % 4]
     return x, cfgs, rng.random(B)
 
 

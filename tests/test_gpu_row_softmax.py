@@ -167,3 +167,20 @@ def test_full_vocabulary_batch_properties(_sampler_session):
     assert np.abs(dx.astype(np.float64).sum(axis=1)).max() <= 1e-5
     dx[np.arange(B), tgt] += 1.0
     assert np.allclose(dx, sm, rtol=1e-5, atol=2e-7)                     # the target entry went through p - 1 + 1
+
+
+def test_sorted_rows(_sampler_session, oracle):
+    """Ascending rows make every thread's running maximum grow at each vector (the sums are
+    rescaled every time), descending ones never: both must give the same values as a shuffled row."""
+    s = _sampler_session
+    rng = np.random.default_rng(6)
+    base = (rng.standard_normal(151936) * 3.0).astype(np.float32)
+    x = np.stack([np.sort(base), np.sort(base)[::-1], base, np.sort(base) * 8.0])
+    tgt = np.array([5, 5, 5, 151935], dtype=np.int32)
+    want_sm, want_ls = _f64_softmax(x)
+    assert np.allclose(row_ops.softmax(s, x), want_sm, rtol=2e-6, atol=1e-37)
+    ls = row_ops.softmax(s, x, log=True)
+    assert np.abs(ls - want_ls).max() <= 2e-6 * np.abs(want_ls).max()
+    _, row_loss, row_lse = row_ops.cross_entropy(s, x, tgt)
+    _, o_loss, o_lse = oracle.cross_entropy_fwd(x, tgt)
+    assert np.allclose(row_lse, o_lse, rtol=1e-5) and np.allclose(row_loss, o_loss, rtol=1e-5, atol=1e-4)
