@@ -141,7 +141,9 @@ __device__ __forceinline__ void rs_max_sum(const RowView<T>& rv, int v0, int v1,
 #pragma unroll
     for (int c = 1; c < VEC; c++) vm = fmaxf(vm, x[c]);
     if (vm > m) {                                              // m = -Inf before: the sums are 0 (or NaN) and stay so
-      const float f = rs_exp1(m - vm);
+      // the accurate exponential here: in a row that keeps growing (sorted logits) the sums are
+      // rescaled at every vector, and the error of a cheaper one would add up over those steps
+      const float f = expf(m - vm);
       s2 = rs_mul2(s2, rs_pk(f, f));
       m = vm;
     }
