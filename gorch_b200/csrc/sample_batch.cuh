@@ -335,8 +335,12 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
       if (v < warm) { r[g] = load_masked(rv, v, xmax, xmin, nan_seen); chunk[v] = r[g]; }
     }
   }
-  // thr: lower edge of the 16-bit key bin holding the k-th largest per-thread maximum
-  float thr = -INFINITY;
+  // thr: lower edge of the 16-bit key bin holding the k-th largest per-thread maximum. Never
+  // -Inf: a -Inf logit has probability 0 whether or not top-k keeps it, so it is never a candidate
+  // (a masked vocabulary would otherwise flood the list with ties at -Inf). A row with fewer than
+  // top_k finite logits simply ends with fewer candidates.
+  constexpr float LOWEST = -3.402823466e+38f;
+  float thr = LOWEST;
   {
     uint32_t prefix = 0, mask = 0;
     int need = topk;
@@ -384,7 +388,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     if (have_thr) {
       if (tid == 0) *s_thr = quotient_class_floor(okey_to_float(prefix), Tm);
       __syncthreads();
-      thr = *s_thr;
+      thr = fmaxf(*s_thr, LOWEST);
     }
   }
   // candidates of the warm-up chunk
@@ -453,7 +457,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     const uint32_t kkey = bu::select_kth<N_NT>(cand, cnt, topk, s_sel, s_bc, tid);
     if (tid == 0) { *s_thr = quotient_class_floor(okey_to_float(kkey), Tm); *s_cnt = 0; }
     __syncthreads();
-    thr = *s_thr;
+    thr = *s_thr;                                            // finite: the list holds finite logits only
     uint2* tmp = reinterpret_cast<uint2*>(chunk);            // 2048 entries
     for (int j = tid; j < cnt; j += N_NT) {
       const uint2 e = cand[j];
@@ -561,7 +565,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     // NaNs order last here (the reference's comparator leaves them unspecified).
     float* ov = A.tk_values + row_id * static_cast<int64_t>(topk);
     int32_t* oi = A.tk_indices + row_id * static_cast<int64_t>(topk);
-    if (giveup) {                                            // more than 512 logits tie at the k-th value
+    if (giveup || nk < topk) {                               // more than 512 logits tie at the k-th value, or it is -Inf
       for (int j = tid; j < topk; j += N_NT) { ov[j] = __int_as_float(0x7fc00000); oi[j] = -1; }
       if (tid == 0 && A.out_flags) A.out_flags[row_id] = FLAG_INTERNAL;
       return;
@@ -581,21 +585,23 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   if (A.vs_records) {                                        // vocab-sharded: hand the list over instead of drawing
     VsRecord& rec = static_cast<VsRecord*>(A.vs_records)[row_id];
     uint32_t fl = 0u;
-    if (anynan || !(fabsf(m) < INFINITY)) fl |= VS_NONFINITE;
+    // a slice of -Inf only (a masked part of the vocabulary) is no verdict on the row: the merge
+    // decides that from all slices; a slice given up early was not read to its end
+    if (!giveup && (anynan || m == INFINITY || m != m)) fl |= VS_NONFINITE;
     if (giveup || nk > VS_CAND) fl |= VS_OVERFLOW;
     const int nout = (fl == 0u) ? nk : 0;
     if (tid == 0) { rec.xmax = xmax; rec.n = nout; rec.flags = fl; rec.pad = 0; }
     for (int j = tid; j < nout; j += N_NT) rec.cand[j] = make_uint2(cand[j].x, cand[j].y + static_cast<uint32_t>(A.vs_col_offset));
     return;
   }
+  if (giveup) {                                              // before any verdict on the row: it may not have been read to its end
+    if (tid == 0) hand_to_single(BA, row_id);
+    return;
+  }
   if (anynan || !(fabsf(m) < INFINITY)) {
     fill_probs_row(QNAN);
     dbg.sum_exp = QNAN;
     write_row(V - 1, FLAG_NONFINITE | FLAG_FALLBACK);
-    return;
-  }
-  if (giveup) {
-    if (tid == 0) hand_to_single(BA, row_id);
     return;
   }
   stamp(2);

@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(VM_NT, 4) vocab_merge_kernel(MergeArgs M) {
     const int cnt = s_cnt;
     const uint32_t vfl = fl_loc;                             // uniform: every thread read every record header
     if (vfl & VS_BAD_CFG) { write_row(-1, FLAG_BAD_CFG); continue; }
-    if ((vfl & (VS_OVERFLOW | VS_UNSUPPORTED)) || cnt == 0) { write_row(-1, FLAG_INTERNAL); continue; }
+    if (vfl & (VS_OVERFLOW | VS_UNSUPPORTED)) { write_row(-1, FLAG_INTERNAL); continue; }
     // ---- greedy (generate.go:134-144): largest logit, lowest index; a NaN at index 0 is never beaten
     if (Tm == 0.0f) {
       unsigned long long best = 0ull;
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(VM_NT, 4) vocab_merge_kernel(MergeArgs M) {
       }
       best = bu::max_u64<NW>(best, sc, tid);
       int id = static_cast<int>(~static_cast<uint32_t>(best & 0xffffffffull));
-      if (vfl & VS_NAN_AT_0) id = 0;
+      if ((vfl & VS_NAN_AT_0) || cnt == 0) id = 0;           // no champion anywhere: index 0 is never beaten
       dbg.kept = 1;
       write_row(id, 0u);
       continue;
@@ -97,7 +97,8 @@ __global__ void __launch_bounds__(VM_NT, 4) vocab_merge_kernel(MergeArgs M) {
     const float m = scale_t(xmax, Tm);
     dbg.max_scaled = m;
     // A NaN anywhere, or an infinite maximum: the walk of generate.go:231-239 falls through
-    if ((vfl & VS_NONFINITE) || !(fabsf(m) < INFINITY)) {
+    // (no candidate in any slice: the row holds no finite logit at all)
+    if ((vfl & VS_NONFINITE) || cnt == 0 || !(fabsf(m) < INFINITY)) {
       dbg.sum_exp = __longlong_as_double(0x7ff8000000000000ll);
       write_row(A.V - 1, FLAG_NONFINITE | FLAG_FALLBACK);
       continue;

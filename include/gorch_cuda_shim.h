@@ -200,7 +200,8 @@ int gorch_cuda_vocab_merge_dev(GorchCudaCtxRef ctx, const void* all_records, int
  * TopK (index_ops.go:153-190): the k largest of each row of x [B,V] (f32, or bf16 upcast), values
  * [B,k] descending and their indices [B,k]; equal values by ascending index (upstream's sort is
  * unstable, so that order is unspecified there); NaNs order last. 1 <= k <= min(V, 256). A row with
- * more than 512 logits tied at its k-th value gets indices -1 and GORCH_FLAG_INTERNAL in out_flags
+ * more than 512 logits tied at its k-th value (which includes a row with fewer than k logits above
+ * -Inf) gets indices -1 and GORCH_FLAG_INTERNAL in out_flags
  * (may be NULL).
  * Multinomial (index_ops.go:203-227): out_ids[b] = first j with uniforms[b] < sum_{i<=j} probs[b,i]
  * (f64 running sum over f32 probabilities), else V-1 (GORCH_FLAG_FALLBACK). The sum is formed in a

@@ -51,3 +51,32 @@ def test_front_loaded_rows_bf16(sampler, oracle):
     x, cfgs, uniforms = _rows(151936, 901)
     bits = oracle.f32_to_bf16_bits(x)
     run_both(sampler, oracle, bits, cfgs, uniforms, allow_tie_cut=True)
+
+
+@pytest.mark.parametrize("V", [50257, 151936])
+def test_masked_vocabulary_rows(sampler, oracle, V):
+    """Large parts of the vocabulary masked with -Inf (constrained decoding): the start of the
+    row, most of it at random, all but fewer entries than top_k, all but the last one."""
+    rng = np.random.Generator(np.random.Philox(key=950 + V))
+    kinds = [(0.8, 40, 0.0, 0), (1.0, 64, 0.95, 1), (0.0, 0, 0.0, 0), (1.0, 0, 0.9, 0), (1.0, 0, 0.99, 1), (0.7, 0, 0.0, 0)]
+    shapes = 5
+    B = shapes * len(kinds)
+    x = (rng.standard_normal((B, V)) * 2.0).astype(np.float32)
+    cfgs = np.zeros(B, dtype=CFG_DTYPE)
+    for b in range(B):
+        cfgs[b] = kinds[b // shapes]
+        shape = b % shapes
+        if shape == 0:
+            x[b, :8192] = -np.inf
+        elif shape == 1:
+            x[b, rng.random(V) < 0.9] = -np.inf
+        elif shape == 2:
+            keep = rng.choice(V, size=30, replace=False)
+            row = np.full(V, -np.inf, dtype=np.float32)
+            row[keep] = x[b, keep]
+            x[b] = row
+        elif shape == 3:
+            x[b, :-1] = -np.inf
+        else:
+            x[b, 4096:] = -np.inf
+    run_both(sampler, oracle, x, cfgs, rng.random(B), allow_tie_cut=True)

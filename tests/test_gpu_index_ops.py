@@ -104,3 +104,19 @@ def test_topk_rows_whose_start_is_not_typical(sampler, oracle):
     vals, idx = sampler.topk(bits, k)
     wv, wi = oracle.topk(oracle.bf16_bits_to_f32(bits), k)
     assert np.array_equal(vals, wv) and np.array_equal(idx.astype(np.int64), wi)
+
+
+def test_topk_masked_rows(sampler, oracle):
+    """-Inf over the start of the row or most of it does not disturb the k largest; a row with
+    fewer than k finite logits has its k-th value at -Inf among thousands of ties and is flagged."""
+    rng = np.random.Generator(np.random.Philox(key=79))
+    B, V, k = 6, 151936, 64
+    x = (rng.standard_normal((B, V)) * 2.0).astype(np.float32)
+    x[0:2, :8192] = -np.inf
+    x[2:4][:, rng.random(V) < 0.95] = -np.inf
+    x[4, 4096:] = -np.inf
+    x[5, 30:] = -np.inf                                   # 30 finite logits, k = 64
+    vals, idx = sampler.topk(x, k)
+    wv, wi = oracle.topk(x, k)
+    assert np.array_equal(vals[:5], wv[:5]) and np.array_equal(idx[:5].astype(np.int64), wi[:5])
+    assert (idx[5] == -1).all()

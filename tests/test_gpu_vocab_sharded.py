@@ -98,3 +98,23 @@ def test_slices_whose_start_is_not_typical(sampler, oracle, world):
         cfgs[b] = (0.9, 64, 0.95, 1) if b % 2 else (1.0, 40, 0.0, 0)
     uniforms = rng.random(B)
     check(sampler, oracle, logits, cfgs, uniforms, world)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_masked_slices(sampler, oracle, world):
+    """-Inf over a whole slice, over the start of every slice, over most of the row: a masked
+    slice is no verdict on the row, and -Inf logits never crowd out the candidates."""
+    rng = np.random.Generator(np.random.Philox(key=88 + world))
+    B, V = 12, 151936
+    logits = (rng.standard_normal((B, V)) * 2.0).astype(np.float32)
+    lo1, hi1 = workloads.shard_vocab(V, 1, world)
+    logits[0:3, lo1:hi1] = -np.inf                     # slice 1 fully masked
+    for r in range(world):
+        lo, _ = workloads.shard_vocab(V, r, world)
+        logits[3:6, lo:lo + 8192] = -np.inf            # the start of every slice masked
+    logits[6:9][:, rng.random(V) < 0.9] = -np.inf      # most of the row masked
+    logits[9, 100:] = -np.inf                          # only slice 0 has anything
+    cfgs = np.zeros(B, dtype=CFG_DTYPE)
+    for b in range(B):
+        cfgs[b] = [(0.9, 64, 0.95, 1), (1.0, 40, 0.0, 0), (0.0, 0, 0.0, 0)][b % 3]
+    check(sampler, oracle, logits, cfgs, rng.random(B), world)
