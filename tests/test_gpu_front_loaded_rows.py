@@ -80,3 +80,31 @@ def test_masked_vocabulary_rows(sampler, oracle, V):
         else:
             x[b, 4096:] = -np.inf
     run_both(sampler, oracle, x, cfgs, rng.random(B), allow_tie_cut=True)
+
+
+@pytest.mark.parametrize("V", [50257, 151936])
+def test_quantised_peaked_and_wide_range_rows(sampler, oracle, V):
+    """Distributions the iid configs never produce: logits quantised to quarters (every value
+    shared by hundreds of tokens, so every cut falls inside a run of ties), one dominant token,
+    a range of hundreds of units (most exponentials underflow), very small and very large
+    temperatures. (No flat row under mode A's top-p: upstream's trimming loop, which the oracle
+    restates, is quadratic in the number of tokens it removes and takes minutes there.)"""
+    rng = np.random.Generator(np.random.Philox(key=970 + V))
+    kinds = [(0.8, 40, 0.0, 0), (1.0, 64, 0.95, 1), (1.0, 0, 0.9, 0), (1.0, 0, 0.99, 1), (0.01, 0, 0.9, 1),
+             (100.0, 0, 0.5, 1), (0.05, 50, 0.9, 0), (50.0, 200, 0.99, 1)]
+    shapes = 4
+    B = shapes * len(kinds)
+    x = (rng.standard_normal((B, V)) * 2.0).astype(np.float32)
+    cfgs = np.zeros(B, dtype=CFG_DTYPE)
+    for b in range(B):
+        cfgs[b] = kinds[b // shapes]
+        shape = b % shapes
+        if shape == 0:
+            x[b] = np.round(x[b] * 4.0) / 4.0
+        elif shape == 1:
+            x[b, int(rng.integers(0, V))] += 100.0
+        elif shape == 2:
+            x[b] *= 40.0
+        else:
+            x[b] = np.round(x[b]) + np.float32(1e-3) * (np.arange(V) % 3 == 0)
+    run_both(sampler, oracle, x, cfgs, rng.random(B), allow_tie_cut=True)
