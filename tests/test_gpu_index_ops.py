@@ -120,3 +120,41 @@ def test_topk_masked_rows(sampler, oracle):
     wv, wi = oracle.topk(x, k)
     assert np.array_equal(vals[:5], wv[:5]) and np.array_equal(idx[:5].astype(np.int64), wi[:5])
     assert (idx[5] == -1).all()
+
+
+@pytest.mark.parametrize("V", [50257, 151936])
+def test_multinomial_concentrated_rows(sampler, oracle, V):
+    """All the mass at the start, at the end, in one token, in long blocks separated by zeros,
+    unnormalised rows (sums of 0.3 and of 40), with uniforms at 0, tiny, mid and next to 1."""
+    rng = np.random.Generator(np.random.Philox(key=81 + V))
+    shapes, us = 7, [0.0, 1e-12, 0.25, 0.5, 0.75, 1.0 - 1e-9]
+    B = shapes * len(us)
+    p = np.zeros((B, V), dtype=np.float32)
+    u = np.zeros(B)
+    for b in range(B):
+        shape, u[b] = b % shapes, us[b // shapes]
+        if shape == 0:
+            p[b, 0] = 1.0
+        elif shape == 1:
+            p[b, V - 1] = 1.0
+        elif shape == 2:
+            p[b, :10] = 0.0999
+            p[b, 10:] = 0.001 / (V - 10)
+        elif shape == 3:
+            p[b, -3:] = (0.2, 0.3, 0.5)
+        elif shape == 4:
+            p[b, 5000:9000] = 1.0 / 8000
+            p[b, V - 9000:V - 5000] = 1.0 / 8000
+        elif shape == 5:
+            p[b] = (rng.random(V) * 0.6 / V).astype(np.float32)         # sums to about 0.3
+        else:
+            p[b] = (rng.random(V) * 80.0 / V).astype(np.float32)        # sums to about 40
+    ids, flags = sampler.multinomial(p, u)
+    want = oracle.multinomial(p, u)
+    excused = (flags & FLAG_BOUNDARY) != 0
+    assert np.array_equal(ids[~excused].astype(np.int64), want[~excused])
+    # uniforms at 0 and next to the total sit on an edge of their interval by construction: those
+    # rows are flagged, and must still land on a token that has probability, or fall through
+    ok = (flags & FLAG_FALLBACK) != 0
+    assert np.all((p[np.arange(B), ids] > 0) | ok)
+    assert (~excused).sum() >= B // 2
