@@ -6,7 +6,7 @@ driven by the CPU sampling oracle. Token ids, lengths and end reasons are intege
 import numpy as np
 import pytest
 
-from gorch_b200.config import CFG_DTYPE, DTYPE_F32, MODE_A, MODE_B, GenerateConfig, QwenGenerateConfig
+from gorch_b200.config import CFG_DTYPE, DTYPE_BF16, DTYPE_F32, MODE_A, MODE_B, GenerateConfig, QwenGenerateConfig
 from gorch_b200.generate import (GEN_ERROR, GEN_LIVE, LOOP_CACHED, LOOP_QWEN, LOOP_UNCACHED,
                                  DeviceGenerateState, generate_on_device)
 from gorch_b200.sampling import GorchCudaError, generate_with_config, qwen_generate
@@ -149,9 +149,11 @@ class _DevInts:
 
 class DeviceTableModel:
     def __init__(self, table, loop):
+        """table: float32, or uint16 bf16 bit patterns (given to torch as int16)."""
         import torch
         self.torch = torch
-        self.t = torch.from_numpy(table).cuda()
+        self.code = DTYPE_BF16 if table.dtype == np.uint16 else DTYPE_F32
+        self.t = torch.from_numpy(table.view(np.int16) if table.dtype == np.uint16 else table).cuda()
         self.loop = loop
         self.logits = None
 
@@ -166,7 +168,7 @@ class DeviceTableModel:
         else:
             pos = self._ints(st.cache_len_ptr, st.B) - 1
         self.logits = self.t[(7 * tok + 13 * pos) % M_ROWS].contiguous()
-        return self.logits.data_ptr(), DTYPE_F32, V_TAB, V_TAB
+        return self.logits.data_ptr(), self.code, V_TAB, V_TAB
 
     prefill_dev = forward_dev
 
@@ -182,13 +184,18 @@ class OracleSampler:
 
 
 @pytest.mark.parametrize("loop", [LOOP_UNCACHED, LOOP_CACHED, LOOP_QWEN])
-def test_batched_generation_on_device_matches_the_host_loops(_sampler_session, oracle, loop):
+@pytest.mark.parametrize("B,bf16", [(48, False), (200, True)])
+def test_batched_generation_on_device_matches_the_host_loops(_sampler_session, oracle, loop, B, bf16):
+    """48 sequences of f32 logits (the small-batch kernels) and 200 of bf16 logits (the batch
+    kernels), every sampling kind, each of the three loops."""
     import torch
     s = _sampler_session
     s.set_kernel_variant(0, 0)
     table = _table()
-    rng = np.random.default_rng(40 + loop)
-    B, max_new = 48, 14
+    if bf16:
+        table = oracle.f32_to_bf16_bits(table)
+    rng = np.random.default_rng(40 + loop + B)
+    max_new = 14
     prompts = [rng.integers(0, V_TAB, int(rng.integers(1, 30 if loop != LOOP_QWEN else 12))).tolist() for _ in range(B)]
     cfgs = np.zeros(B, dtype=CFG_DTYPE)
     mode = MODE_B if loop == LOOP_QWEN else MODE_A
@@ -205,7 +212,8 @@ def test_batched_generation_on_device_matches_the_host_loops(_sampler_session, o
     finally:
         torch.cuda.synchronize()
         s.set_stream(None)
-    host = HostQwenTableModel(table) if loop == LOOP_QWEN else HostTableModel(table)
+    host_table = oracle.bf16_bits_to_f32(table) if bf16 else table          # the upcast of tensor.go:96-99
+    host = HostQwenTableModel(host_table) if loop == LOOP_QWEN else HostTableModel(host_table)
     smp = OracleSampler(oracle)
     ended = set()
     for b in range(B):
