@@ -3,13 +3,19 @@
 one batch of synthetic logits.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4] [--impl reference]
+                  [--no-configs] [--no-ops] [--op NAME --op-rows R --op-vocab V]
 
 Own arm: `value` is rows/s with the batch resident in HBM (device-pointer
 entry point, CUDA events on the launching stream); `e2e` is the same metric
 through the host-pointer C-ABI call with pinned host buffers, copies inside
-the timed region. `--impl reference` times the CPU restatement of the
-reference's routines on the host cores. Under torchrun every rank runs its own
-rows (no collective on the data path); rank 0 prints one JSON line.
+the timed region. After the timed region rank 0 compares the timed call's ids
+with the CPU oracle and reports the counts under `parity`. At N=1 the same JSON
+line also carries `configs` (every other BASELINE config, 20 timed steps each,
+with its own parity counts) and `ops` (TopK, Multinomial, softmax, log-softmax,
+cross-entropy forward / backward on 512 x 151,936 f32). `--impl reference`
+times the CPU restatement of the reference's routines on the host cores. Under
+torchrun every rank runs its own rows (no collective on the data path); rank 0
+prints one JSON line.
 """
 from __future__ import annotations
 
@@ -27,6 +33,7 @@ sys.path.insert(0, ROOT)
 
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "sampled_rows_per_s"
+L2_BYTES = 126 * 2 ** 20
 
 
 def parse():
@@ -45,7 +52,15 @@ def parse():
                     help="every rank holds a column slice of the SAME rows (C5): local candidates, one all-gather, "
                          "merge on every rank; total work fixed (strong scaling), no host-pointer leg")
     ap.add_argument("--profile", action="store_true",
-                    help="short run for ncu: no e2e leg, no CPU baseline, no clock hold")
+                    help="short run for ncu: no e2e leg, no CPU baseline, no clock hold, no extra legs")
+    ap.add_argument("--no-configs", action="store_true", help="skip the leg that times the other configs")
+    ap.add_argument("--no-ops", action="store_true", help="skip the leg that times the row ops")
+    ap.add_argument("--op", default=None, choices=["softmax", "log_softmax", "ce_fwd", "ce_bwd", "topk", "multinomial"],
+                    help="time one row op only (a small case for a profiler), print its line and exit")
+    ap.add_argument("--op-rows", type=int, default=512)
+    ap.add_argument("--op-vocab", type=int, default=151936)
+    ap.add_argument("--op-dtype", default="f32", choices=["f32", "bf16"])
+    ap.add_argument("--op-topk", type=int, default=64)
     return ap.parse_args()
 
 
@@ -63,9 +78,9 @@ def workload_config(w, args, world):
     return {
         "workload": w.name, "rows_per_gpu": int(w.B), "vocab": int(w.V), "logits_dtype": w.dtype,
         "topp_mode": "A(model/generate.go)" if mode == 0 else "B(model/qwen/generate.go)",
-        "sharding": (f"vocab x{world}, one all-gather of {world}x{int(w.B)} records of 1040 B" if args.vocab_sharded
+        "sharding": (f"vocab x{world}, one all-gather of {world}x{int(w.B)} records" if args.vocab_sharded
                      else f"rows x{world}, no collective"),
-        "l2": "inputs larger than L2" if w.logits.nbytes > 126 * 2 ** 20 else "L2 flushed between steps",
+        "l2": "inputs larger than L2" if w.logits.nbytes > L2_BYTES else "L2 flushed between steps",
     }
 
 
@@ -140,44 +155,240 @@ def time_cpu(w, rows, threads, seconds):
 
 def reference_arm(args, rank, world):
     """The reference's own CPU implementation of the path (its Go routines restated
-    in C++: no Go toolchain exists offline), all host threads, rank 0 only."""
+    in C++: no Go toolchain exists offline), all host threads, rank 0 only, on the
+    workload's own row count."""
     if rank != 0:
         return
     from gorch_b200 import workloads
     from oracle import oracle as orc
     orc.build()
     threads = orc.hw_threads()
-    rows = args.rows or max(threads, 64)
-    w = workloads.make(args.workload, rows, args.mode)
+    w = workloads.make(args.workload, args.rows, args.mode)
+    rows = w.B
     sub = (w.logits, w.cfgs, w.uniforms)
-    for _ in range(args.warmup):
+    # a step of the largest configs takes about a second of host time: bound the run to a few minutes
+    steps = max(1, min(args.steps, 40))
+    warm = max(1, min(args.warmup, 3))
+    for _ in range(warm):
         orc.sample_batch(*sub, want_info=False, flags=0, threads=threads)
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         orc.sample_batch(*sub, want_info=False, flags=0, threads=threads)
     dt = time.perf_counter() - t0
-    value = rows * args.steps / dt
+    value = rows * steps / dt
     cfg = workload_config(w, args, 1)
-    cfg["rows_per_gpu"] = rows
     cfg["sharding"] = "host threads over rows"
     cfg["l2"] = "n/a (host arm)"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
+        "steps": steps, "warmup": warm, "ms_per_step": 1e3 * dt / steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "accum_dtype": "f64",
         "data": "synthetic", "config": cfg,
         "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port",
-                         "sample": f"{rows} rows of {w.name} per step, C++ restatement of the Go routines"},
+                         "sample": f"{rows} rows of {w.name} per step ({steps} of the {args.steps} steps asked for), "
+                                   "C++ restatement of the Go routines"},
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
+def parity_counts(w, ids, flags, max_rows=None):
+    """The timed call's ids against the CPU oracle (rank 0, after the timed region).
+    id_mismatch counts every differing id; of those, `excused` rows are the ones the contract
+    leaves open: the uniform within 1e-6 of a CDF edge, or a top-p cut inside a group of equal
+    probabilities or inside the kernel's rounding band (flagged by the kernel or seen by the oracle)."""
+    from gorch_b200.config import FLAG_BOUNDARY, FLAG_TIE_CUT, FLAG_TOPP_EDGE
+    from oracle import oracle as orc
+    n = w.B if max_rows is None else min(w.B, max_rows)
+    ora = orc.sample_batch(w.logits[:n], w.cfgs[:n], w.uniforms[:n], flags=orc.FAST_KTH, threads=orc.hw_threads())
+    ids, flags = np.asarray(ids[:n]).astype(np.int64), np.asarray(flags[:n]).astype(np.uint32)
+    info = ora["info"]
+    u = w.uniforms[:n]
+    near = (np.minimum(np.abs(u - info["edge_lo"]), np.abs(u - info["edge_hi"])) <= 1e-6) | ((flags & FLAG_BOUNDARY) != 0)
+    soft = ((flags & (FLAG_TIE_CUT | FLAG_TOPP_EDGE)) != 0) | (info["cut_in_tie"] != 0)
+    diff = ids != ora["ids"]
+    return {"rows_checked": int(n), "id_mismatch": int(diff.sum()), "excused": int((diff & (near | soft)).sum()),
+            "unexcused": int((diff & ~(near | soft)).sum()),
+            "boundary_rows": int(((flags & FLAG_BOUNDARY) != 0).sum()),
+            "tie_cut_rows": int(((flags & FLAG_TIE_CUT) != 0).sum()),
+            "topp_edge_rows": int(((flags & FLAG_TOPP_EDGE) != 0).sum())}
+
+
+def dominant_kernel(w):
+    """The kernel that does the streaming for this workload (see profiles/)."""
+    row_bytes = w.V * w.logits.dtype.itemsize          # the library's dispatch rule (shim.cu: use_batch_mode)
+    if not (w.B >= 384 or (w.B >= 32 and w.B * row_bytes >= 24 << 20)):
+        return "sample_cluster_kernel"
+    k = w.cfgs["top_k"]
+    t = w.cfgs["temperature"]
+    narrow = int(((k > 0) | (t == 0.0)).sum())
+    if narrow == w.B:
+        return "narrow_rows_kernel"
+    if narrow == 0:
+        return "wide_rows_kernel"
+    return "narrow_rows_kernel || wide_rows_kernel"
+
+
+def measured_traffic(w):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu capture
+    of this workload (profiles/), scaled to the rows of this launch, or None when no capture covers it."""
+    path = os.path.join(ROOT, "gorch_b200", "measured_traffic.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f).get(w.name)
+        if rec is None or rec.get("topp_mode") != int(w.cfgs["topp_mode"][0]):
+            return None
+        return int(rec["dram_bytes_per_row"] * w.B)
+    except Exception:
+        return None
+
+
+class DeviceBatch:
+    """One workload resident on the device, with a step() that samples it through the device-pointer entry."""
+
+    def __init__(self, torch, smp, w, pinned=False):
+        from gorch_b200.config import DTYPE_BF16, DTYPE_F32
+        self.w, self.smp = w, smp
+        self.code = DTYPE_BF16 if w.dtype == "bf16" else DTYPE_F32
+        B = w.B
+        h_logits = torch.from_numpy(w.logits.view(np.int16) if w.dtype == "bf16" else w.logits)
+        h_cfgs = torch.from_numpy(w.cfgs.view(np.uint8).reshape(B, 16).copy())
+        h_uni = torch.from_numpy(w.uniforms.copy())
+        if pinned:
+            h_logits, h_cfgs, h_uni = h_logits.pin_memory(), h_cfgs.pin_memory(), h_uni.pin_memory()
+        self.h_logits, self.h_cfgs, self.h_uni = h_logits, h_cfgs, h_uni
+        self.d_logits = h_logits.cuda(non_blocking=True)
+        self.d_cfgs = h_cfgs.cuda(non_blocking=True)
+        self.d_uni = h_uni.cuda(non_blocking=True)
+        self.d_ids = torch.empty(B, dtype=torch.int32, device="cuda")
+        self.d_flags = torch.empty(B, dtype=torch.int32, device="cuda")
+
+    def step(self):
+        w = self.w
+        self.smp.sample_dev_ptrs(self.d_logits.data_ptr(), self.code, w.B, w.V, w.V, self.d_cfgs.data_ptr(),
+                                 self.d_uni.data_ptr(), self.d_ids.data_ptr(), self.d_flags.data_ptr())
+
+
+def time_steps(torch, stream, fn, steps, warmup, flush):
+    """Median and mean device time (ms) of fn() over `steps` launches after `warmup`."""
+    ts = []
+    for it in range(warmup + steps):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        fn()
+        e1.record(stream)
+        if it >= warmup:
+            ts.append((e0, e1))
+    torch.cuda.synchronize()
+    ms = [a.elapsed_time(b) for a, b in ts]
+    return float(np.median(ms)), float(np.mean(ms))
+
+
+def configs_leg(torch, smp, stream, flush, peak, skip):
+    """Every BASELINE config except the headline: 20 timed steps each after 3 warm-up steps, L2 flushed
+    between steps where the batch fits in it; step time, rows/s, algorithmic GB/s, fraction of the HBM
+    peak, and the parity counts of the last timed call."""
+    from gorch_b200 import workloads
+    out = {}
+    cases = [("c1", "c1", None), ("c2", "c2", None), ("c2_mode_b", "c2", 1), ("c3", "c3", None),
+             ("c4_mode_a", "c4", 0), ("c4", "c4", None), ("c5", "c5", None)]
+    for key, name, mode in cases:
+        if key == skip:
+            continue
+        w = workloads.make(name, None, mode)
+        db = DeviceBatch(torch, smp, w)
+        torch.cuda.synchronize()
+        fl = flush if w.logits.nbytes <= L2_BYTES else None
+        launches0 = smp.counters()["kernel_launches"]
+        med, mean = time_steps(torch, stream, db.step, 20, 3, fl)
+        launches = smp.counters()["kernel_launches"] - launches0
+        gbs = w.B * w.bytes_per_row / (mean / 1e3) / 1e9
+        out[key] = {"workload": w.name, "rows": int(w.B), "vocab": int(w.V), "dtype": w.dtype,
+                    "topp_mode": int(w.cfgs["topp_mode"][0]),
+                    "us_per_step": round(mean * 1e3, 2), "us_median": round(med * 1e3, 2),
+                    "rows_per_s": round(w.B / (mean / 1e3)), "gbs": round(gbs, 1), "frac": round(gbs / peak, 4),
+                    "kernel": dominant_kernel(w), "launches_per_step": launches // 23,
+                    "l2": "inputs larger than L2" if fl is None else "L2 flushed between steps",
+                    "parity": parity_counts(w, db.d_ids.cpu().numpy(), db.d_flags.cpu().numpy())}
+        del db
+        torch.cuda.empty_cache()
+    return out
+
+
+def ops_leg(torch, smp, stream, flush, peak, only=None, rows=512, vocab=151936, dtype="f32", topk=64,
+            iters=20, warmup=3):
+    """The row ops beside the sampling step on synthetic normal logits x 2 (the distribution of the
+    reference's cross-entropy tests, ce_metal_test.go:44-54). GB/s = algorithmic bytes / time: softmax and
+    log-softmax read and write the tensor once, the cross-entropy forward reads it once, the backward reads
+    it and writes f32, TopK and Multinomial (over the softmax output, f32) read it once."""
+    import ctypes as C
+
+    from gorch_b200 import row_ops, sampling
+    B, V = rows, vocab
+    tdt = torch.float32 if dtype == "f32" else torch.bfloat16
+    code = 0 if dtype == "f32" else 1
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(B, V, device="cuda", dtype=torch.float32, generator=gen).mul_(2.0).to(tdt)
+    out = torch.empty_like(x)
+    dx = torch.empty(B, V, device="cuda", dtype=torch.float32)
+    tgt = torch.randint(0, V, (B,), device="cuda", dtype=torch.int32, generator=gen)
+    row_loss = torch.empty(B, device="cuda")
+    row_lse = torch.empty(B, device="cuda")
+    mean = torch.empty(1, device="cuda")
+    es = x.element_size()
+    s = smp
+    k = min(topk, V)
+    tk_val = torch.empty(B, k, device="cuda", dtype=torch.float32)
+    tk_idx = torch.empty(B, k, device="cuda", dtype=torch.int32)
+    probs = torch.softmax(x.float(), dim=1)
+    uni = torch.rand(B, device="cuda", dtype=torch.float64, generator=gen)
+    ids = torch.empty(B, device="cuda", dtype=torch.int32)
+    flags = torch.empty(B, device="cuda", dtype=torch.int32)
+
+    def run_topk():
+        err = C.c_void_p()
+        rc = s._lib.gorch_cuda_topk_dev(s._ctx, x.data_ptr(), code, B, V, V, k, tk_val.data_ptr(), tk_idx.data_ptr(),
+                                        flags.data_ptr(), C.byref(err))
+        sampling._check(s._lib, rc, err)
+
+    def run_multinomial():
+        err = C.c_void_p()
+        rc = s._lib.gorch_cuda_multinomial_dev(s._ctx, probs.data_ptr(), B, V, V, uni.data_ptr(), ids.data_ptr(),
+                                               flags.data_ptr(), C.byref(err))
+        sampling._check(s._lib, rc, err)
+
+    ops = {
+        "softmax": (lambda: row_ops.softmax_ptrs(s, x.data_ptr(), code, B, V, V, out.data_ptr(), V, False), 2 * es),
+        "log_softmax": (lambda: row_ops.softmax_ptrs(s, x.data_ptr(), code, B, V, V, out.data_ptr(), V, True), 2 * es),
+        "ce_fwd": (lambda: row_ops.cross_entropy_fwd_ptrs(s, x.data_ptr(), code, B, V, V, tgt.data_ptr(), row_loss.data_ptr(),
+                                                          row_lse.data_ptr(), mean.data_ptr()), es),
+        "ce_bwd": (lambda: row_ops.cross_entropy_bwd_ptrs(s, x.data_ptr(), code, B, V, V, tgt.data_ptr(), row_lse.data_ptr(),
+                                                          1.0 / B, dx.data_ptr(), V), es + 4),
+        "topk": (run_topk, es),
+        "multinomial": (run_multinomial, 4),
+    }
+    ops["ce_fwd"][0]()                      # the backward needs a logsumexp to read
+    torch.cuda.synchronize()
+    res = {}
+    for name, (fn, bytes_per_elem) in ops.items():
+        if only not in (None, name):
+            continue
+        med, _ = time_steps(torch, stream, fn, iters, warmup, flush)
+        gbs = B * V * bytes_per_elem / (med / 1e3) / 1e9
+        res[name] = {"rows": B, "vocab": V, "dtype": dtype, "us": round(med * 1e3, 1), "gbs": round(gbs, 1),
+                     "frac": round(gbs / peak, 4)}
+        if name == "topk":
+            res[name]["k"] = k
+    return res
+
+
 def main():
     args = parse()
     if args.profile:
-        args.no_e2e = args.no_cpu_baseline = True
+        args.no_e2e = args.no_cpu_baseline = args.no_configs = args.no_ops = True
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -188,7 +399,6 @@ def main():
     import torch
     import torch.distributed as dist
     from gorch_b200 import build, sampling, workloads
-    from gorch_b200.config import CFG_DTYPE, DTYPE_BF16, DTYPE_F32
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
@@ -196,55 +406,65 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     build.build()
-    workloads.set_shard(0 if args.vocab_sharded else rank)
-    if args.vocab_sharded:
-        args.no_e2e = True
-    w = workloads.make(args.workload, args.rows, args.mode)
-    B, V = w.B, w.V
-    dt_code = DTYPE_BF16 if w.dtype == "bf16" else DTYPE_F32
+    peak, peak_kind = peaks()
     smp = sampling.CudaSampler(local_rank)
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
     smp.set_stream(stream.cuda_stream)
 
-    # host (pinned) and device copies of the inputs
-    h_logits = torch.from_numpy(w.logits.view(np.int16) if w.dtype == "bf16" else w.logits).pin_memory()
-    h_cfgs = torch.from_numpy(w.cfgs.view(np.uint8).reshape(B, 16).copy()).pin_memory()
-    h_uni = torch.from_numpy(w.uniforms.copy()).pin_memory()
+    if args.op is not None:                  # one row op, for a profiler
+        flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device="cuda")
+        res = ops_leg(torch, smp, stream, flush, peak, only=args.op, rows=args.op_rows, vocab=args.op_vocab,
+                      dtype=args.op_dtype, topk=args.op_topk, iters=max(1, args.steps if args.steps < 200 else 20),
+                      warmup=max(1, args.warmup))
+        print(json.dumps({"op": args.op, **res[args.op]}), flush=True)
+        smp.set_stream(None)
+        smp.release()
+        return
+
+    workloads.set_shard(0 if args.vocab_sharded else rank)
+    if args.vocab_sharded:
+        args.no_e2e = True
+    w = workloads.make(args.workload, args.rows, args.mode)
+    B, V = w.B, w.V
+    db = DeviceBatch(torch, smp, w, pinned=True)
+    dt_code = db.code
     h_ids = torch.empty(B, dtype=torch.int32).pin_memory()
     h_flags = torch.empty(B, dtype=torch.int32).pin_memory()
-    d_logits = h_logits.cuda(non_blocking=True)
-    d_cfgs = h_cfgs.cuda(non_blocking=True)
-    d_uni = h_uni.cuda(non_blocking=True)
-    d_ids = torch.empty(B, dtype=torch.int32, device="cuda")
-    d_flags = torch.empty(B, dtype=torch.int32, device="cuda")
+    d_ids, d_flags = db.d_ids, db.d_flags
+    extra_legs = world == 1 and not args.vocab_sharded and not (args.no_configs and args.no_ops)
     flush = None
-    if w.logits.nbytes <= 126 * 2 ** 20:
+    if w.logits.nbytes <= L2_BYTES or extra_legs:
         flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device="cuda")
+    main_flush = flush if w.logits.nbytes <= L2_BYTES else None
     torch.cuda.synchronize()
-
-    def step():
-        smp.sample_dev_ptrs(d_logits.data_ptr(), dt_code, B, V, V, d_cfgs.data_ptr(), d_uni.data_ptr(),
-                            d_ids.data_ptr(), d_flags.data_ptr())
+    step = db.step
+    phases = None
 
     if args.vocab_sharded:
         lo, hi = workloads.shard_vocab(V, rank, world)
-        d_slice = d_logits[:, lo:hi].contiguous()
-        del d_logits
-        d_rec = torch.empty((B, sampling.VS_RECORD_BYTES), dtype=torch.uint8, device="cuda")
-        d_all = torch.empty((world, B, sampling.VS_RECORD_BYTES), dtype=torch.uint8, device="cuda")
-        if flush is None and d_slice.numel() * d_slice.element_size() <= 126 * 2 ** 20:
-            flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device="cuda")
+        d_slice = db.d_logits[:, lo:hi].contiguous()
+        db.d_logits = None
+        rec_bytes = sampling.VS_RECORD_BYTES
+        d_rec = torch.empty((B, rec_bytes), dtype=torch.uint8, device="cuda")
+        d_all = torch.empty((world, B, rec_bytes), dtype=torch.uint8, device="cuda")
+        if main_flush is None and d_slice.numel() * d_slice.element_size() <= L2_BYTES:
+            main_flush = flush if flush is not None else torch.empty(256 * 2 ** 20, dtype=torch.uint8, device="cuda")
         torch.cuda.synchronize()
+        pe = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
 
         def step():  # noqa: F811
-            smp.vocab_local_ptrs(d_slice.data_ptr(), dt_code, B, hi - lo, hi - lo, lo, d_cfgs.data_ptr(), d_rec.data_ptr())
+            pe[0].record(stream)
+            smp.vocab_local_ptrs(d_slice.data_ptr(), dt_code, B, hi - lo, hi - lo, lo, db.d_cfgs.data_ptr(), d_rec.data_ptr())
+            pe[1].record(stream)
             if world > 1:
                 dist.all_gather_into_tensor(d_all.view(-1), d_rec.view(-1))
             else:
                 d_all[0].copy_(d_rec)
-            smp.vocab_merge_ptrs(d_all.data_ptr(), world, B, V, d_cfgs.data_ptr(), d_uni.data_ptr(),
+            pe[2].record(stream)
+            smp.vocab_merge_ptrs(d_all.data_ptr(), world, B, V, db.d_cfgs.data_ptr(), db.d_uni.data_ptr(),
                                  d_ids.data_ptr(), d_flags.data_ptr())
+            pe[3].record(stream)
 
     def barrier():
         if world > 1:
@@ -252,8 +472,8 @@ def main():
         torch.cuda.synchronize()
 
     for _ in range(max(args.warmup, 3)):
-        if flush is not None:
-            flush.zero_()
+        if main_flush is not None:
+            main_flush.zero_()
         step()
     barrier()
     clocks = ClockSampler(local_rank)
@@ -263,8 +483,8 @@ def main():
     launches0 = smp.counters()["kernel_launches"]
     barrier()
     for a, b in evs:
-        if flush is not None:
-            flush.zero_()
+        if main_flush is not None:
+            main_flush.zero_()
         a.record(stream)
         step()
         b.record(stream)
@@ -272,6 +492,10 @@ def main():
     launches = smp.counters()["kernel_launches"] - launches0
     kernel_ms = [a.elapsed_time(b) for a, b in evs]
     total_ms = float(sum(kernel_ms))          # device time of the K steps (flush writes excluded)
+    if args.vocab_sharded:
+        phases = {"local_us": round(pe[0].elapsed_time(pe[1]) * 1e3, 1), "all_gather_us": round(pe[1].elapsed_time(pe[2]) * 1e3, 1),
+                  "merge_us": round(pe[2].elapsed_time(pe[3]) * 1e3, 1), "of": "the last timed step on rank 0"}
+    timed_ids, timed_flags = d_ids.cpu().numpy().copy(), d_flags.cpu().numpy().copy()
     # keep the load on for a moment if the timed region was too short for NVML to see it
     t_end = time.perf_counter() + (0.0 if args.profile else max(0.0, 0.6 - total_ms / 1e3))
     while time.perf_counter() < t_end:
@@ -285,8 +509,9 @@ def main():
     if not args.no_e2e:
         smp.set_stream(None)
         ke = max(3, min(K, 20))
+
         def host_step():
-            smp.sample_host_ptrs(h_logits.data_ptr(), dt_code, B, V, V, h_cfgs.data_ptr(), h_uni.data_ptr(),
+            smp.sample_host_ptrs(db.h_logits.data_ptr(), dt_code, B, V, V, db.h_cfgs.data_ptr(), db.h_uni.data_ptr(),
                                  h_ids.data_ptr(), h_flags.data_ptr())
         host_step(); host_step()
         barrier()
@@ -294,7 +519,7 @@ def main():
         for _ in range(ke):
             host_step()
         e2e_s = time.perf_counter() - t0
-        if not torch.equal(h_ids.cuda(), d_ids):
+        if not np.array_equal(h_ids.numpy(), timed_ids):
             raise SystemExit("host and device entry points disagree")
         smp.set_stream(stream.cuda_stream)
     barrier()
@@ -304,7 +529,6 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms_max, e2e_ms_max = t.tolist()
     if rank == 0:
-        peak, peak_kind = peaks()
         rows_total = B * K if args.vocab_sharded else B * world * K
         value = rows_total / (total_ms_max / 1e3)
         alg_bytes = B * w.bytes_per_row
@@ -315,19 +539,33 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": K,
             "warmup": max(args.warmup, 3), "ms_per_step": total_ms_max / K, "higher_is_better": True,
-            "scaling": "strong" if args.vocab_sharded else "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "scaling": "strong" if args.vocab_sharded else "weak", "vs_baseline": None,
+            "dtype": w.dtype, "accum_dtype": "f64", "data": "synthetic",
             "config": workload_config(w, args, world),
             "logits_gbs_per_gpu": achieved,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": measured_traffic(w), "peak_source": peak_kind,
+                         "frac": achieved / peak, "traffic": None if args.vocab_sharded else measured_traffic(w),
+                         "peak_source": peak_kind,
                          "kernel": dominant_kernel(w), "algorithmic_bytes_per_launch": alg_bytes,
                          "timed": "whole step (every kernel of the call), CUDA events on the launching stream"},
             "clocks": clk, "gpu_launches": int(launches),
+            "parity": parity_counts(w, timed_ids, timed_flags),
         }
+        if phases is not None:
+            line["phases"] = phases
         if e2e_ms_max > 0:
             line["e2e"] = {"value": rows_total / (e2e_ms_max / 1e3), "unit": "rows/s",
                            "h2d_bytes_per_step": int(w.logits.nbytes + B * 24),
                            "d2h_bytes_per_step": int(B * 8)}
+        if extra_legs:
+            # the other configs and the row ops, device-resident, on this same GPU
+            db = None
+            torch.cuda.empty_cache()
+            if not args.no_configs:
+                line["configs"] = configs_leg(torch, smp, stream, flush, peak,
+                                              skip=args.workload if args.rows is None and args.mode is None else None)
+            if not args.no_ops:
+                line["ops"] = ops_leg(torch, smp, stream, flush, peak)
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle as orc
             threads = orc.hw_threads()
@@ -340,31 +578,8 @@ def main():
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    smp.set_stream(None)
     smp.release()
-
-
-def dominant_kernel(w):
-    """The kernel that does the streaming for this workload (see profiles/)."""
-    row_bytes = w.V * w.logits.dtype.itemsize          # the library's dispatch rule (shim.cu: use_batch_mode)
-    if not (w.B >= 384 or (w.B >= 32 and w.B * row_bytes >= 24 << 20)):
-        return "sample_cluster_kernel"
-    if int(w.cfgs["top_k"][0]) > 0 or float(w.cfgs["temperature"][0]) == 0.0:
-        return "narrow_rows_kernel"
-    return "wide_rows_kernel"
-
-
-def measured_traffic(w):
-    """DRAM bytes per launch of the dominant kernel from the committed ncu capture
-    of this workload (profiles/), or None when no capture covers it."""
-    path = os.path.join(ROOT, "gorch_b200", "measured_traffic.json")
-    try:
-        with open(path) as f:
-            rec = json.load(f).get(w.name)
-        if rec is None or rec.get("rows") != w.B or rec.get("topp_mode") != int(w.cfgs["topp_mode"][0]):
-            return None
-        return rec["dram_bytes_per_launch"]
-    except Exception:
-        return None
 
 
 if __name__ == "__main__":

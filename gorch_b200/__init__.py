@@ -9,13 +9,13 @@ softmax / cross-entropy ops (sampling.py, row_ops.py), row and vocab sharding
 (distributed.py), and the seeded synthetic workloads used for measurement.
 """
 from .config import (CFG_DTYPE, FLAG_BAD_CFG, FLAG_BOUNDARY, FLAG_FALLBACK, FLAG_GENERAL_PATH,
-                     FLAG_INTERNAL, FLAG_NONFINITE, FLAG_TIE_CUT, FLAG_TIMEOUT, FLAG_TOPP_EDGE,
+                     FLAG_INTERNAL, FLAG_NONFINITE, FLAG_TIE_CUT, FLAG_TOPP_EDGE,
                      MODE_A, MODE_B, GenerateConfig, QwenGenerateConfig, default_generate_config,
                      greedy_config, qwen_greedy)
 
 __all__ = [
     "CFG_DTYPE", "MODE_A", "MODE_B", "GenerateConfig", "QwenGenerateConfig",
     "default_generate_config", "greedy_config", "qwen_greedy",
-    "FLAG_BOUNDARY", "FLAG_FALLBACK", "FLAG_NONFINITE", "FLAG_TIE_CUT", "FLAG_TIMEOUT",
+    "FLAG_BOUNDARY", "FLAG_FALLBACK", "FLAG_NONFINITE", "FLAG_TIE_CUT",
     "FLAG_TOPP_EDGE", "FLAG_GENERAL_PATH", "FLAG_INTERNAL", "FLAG_BAD_CFG",
 ]

@@ -25,7 +25,6 @@ FLAG_BOUNDARY = 1 << 0      # uniform within 1e-6 of an edge of the chosen CDF i
 FLAG_FALLBACK = 1 << 1      # walk fell through: id = V-1 (model/generate.go:239)
 FLAG_NONFINITE = 1 << 2     # NaN / +-Inf poisoned the softmax: id = V-1 as in the reference
 FLAG_TIE_CUT = 1 << 3       # mode B: the cut separates equal probabilities (order unpinned upstream)
-FLAG_TIMEOUT = 1 << 4       # a bounded device-side wait gave up
 FLAG_TOPP_EDGE = 1 << 5     # top-p stop test decided within 1e-12 of its threshold
 FLAG_GENERAL_PATH = 1 << 6  # row took the full-row path (informational)
 FLAG_INTERNAL = 1 << 7      # an internal invariant failed; the id is unreliable

@@ -247,9 +247,9 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   RowDebug dbg;
   dbg.sum_exp = 0; dbg.resum = 1.0; dbg.edge_lo = 0; dbg.edge_hi = 0; dbg.kept = 0;
   dbg.max_scaled = 0; dbg.threshold = __int_as_float(0x7fc00000); dbg.path = 0;
-  for (int q = 0; q < 8; q++) dbg.cycles[q] = 0;
+  for (int q = 0; q < 8; q++) dbg.reserved[q] = 0;
   long long tprev = clock64();
-  auto stamp = [&](int slot) { const long long now = clock64(); dbg.cycles[slot] = static_cast<uint32_t>(now - tprev); tprev = now; };
+  auto stamp = [&](int slot) { const long long now = clock64(); dbg.reserved[slot] = static_cast<uint32_t>(now - tprev); tprev = now; };
   auto write_row = [&](int id, uint32_t fl) {
     if (tid == 0) {
       A.out_ids[row_id] = id;
@@ -543,7 +543,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   nan_seen |= (run != run);
   xmax = run;
   stamp(1);
-  dbg.cycles[5] = static_cast<uint32_t>(*s_cnt);
+  dbg.reserved[5] = static_cast<uint32_t>(*s_cnt);
   int nk = 0;
   if (!giveup && *s_cnt > N_CAP) giveup = true;
   if (!giveup && tight && *s_cnt < topk) {                   // the estimated threshold was too tight for this row

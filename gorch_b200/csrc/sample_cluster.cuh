@@ -268,9 +268,9 @@ __global__ void __launch_bounds__(NT, 2) sample_cluster_kernel(ClusterArgs CA) {
   RowDebug dbg;
   dbg.sum_exp = 0; dbg.resum = 1.0; dbg.edge_lo = 0; dbg.edge_hi = 0; dbg.kept = 0;
   dbg.max_scaled = 0; dbg.threshold = __int_as_float(0x7fc00000); dbg.path = 0;
-  for (int q = 0; q < 8; q++) dbg.cycles[q] = 0;
+  for (int q = 0; q < 8; q++) dbg.reserved[q] = 0;
   long long tprev = clock64();
-  auto stamp = [&](int slot) { long long now = clock64(); dbg.cycles[slot] = static_cast<uint32_t>(now - tprev); tprev = now; };
+  auto stamp = [&](int slot) { long long now = clock64(); dbg.reserved[slot] = static_cast<uint32_t>(now - tprev); tprev = now; };
 
   // ================================================================ greedy
   if (Tm == 0.0f) {

@@ -17,7 +17,6 @@ constexpr uint32_t FLAG_BOUNDARY = 1u << 0;
 constexpr uint32_t FLAG_FALLBACK = 1u << 1;
 constexpr uint32_t FLAG_NONFINITE = 1u << 2;
 constexpr uint32_t FLAG_TIE_CUT = 1u << 3;
-constexpr uint32_t FLAG_TIMEOUT = 1u << 4;
 constexpr uint32_t FLAG_TOPP_EDGE = 1u << 5;
 constexpr uint32_t FLAG_GENERAL_PATH = 1u << 6;
 constexpr uint32_t FLAG_INTERNAL = 1u << 7;
@@ -39,7 +38,7 @@ struct RowDebug {  // optional per-row record for the parity tests
   float max_scaled; // max of logits/T
   float threshold;  // top-k threshold in logits/T units (NaN when inactive)
   int32_t path;     // 0 greedy, 1 small-set path, 2 full-row path
-  uint32_t cycles[8]; // SM clock ticks between the phases of the row, as seen by rank 0 / thread 0
+  uint32_t reserved[8]; // scratch of the kernels (phase clocks, list sizes); no meaning is promised
 };
 
 // ---------------------------------------------------------------------------

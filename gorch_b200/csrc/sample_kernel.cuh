@@ -376,7 +376,7 @@ __device__ void single_cta_row(const KernelArgs& A, const int64_t row_id, unsign
   RowDebug dbg;
   dbg.sum_exp = 0; dbg.resum = 1.0; dbg.edge_lo = 0; dbg.edge_hi = 0; dbg.kept = 0;
   dbg.max_scaled = 0; dbg.threshold = __int_as_float(0x7fc00000); dbg.path = 0;
-  for (int q = 0; q < 8; q++) dbg.cycles[q] = 0;
+  for (int q = 0; q < 8; q++) dbg.reserved[q] = 0;
 
   // ------------------------------------------------------------------ greedy
   // generate.go:75-76 + 134-144: strict '>' from index 0. Lowest index wins

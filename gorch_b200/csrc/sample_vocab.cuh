@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(VM_NT, 4) vocab_merge_kernel(MergeArgs M) {
     RowDebug dbg;
     dbg.sum_exp = 0; dbg.resum = 1.0; dbg.edge_lo = 0; dbg.edge_hi = 0; dbg.kept = 0;
     dbg.max_scaled = 0; dbg.threshold = __int_as_float(0x7fc00000); dbg.path = 3;
-    for (int q = 0; q < 8; q++) dbg.cycles[q] = 0;
+    for (int q = 0; q < 8; q++) dbg.reserved[q] = 0;
     auto write_row = [&](int id, uint32_t fl) {
       if (tid == 0) {
         A.out_ids[row] = id;

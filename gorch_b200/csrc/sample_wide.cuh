@@ -466,6 +466,492 @@ __device__ __noinline__ bool wide_big_zone(const WSpan& sp_in, const RowView<T>&
   return true;
 }
 
+// ---------------------------------------------------------------------------------------------
+// One-pass front end. Where a sample of the row (every eighth step of every warp) places the
+// top-p cut inside a narrow window of logit values, one pass over the row is enough: it sums the
+// mass of everything (S) and of what lies above the window (certainly kept, per piece) with the fast
+// exponential, relative to an anchor near the row maximum, and notes which lane-steps hold a logit
+// inside the window; those few vectors are read again (from L2) into the exact zone list, and the
+// tail decides the cut inside the window as it does after two passes. The sample only chooses the
+// window: whether the cut really lies inside it is checked on the sums of the whole row, and a row
+// whose window failed (or that the sample cannot place: a few heavy tokens, NaN, a wide window) takes
+// the two-pass front end. Rows without a cut need no window at all.
+//
+// Error budget of the fast sums against exp(d) in f64, d = x/T - max rounded to f32 as upstream:
+// ex2.approx 2.4e-7, three f32 additions per step before the f64 accumulators 1.8e-7, and per unit
+// of |x/T - anchor| the roundings of that difference, of d itself, of the product with log2(e) and
+// of the constant, 2e-7 together: W1_EPS_FIXED + W1_EPS_PER_D * (largest |d| that carries mass).
+// ---------------------------------------------------------------------------------------------
+constexpr int W1_STRIDE = 8;             // the sample: every eighth step
+#ifndef GS_W1_PF
+#define GS_W1_PF 10
+#endif
+constexpr int W1_PF = GS_W1_PF;          // steps ahead that the pass asks L2 for its lines (0: never)
+constexpr int W_ZCAP1 = 2 * W_ZCAP;      // zone list of the one-pass front end (zone + table areas)
+constexpr double W1_EPS_FIXED = 4.5e-7;
+constexpr double W1_EPS_PER_D = 2.0e-7;
+constexpr float W1_MAGIC = 2097152.0f;   // 2^21: floats in [2^21, 2^22) have an ulp of 1/4
+constexpr float W1_FCLAMP = 2097152.0f + 4095.75f;
+static_assert(W_OFF_EB == W_OFF_ZONE + W_ZCAP * 8 && W_EB_REP * W_EB_REP_ENTRIES * 8 >= W_ZCAP * 8, "the long zone list spans both areas");
+
+__device__ __forceinline__ void l2_prefetch(const void* p) { asm volatile("prefetch.global.L2 [%0];" :: "l"(p)); }
+__device__ __forceinline__ float ex2_approx(float t) { float e; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t)); return e; }
+__device__ __forceinline__ float set_ge(float a, float b) { float r; asm("set.ge.f32.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }   // 1.0f or 0.0f
+__device__ __forceinline__ float min3abs(float a, float b, float c) { float d; asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(fabsf(b)), "f"(fabsf(c))); return d; }
+
+// Histogram bucket of a raw logit: y = (anchor' - x) * hs, f = RN(hc - x * hs) rounds the exact
+// y + 2^21 to a multiple of 1/4 (one rounding, by fma); bits 2..13 of f are the bucket: y in
+// [b - 1/8, b + 7/8]. f is clamped from above (everything below the range, -Inf and NaN land in the
+// last bucket); a logit above the anchor leaves the binade and lands anywhere inside the array:
+// the caller checks the maximum it saw against the anchor.
+__device__ __forceinline__ uint32_t bucket_off1(float x, float nhs, float hc) {
+  return __float_as_uint(fminf(fmaf(x, nhs, hc), W1_FCLAMP)) & 0x3ffcu;
+}
+// Smallest float whose bucket is <= bmax (the buckets fall as x rises). +Inf: none; -Inf: every float.
+__device__ __forceinline__ float bucket_floor1(int bmax, float nhs, float hc, bool& ok) {
+  if (bmax >= W_NB - 1) return -INFINITY;
+  if (bmax < 0) return INFINITY;
+  float x = ((hc - W1_MAGIC) - (static_cast<float>(bmax) + 0.875f)) / (-nhs);
+  const uint32_t lim = static_cast<uint32_t>(bmax) * 4u + 3u;
+  int it = 0;
+  while (bucket_off1(x, nhs, hc) > lim && it < 24) { x = nextafterf(x, INFINITY); it++; }
+  while (it < 24) {
+    const float below = nextafterf(x, -INFINITY);
+    if (bucket_off1(below, nhs, hc) > lim) break;
+    x = below; it++;
+  }
+  if (it >= 24) ok = false;
+  return x;
+}
+// x / T in IEEE f32 round-to-nearest by q0 = x y, r = fma(-q0, T, x), q = fma(r, y, q0) with y = RN(1/T):
+// the correctly rounded quotient whenever T's significand is not all ones and nothing over- or underflows
+// (the caller takes this form for 2^-20 <= T <= 2^20 only and clamps x at -1e30: whatever lies below has
+// mass 0 either way).
+__device__ __forceinline__ f32x2_t div2_fast(f32x2_t X, float T, float y) {
+  const f32x2_t Y = pk2(y, y);
+  const f32x2_t Q0 = mul2(X, Y);
+  const f32x2_t R = fma2(Q0, pk2(-T, -T), X);
+  return fma2(R, Y, Q0);
+}
+
+struct OnePassOut {
+  float m;                 // row maximum of x / T
+  double S, Ktot;          // all mass; mass above the window (both relative to exp(m))
+  int nz;                  // zone entries in the list
+  float xA, xB;            // above the window: x >= xA; the window: xB <= x < xA
+  double eps;              // relative error bound of S and Ktot
+};
+struct P1Consts {
+  float as, Tm, yT;        // anchor in units of x / T; temperature and its rounded reciprocal
+  float xA, xB;            // above the window: x >= xA; the window: xB <= x < xA
+  float xmid, xhalf;       // |x - xmid| <= xhalf is a superset of the window
+  uint32_t zl_s, zcnt_s;   // shared-memory addresses of the window list (W_ZCAP1 entries of (logit bits, index)) and its counter
+};
+struct P1Acc {
+  double tot;              // running piece without a cut: all its mass; with a cut: all mass so far
+  double kep;              // with a cut: mass above the window of the running piece
+  double stot;             // without a cut: all mass of the pieces done
+  float vmax;              // NaN-propagating running maximum
+};
+
+// The window's logits of one lane-step go to the list. Only lanes that saw a logit near the window
+// come here; CHECK: the step may hold logits outside the row (index tested against V).
+template <int VEC, bool CHECK>
+__device__ __forceinline__ void p1_append(const float* x, int i_first, int V, const P1Consts& k) {
+#pragma unroll
+  for (int c = 0; c < 8; c++) {
+    if (x[c] < k.xA && x[c] >= k.xB) {                         // (masked logits are -Inf: never at or above a finite xB)
+      const int i = i_first + (c / VEC) * 32 * VEC + (c % VEC);
+      if (!CHECK || (i >= 0 && i < V)) {
+        uint32_t slot;
+        asm volatile("atom.shared.add.u32 %0, [%1], 1;" : "=r"(slot) : "r"(k.zcnt_s) : "memory");
+        if (slot < static_cast<uint32_t>(W_ZCAP1)) {
+          asm volatile("st.shared.v2.u32 [%0], {%1, %2};" :: "r"(k.zl_s + slot * 8u), "r"(__float_as_uint(x[c])), "r"(static_cast<uint32_t>(i)) : "memory");
+        }
+      }
+    }
+  }
+}
+
+// Eight logits of a lane: exp(x/T - anchor) = 2^((x/T - anchor) log2 e); masked logits are -Inf and
+// add 2^-Inf = 0. Three f32 additions per sum, then f64. Returns whether a logit lies near the window.
+template <bool TONE, bool CUT>
+__device__ __forceinline__ bool p1_body(const float* x, const P1Consts& k, P1Acc& a) {
+  const float LOG2E = 1.4426950408889634f;
+  const f32x2_t NA = pk2(-k.as, -k.as), LL = pk2(LOG2E, LOG2E);
+  a.vmax = max3nan(a.vmax, x[0], x[1]); a.vmax = max3nan(a.vmax, x[2], x[3]);
+  a.vmax = max3nan(a.vmax, x[4], x[5]); a.vmax = max3nan(a.vmax, x[6], x[7]);
+  float nearest = INFINITY;
+  f32x2_t E[4], KK[2];
+#pragma unroll
+  for (int c = 0; c < 4; c++) {
+    const f32x2_t X = pk2(x[2 * c], x[2 * c + 1]);
+    f32x2_t S_;
+    if (TONE) S_ = X;
+    else S_ = div2_fast(pk2(fmaxf(x[2 * c], -1e30f), fmaxf(x[2 * c + 1], -1e30f)), k.Tm, k.yT);
+    float t0, t1;
+    upk2(mul2(add2(S_, NA), LL), t0, t1);
+    E[c] = pk2(ex2_approx(t0), ex2_approx(t1));
+    if (CUT) {
+      const f32x2_t M = pk2(set_ge(x[2 * c], k.xA), set_ge(x[2 * c + 1], k.xA));
+      if ((c & 1) == 0) KK[c >> 1] = mul2(E[c], M); else KK[c >> 1] = fma2(E[c], M, KK[c >> 1]);
+      float z0, z1;
+      upk2(add2(X, pk2(-k.xmid, -k.xmid)), z0, z1);
+      nearest = min3abs(nearest, z0, z1);
+    }
+  }
+  { float p, q; upk2(add2(add2(E[0], E[1]), add2(E[2], E[3])), p, q); a.tot += static_cast<double>(p + q); }
+  if (CUT) {
+    float p, q;
+    upk2(add2(KK[0], KK[1]), p, q);
+    a.kep += static_cast<double>(p + q);
+  }
+  return CUT && nearest <= k.xhalf;
+}
+template <bool CUT>
+__device__ __forceinline__ void p1_piece_end(int st, int nst, int lane, double* part_w, P1Acc& a) {
+  if ((st & (W_G - 1)) == W_G - 1 || st == nst - 1) {
+    const double kw = warp_sum_d(CUT ? a.kep : a.tot);
+    if (lane == 0) part_w[st / W_G] = kw;
+    if (CUT) { a.kep = 0.0; } else { a.stot += a.tot; a.tot = 0.0; }
+  }
+}
+// A step that holds the row's first or last vector, or vectors past the end: loaded on the spot and masked.
+template <typename T, bool TONE, bool CUT>
+__device__ __noinline__ void p1_edge_step(const WSpan& sp, const RowView<T>& rv, int lane, int st,
+                                          const P1Consts& k, double* part_w, P1Acc& a) {
+  constexpr int VEC = Elem<T>::VEC, EPI = 8 / VEC, SV = 32 * EPI;
+  const int gv = sp.first + st * SV + lane;
+  float x[8];
+#pragma unroll
+  for (int h = 0; h < EPI; h++) {
+    const int g = gv + 32 * h;
+    float xv[VEC];
+    Elem<T>::unpack(__ldg(rv.vbase + min(g, rv.nvec - 1)), xv);
+    const int i0 = g * VEC - rv.shift;
+#pragma unroll
+    for (int c = 0; c < VEC; c++) {
+      const int i = i0 + c;
+      x[h * VEC + c] = (g < rv.nvec && i >= 0 && i < rv.V) ? xv[c] : -INFINITY;
+    }
+  }
+  if (p1_body<TONE, CUT>(x, k, a)) p1_append<VEC, true>(x, gv * VEC - rv.shift, rv.V, k);
+  p1_piece_end<CUT>(st, sp.nst, lane, part_w, a);
+}
+// The pass: part_w[piece] (this warp's pieces) receives the mass of each piece (of all its logits
+// without a cut, of those above the window with one); the lane-private sum of all mass comes back
+// in Ssum, the lane's running maximum in vmax.
+template <typename T, bool TONE, bool CUT>
+__device__ __noinline__ void wide_onepass_stream(const WSpan& sp, const RowView<T>& rv, int lane, const P1Consts& k_in,
+                                                 double* part_w, double& Ssum, float& vmax) {
+  constexpr int VEC = Elem<T>::VEC, EPI = 8 / VEC, SV = 32 * EPI;
+  const P1Consts k = k_in;
+  P1Acc a;
+  a.tot = 0.0; a.kep = 0.0; a.stot = 0.0; a.vmax = -INFINITY;
+  const int nst = sp.nst, clean_lo = sp.clean_lo, clean_hi = sp.clean_hi;
+  int st = 0;
+  for (; st < clean_lo; st++) p1_edge_step<T, TONE, CUT>(sp, rv, lane, st, k, part_w, a);
+  // Clean steps: every vector exists and none is the row's first or last. Two register buffers used
+  // in turn (no copies between them): a step's vectors are asked for two steps ahead, and L2 is asked
+  // for the lines W1_PF steps ahead. The steady loop runs while both refills stay inside the clean
+  // range; what is left is loaded on the spot. (Four steps in flight, two of them in a cp.async ring
+  // in shared memory, were measured and changed nothing: the pass is bound by instruction issue.)
+  auto unpack8 = [&](const uint4& q0, const uint4& q1, float* x) {
+    if (EPI == 2) { Elem<T>::unpack(q0, x); Elem<T>::unpack(q1, x + 4 * (EPI - 1)); }
+    else Elem<T>::unpack(q0, x);
+  };
+  if (clean_hi - clean_lo >= 4) {
+    const uint4* p = sp.lane_src + clean_lo * SV;
+    int i_first = (sp.first + clean_lo * SV + lane) * VEC - rv.shift;
+    const int st_end = clean_lo + ((clean_hi - clean_lo - 2) & ~1);   // steps [clean_lo, st_end) in pairs, refills < clean_hi
+    uint4 a0 = __ldg(p), a1 = a0, b0, b1;
+    if (EPI == 2) a1 = __ldg(p + 32);
+    b0 = __ldg(p + SV); b1 = b0;
+    if (EPI == 2) b1 = __ldg(p + SV + 32);
+    const int pf_end = clean_hi - W1_PF;                      // last step that may still ask for step + W1_PF
+    float x[8];
+#pragma unroll 1
+    for (; st < st_end; st += 2) {
+      unpack8(a0, a1, x);
+      a0 = __ldg(p + 2 * SV); if (EPI == 2) a1 = __ldg(p + 2 * SV + 32);
+      if (W1_PF > 0 && st + 1 < pf_end) {
+        l2_prefetch(p + W1_PF * SV); l2_prefetch(p + (W1_PF + 1) * SV);
+        if (EPI == 2) { l2_prefetch(p + W1_PF * SV + 32); l2_prefetch(p + (W1_PF + 1) * SV + 32); }
+      }
+      if (p1_body<TONE, CUT>(x, k, a)) p1_append<VEC, false>(x, i_first, 0, k);
+      p1_piece_end<CUT>(st, nst, lane, part_w, a);
+      unpack8(b0, b1, x);
+      b0 = __ldg(p + 3 * SV); if (EPI == 2) b1 = __ldg(p + 3 * SV + 32);
+      if (p1_body<TONE, CUT>(x, k, a)) p1_append<VEC, false>(x, i_first + SV * VEC, 0, k);
+      p1_piece_end<CUT>(st + 1, nst, lane, part_w, a);
+      p += 2 * SV;
+      i_first += 2 * SV * VEC;
+    }
+    unpack8(a0, a1, x);
+    if (p1_body<TONE, CUT>(x, k, a)) p1_append<VEC, false>(x, i_first, 0, k);
+    p1_piece_end<CUT>(st, nst, lane, part_w, a);
+    unpack8(b0, b1, x);
+    if (p1_body<TONE, CUT>(x, k, a)) p1_append<VEC, false>(x, i_first + SV * VEC, 0, k);
+    p1_piece_end<CUT>(st + 1, nst, lane, part_w, a);
+    st += 2;
+  }
+  for (; st < nst; st++) p1_edge_step<T, TONE, CUT>(sp, rv, lane, st, k, part_w, a);
+  Ssum = CUT ? a.tot : a.stot;
+  vmax = a.vmax;
+}
+
+// false: the row takes the two-pass front end (nothing of the row has been decided or written).
+template <typename T>
+__device__ __noinline__ bool wide_front_onepass(const BatchArgs& BA, const int64_t row_id, const RowView<T>& rv, const WSpan& sp,
+                                                unsigned char* dyn, WideShared& sh, const RowCfg cfg, const bool cut_on,
+                                                const int span, const int ppw, const int npiece, OnePassOut& out, uint32_t* clk) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  long long tprev = clock64();
+  auto stamp = [&](int slot) { const long long now = clock64(); clk[slot] = static_cast<uint32_t>(now - tprev); tprev = now; };
+  auto fail = [&](int why) -> bool { out.nz = why; return false; };   // why the row takes two passes (diagnostics)
+  constexpr int VEC = Elem<T>::VEC, EPI = 8 / VEC, SV = 32 * EPI;
+  bu::Scratch& sc = sh.sc;
+  const double* s_tab = sh.tab;
+  uint32_t* hist = reinterpret_cast<uint32_t*>(dyn + W_OFF_HIST);
+  uint2* zl = reinterpret_cast<uint2*>(dyn + W_OFF_ZONE);                 // W_ZCAP1 entries
+  double* part = reinterpret_cast<double*>(dyn + W_OFF_PART);
+  const float Tm = cfg.temperature;
+  const int mode = cfg.topp_mode;
+  const double plim = (mode == 0) ? static_cast<double>(cfg.top_p) * 1.5 : static_cast<double>(cfg.top_p);
+  const bool t_is_one = (Tm == 1.0f);
+  const uint32_t tb = __float_as_uint(Tm);
+  if (!t_is_one && !(Tm >= 9.5367431640625e-7f && Tm <= 1048576.0f && (tb & 0x7fffffu) != 0x7fffffu)) return fail(1);
+  if (rv.nvec < W_NW * SV * 8) return fail(2);                              // short rows: nothing to gain
+
+  // ask L2 for the sample's lines now: the sweep below then finds them there
+  if (cut_on) {
+    for (int st = 0; st < sp.nst; st += W1_STRIDE) {
+#pragma unroll
+      for (int h = 0; h < EPI; h++) {
+        const int g = sp.first + st * SV + lane + 32 * h;
+        if (g < rv.nvec) asm volatile("prefetch.global.L2::evict_last [%0];" :: "l"(rv.vbase + g));
+      }
+    }
+  }
+  // ---- a first look: every warp's first step gives a value near the row maximum and the range
+  float smax = -INFINITY, smin = INFINITY;
+  bool snan = false;
+#pragma unroll
+  for (int h = 0; h < EPI; h++) {
+    const int g = sp.first + 32 * h + lane;
+    if (sp.nst > 0 && g < rv.nvec) rv.visit(g, [&](float xv, int) { smax = fmaxf(smax, xv); smin = fminf(smin, xv); snan |= (xv != xv); });
+  }
+  if (bu::max_i<W_NW>(snan ? 1 : 0, sc, tid)) return fail(3);
+  smax = okey_to_float(static_cast<uint32_t>(bu::max_u64<W_NW>(static_cast<unsigned long long>(okey(smax)), sc, tid)));
+  smin = okey_to_float(static_cast<uint32_t>(bu::min_u64<W_NW>(static_cast<unsigned long long>(okey(smin)), sc, tid)));
+  const float r0 = smax - smin;
+  if (!(r0 >= 0.0f && r0 < 1e30f && fabsf(smax) < 1e30f)) return fail(3);
+  // the anchor of the fast exponentials: where the row maximum is expected (for bell-shaped rows the
+  // maximum of the whole row lies about an eighth of the first look's range above its maximum)
+  const float as = scale_t(smax + 0.125f * r0, Tm);
+  if (!(fabsf(as) < 1e30f)) return fail(3);
+
+  stamp(0);
+  P1Consts k;
+  k.as = as; k.Tm = Tm; k.yT = t_is_one ? 1.0f : __frcp_rn(Tm);
+  k.xA = -INFINITY; k.xmid = 0.0f; k.xhalf = -1.0f;
+  k.xB = -INFINITY; k.zl_s = smem_addr(zl); k.zcnt_s = smem_addr(&sh.cnt);
+  float xA = -INFINITY, xB = -INFINITY;
+  double eps = W1_EPS_FIXED + W1_EPS_PER_D * 9.7;
+  if (cut_on) {
+    // ---- the sample: count histogram over 4096 buckets of (anchor - x), anchor half of the first
+    // look's range above its maximum, bucket width so that the range and as much again below fit
+    const float margin = fmaxf(0.5f * r0, 1e-3f * fmaxf(1.0f, fabsf(smax)));
+    const float hs = 4094.0f / fmaxf(2.25f * r0 + margin, 1e-30f);
+    const float Tc = Tm;
+    // bucket width in units of x / T between 2^-16 and 2^-7
+    const float hs_c = fminf(fmaxf(hs, 128.0f / Tc), 65536.0f / Tc);
+    if (!(hs_c > 1e-30f && hs_c < 1e30f)) return fail(4);
+    const float nhs = -hs_c;
+    const float hc = fmaf(smax + margin, hs_c, W1_MAGIC);
+    if (!(fabsf(hc) < 1e30f)) return fail(4);
+    for (int j = tid; j < W_NB; j += W_NT) hist[j] = 0;
+    __syncthreads();
+    float svmax = -INFINITY;
+    const uint32_t hb = smem_addr(hist);
+    // four sampled steps at a time: their loads are in flight together
+    for (int st0 = 0; st0 < sp.nst; st0 += 4 * W1_STRIDE) {
+      uint4 q[4 * EPI];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+#pragma unroll
+        for (int h = 0; h < EPI; h++) {
+          const int g = sp.first + (st0 + u * W1_STRIDE) * SV + lane + 32 * h;
+          q[u * EPI + h] = __ldg(rv.vbase + min(g, rv.nvec - 1));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        if (st0 + u * W1_STRIDE < sp.nst) {
+#pragma unroll
+          for (int h = 0; h < EPI; h++) {
+            const int g = sp.first + (st0 + u * W1_STRIDE) * SV + lane + 32 * h;
+            if (g < rv.nvec) {
+              rv.visit_raw(q[u * EPI + h], g, [&](float xv, int, int) {
+                svmax = maxnan(svmax, xv);
+                asm volatile("red.shared.add.u32 [%0], 1;" :: "r"(bucket_off1(xv, nhs, hc) + hb) : "memory");
+              });
+            }
+          }
+        }
+      }
+    }
+    const int bad_s = bu::max_i<W_NW>((svmax != svmax) ? 1 : 0, sc, tid);  // also orders the histogram
+    stamp(1);
+    svmax = okey_to_float(static_cast<uint32_t>(bu::max_u64<W_NW>(static_cast<unsigned long long>(okey(svmax)), sc, tid)));
+    if (bad_s || !(fmaf(svmax, nhs, hc) >= W1_MAGIC)) return fail(6);       // NaN, or a sampled logit above the anchor
+    // ---- the window from the sample's histogram: bucket b holds y = (anchor' - x) hs in
+    // [b - 1/8, b + 7/8], a width of w = 1 / (hs T) in units of x / T; masses relative to
+    // exp(anchor' / T) lie between exp(-(b + 7/8) w) and exp(-(b - 1/8) w). The bracket is the one of
+    // the two-pass front end, widened by the sampling error of a mass fraction estimated from n logits.
+    // Placing the window is a matter of speed, not of correctness (the pass checks it on the whole
+    // row): f32 and the fast exponential do.
+    constexpr int PER = W_NB / W_NT;
+    const double wd = 1.0 / (static_cast<double>(hs_c) * static_cast<double>(Tm));
+    const float wl2 = static_cast<float>(wd * 1.4426950408889634);        // bucket width in units of log2
+    const float ratio = ex2_approx(-wl2);
+    const float edge0 = ex2_approx(-(static_cast<float>(tid * PER) - 0.125f) * wl2);
+    float slo = 0.0f, shi = 0.0f;
+    int cnt_loc = 0, lowest = -1, top = W_NB;
+    uint32_t cnt[PER];                                                    // this thread's buckets, read once
+    {
+      const uint4* mine = reinterpret_cast<const uint4*>(hist) + tid * (PER / 4);
+#pragma unroll
+      for (int q = 0; q < PER / 4; q++) { const uint4 v = mine[q]; cnt[4 * q] = v.x; cnt[4 * q + 1] = v.y; cnt[4 * q + 2] = v.z; cnt[4 * q + 3] = v.w; }
+    }
+    {
+      float edge = edge0;
+#pragma unroll
+      for (int j = 0; j < PER; j++) {
+        const int b = tid * PER + j;
+        const int ci = static_cast<int>(cnt[j]);
+        const float c = static_cast<float>(ci);
+        const float ehi = edge;
+        edge *= ratio;
+        const float elo = (b == W_NB - 1) ? 0.0f : edge;
+        slo = fmaf(c, elo, slo); shi = fmaf(c, ehi, shi);
+        cnt_loc += ci;
+        if (ci) { lowest = b; top = min(top, b); }
+      }
+    }
+    double ex_lo, ex_hi, tot_lo, tot_hi;
+    bu::scan_excl_d2<W_NW>(static_cast<double>(slo), static_cast<double>(shi), ex_lo, ex_hi, tot_lo, tot_hi, sc, tid);
+    const int nsamp = bu::sum_i<W_NW>(cnt_loc, sc, tid);
+    int nlow = -lowest;                                                   // the lowest populated bucket as a minimum of negatives
+    bu::min_i2<W_NW>(top, nlow, sc, tid);
+    lowest = -nlow;
+    if (nsamp < 4096 || !(tot_lo > 0.0)) return fail(7);
+    // a few heavy tokens: the sample cannot place the cut (one token above a thousandth of the mass)
+    const double heavy = static_cast<double>(ex2_approx(-(static_cast<float>(top) - 0.125f) * wl2));
+    if (heavy > 1e-3 * tot_lo) return fail(8);
+    // five standard errors of a mass fraction estimated from nsamp logits
+    const double delta = 5.0 * sqrt(plim * fabs(1.0 - plim) / static_cast<double>(nsamp)) + 4.0 / static_cast<double>(nsamp);
+    const float p_lo = static_cast<float>(plim - delta), p_hi = static_cast<float>(plim + delta);
+    if (!(p_lo > 0.0f)) return fail(9);
+    int b1 = W_NB - 1, b2 = W_NB - 1, wcount = 0;
+    {
+      float edge = edge0, a_lo = static_cast<float>(ex_lo), a_hi = static_cast<float>(ex_hi);
+      const float t_lo = static_cast<float>(tot_lo), t_hi = static_cast<float>(tot_hi);
+#pragma unroll
+      for (int j = 0; j < PER; j++) {
+        const int b = tid * PER + j;
+        const float c = static_cast<float>(cnt[j]);
+        const float ehi = edge;
+        edge *= ratio;
+        const float elo = (b == W_NB - 1) ? 0.0f : edge;
+        a_lo = fmaf(c, elo, a_lo); a_hi = fmaf(c, ehi, a_hi);
+        const float den_hi = a_hi + (t_lo - a_lo), den_lo = a_lo + (t_hi - a_hi);
+        const bool c1 = a_hi >= p_lo * den_hi, c2 = a_lo >= p_hi * den_lo;
+        if (c1 && a_hi > 0.0f) b1 = min(b1, b);
+        if (c2 && a_lo > 0.0f) b2 = min(b2, b);
+      }
+    }
+    bu::min_i2<W_NW>(b1, b2, sc, tid);
+    if (b2 < b1) b2 = b1;
+    if (b1 > 0) b1--;                                                     // one bucket of slack for the f32 sums
+    if (b2 < W_NB - 1) b2++;
+#pragma unroll
+    for (int j = 0; j < PER; j++) { const int b = tid * PER + j; if (b >= b1 && b <= b2) wcount += static_cast<int>(cnt[j]); }
+    wcount = bu::sum_i<W_NW>(wcount, sc, tid);
+    // the window must stay small: its logits go through the exact list
+    if (static_cast<long long>(wcount) * W1_STRIDE > (W_ZCAP1 * 13) / 16) return fail(10);
+    bool ok = true;
+    xA = bucket_floor1(b1 - 1, nhs, hc, ok);
+    xB = bucket_floor1(b2, nhs, hc, ok);
+    if (!ok) return fail(11);
+    k.xA = xA; k.xB = xB;
+    const float xAc = fminf(xA, 3.0e38f), xBc = fmaxf(xB, -3.0e38f);
+    k.xmid = 0.5f * xAc + 0.5f * xBc;
+    k.xhalf = (0.5f * xAc - 0.5f * xBc) * 1.000001f + 1e-30f;
+    if (lowest >= 0 && lowest < W_NB - 1) {
+      const double dmax = (static_cast<double>(lowest) + 1.0) * wd + 1e-3;   // from the histogram's anchor down
+      eps = W1_EPS_FIXED + W1_EPS_PER_D * fmin(9.7, dmax);
+    }
+    __syncthreads();                                                      // the histogram area becomes the record list
+  }
+
+  stamp(2);
+  // ---- the pass
+  if (tid < npiece) part[tid] = 0.0;                                      // pieces past the row's end stay empty
+  if (tid == 0) sh.cnt = 0;
+  __syncthreads();
+  double Ssum = 0.0;
+  float vmax = -INFINITY;
+  double* part_w = part + warp * ppw;
+  if (cut_on) {
+    if (t_is_one) wide_onepass_stream<T, true, true>(sp, rv, lane, k, part_w, Ssum, vmax);
+    else wide_onepass_stream<T, false, true>(sp, rv, lane, k, part_w, Ssum, vmax);
+  } else {
+    if (t_is_one) wide_onepass_stream<T, true, false>(sp, rv, lane, k, part_w, Ssum, vmax);
+    else wide_onepass_stream<T, false, false>(sp, rv, lane, k, part_w, Ssum, vmax);
+  }
+  __syncthreads();
+  stamp(6);
+  const int anynan = bu::max_i<W_NW>((vmax != vmax) ? 1 : 0, sc, tid);
+  const float xmax = okey_to_float(static_cast<uint32_t>(bu::max_u64<W_NW>(static_cast<unsigned long long>(okey(vmax)), sc, tid)));
+  const float m = scale_t(xmax, Tm);
+  if (anynan || !(fabsf(m) < INFINITY)) return fail(12);                     // the two-pass front end reports such rows
+  // the fast sums round x/T - anchor where upstream rounds x/T - max: the two must be close for the
+  // heavy logits to keep the error budget (2e-7 per unit of distance)
+  if (!(fabsf(m - as) <= 2.0f)) return fail(13);
+  int nz = 0;
+  double S = bu::sum_d<W_NW>(Ssum, sc, tid);
+  nz = sh.cnt;
+  if (!(S > 0.0) || !(S < 1e300)) return fail(14);
+  // everything so far is relative to exp(anchor); the tail works relative to exp(max)
+  const double cf = exp(static_cast<double>(as) - static_cast<double>(m));
+  S *= cf;
+  if (tid < npiece) part[tid] *= cf;
+  __syncthreads();
+  double Ktot = 0.0;
+  if (cut_on) {
+    Ktot = bu::sum_d<W_NW>((tid < npiece) ? part[tid] : 0.0, sc, tid);
+    // ---- the window's logits: x -> d = x / T - max, in place, and their mass
+    if (nz > W_ZCAP1 || nz == 0) return fail(5);
+    double zmass = 0.0;
+    for (int j = tid; j < nz; j += W_NT) {
+      const uint2 e = zl[j];
+      const float d = scale_t(__uint_as_float(e.x), Tm) - m;
+      zl[j] = make_uint2(__float_as_uint(d), e.y);
+      zmass += exp_safe(d, s_tab);
+    }
+    zmass = bu::sum_d<W_NW>(zmass, sc, tid);
+    // the cut must lie inside the window by more than the error of the sums
+    const double etol = 1e-12 + 2.0 * plim * fabs(1.0 - plim) * eps + 1e-9;
+    if (!(Ktot / S < plim - etol) || !((Ktot + zmass) / S > plim + etol)) {
+      if (!(xB == -INFINITY && Ktot / S < plim - etol)) return fail(15);     // a window open at the bottom holds whatever is left
+    }
+  }
+  stamp(7);
+  out.m = m; out.S = S; out.Ktot = Ktot; out.nz = nz; out.xA = xA; out.xB = xB; out.eps = eps;
+  return true;
+}
+
 template <typename T>
 __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned char* dyn, WideShared& sh,
                          unsigned long long pol_keep, unsigned long long pol_drop) {
@@ -501,10 +987,9 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
   RowDebug dbg;
   dbg.sum_exp = 0; dbg.resum = 1.0; dbg.edge_lo = 0; dbg.edge_hi = 0; dbg.kept = 0;
   dbg.max_scaled = 0; dbg.threshold = __int_as_float(0x7fc00000); dbg.path = 2;
-  for (int q = 0; q < 8; q++) dbg.cycles[q] = 0;
+  for (int q = 0; q < 8; q++) dbg.reserved[q] = 0;
   long long tprev = clock64();
-  { unsigned long long gt; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt)); dbg.cycles[6] = static_cast<uint32_t>(gt); }
-  auto stamp = [&](int slot) { const long long now = clock64(); dbg.cycles[slot] = static_cast<uint32_t>(now - tprev); tprev = now; };
+  auto stamp = [&](int slot) { const long long now = clock64(); dbg.reserved[slot] = static_cast<uint32_t>(now - tprev); tprev = now; };
   auto write_row = [&](int id, uint32_t fl) {
     if (tid == 0) {
       A.out_ids[row_id] = id;
@@ -530,6 +1015,34 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
   const int npiece = W_NW * ppw;
   const WSpan sp = make_span<T>(rv, warp * span, span, lane);
 
+  // What the tail needs of the row, from either front end.
+  float m = 0.0f, dlow = -INFINITY;
+  float dA = -INFINITY, dB = -INFINITY;    // certainly kept: d >= dA; zone: dB <= d < dA; dropped: d < dB
+  bool fast_ok = false;
+  double S = 0.0, Ktot = 0.0;
+  int nz = 0;
+  // one-pass front end: thresholds on the raw logits (xs), its own error bound and list capacity
+  bool xs = false;
+  int onepass_why = 0;
+  float xA = -INFINITY, xB = -INFINITY;
+  double eps_rel = W_EXP_REL_ERR;
+  int zcap = W_ZCAP;
+  {
+    OnePassOut fo;
+    fo.nz = 0;
+    if (wide_front_onepass<T>(BA, row_id, rv, sp, dyn, sh, cfg, cut_on, span, ppw, npiece, fo, dbg.reserved)) {
+      xs = true;
+      m = fo.m; S = fo.S; Ktot = fo.Ktot; nz = fo.nz; xA = fo.xA; xB = fo.xB; eps_rel = fo.eps; zcap = W_ZCAP1;
+      fast_ok = true;
+      dlow = -INFINITY;
+      dB = (xB == -INFINITY) ? -INFINITY : 0.0f;             // "logits below the zone may exist"
+      dbg.max_scaled = m;
+      dbg.path = 3;
+    } else {
+      onepass_why = fo.nz;
+    }
+  }
+  if (!xs) {
   // ---- a sample of the row (every warp's first step) gives an upper estimate of the maximum
   // and the bucket width, so that pass 1 can already count the histogram the cut needs
   bool anchored = false;
@@ -579,7 +1092,7 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
   const int anynan = bu::max_i<W_NW>(nan_seen ? 1 : 0, sc, tid);
   xmax = okey_to_float(static_cast<uint32_t>(bu::max_u64<W_NW>(static_cast<unsigned long long>(okey(xmax)), sc, tid)));
   xmin = okey_to_float(static_cast<uint32_t>(bu::min_u64<W_NW>(static_cast<unsigned long long>(okey(xmin)), sc, tid)));
-  const float m = scale_t(xmax, Tm);
+  m = scale_t(xmax, Tm);
   dbg.max_scaled = m;
   stamp(0);
   // A NaN anywhere, or an infinite maximum, makes the softmax sum NaN upstream
@@ -590,11 +1103,10 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     write_row(V - 1, flags | FLAG_NONFINITE | FLAG_FALLBACK);
     return;
   }
-  const float dlow = scale_t(xmin, Tm) - m;                  // smallest d of the row (-Inf with a -Inf logit)
-  const bool fast_ok = (dlow > -31.9f);                      // every d inside the bucket table's range
+  dlow = scale_t(xmin, Tm) - m;                  // smallest d of the row (-Inf with a -Inf logit)
+  fast_ok = (dlow > -31.9f);                      // every d inside the bucket table's range
 
   // ---- bracket of the cut from the count histogram
-  float dA = -INFINITY, dB = -INFINITY;    // certainly kept: d >= dA; zone: dB <= d < dA; dropped: d < dB
   if (cut_on) {
     // The histogram of pass 1 counts q = s - anchor; it stands when no logit lies above the anchor.
     // Mass bounds relative to exp(anchor) serve as well as bounds relative to exp(max): only their
@@ -701,20 +1213,26 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
 #undef GS_P3
   __syncthreads();
   if (lane != 0) Ksum = 0.0;                                 // kept mass is already warp-reduced into lane 0
-  double S = Ssum, Ktot = Ksum, unused = 0.0;
+  double unused = 0.0;
+  S = Ssum; Ktot = Ksum;
   bu::sum_d3<W_NW>(S, Ktot, unused, sc, tid);
-  const int nz = sh.cnt;
+  nz = sh.cnt;
   stamp(2);
+  dbg.reserved[6] = static_cast<uint32_t>(onepass_why);     // why the row took two passes
+  }  // two-pass front end
   // A zone that outgrew the list (long runs of equal logits around the cut): the same selection
   // runs over the row itself, one more pass per round.
-  const bool big = cut_on && nz > W_ZCAP;
+  const bool big = cut_on && nz > zcap;
   dbg.sum_exp = S;
 
   // ---- exact cut inside the zone by weighted selection
   unsigned long long cut_key = 0ull;       // zone entries are kept when key < cut_key, or == with cut_incl
   int cut_incl = 0;
   bool bad = false;
-  if (big) {
+  if (big && xs) {
+    if (tid == 0) hand_to_single(BA, row_id);
+    return;
+  } else if (big) {
     if (!wide_big_zone<T>(sp, rv, pol_keep, sh, hist, part, s_tab, m, Tm, dA, dB, dlow, mode, plim, S, Ktot, fast_ok,
                           span, ppw, cut_key, cut_incl, flags)) {
       if (tid == 0) hand_to_single(BA, row_id);
@@ -822,8 +1340,15 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     }
     if (!bad && !all_in) {
       // the sums carry exp_fast_s's error; in G/S >= p it enters as 2 p (1-p) times that bound
-      const double etol = 1e-12 + (fast_ok ? 2.0 * plim * fabs(1.0 - plim) * W_EXP_REL_ERR : 0.0);
+      const double etol = 1e-12 + (fast_ok ? 2.0 * plim * fabs(1.0 - plim) * eps_rel : 0.0);
       if (fabs(g_at / S - plim) <= etol || fabs(g_before / S - plim) <= etol) flags |= FLAG_TOPP_EDGE;
+      if (xs) {
+        // Several logits can share one d, and the order among equal d is by index: a cut whose d is also
+        // the d of a logit outside the window (at its upper or lower edge) is decided on the whole row.
+        const float dc = zone_key_d(cut_key);
+        if (xA < INFINITY && dc == scale_t(xA, Tm) - m) bad = true;
+        if (xB > -INFINITY && dc == scale_t(nextafterf(xB, -INFINITY), Tm) - m) bad = true;
+      }
       if (mode == 1) {
         // a later key with the same d as c*: the cut separates equal probabilities
         int tie = 0;
@@ -865,8 +1390,8 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     if (i < 0 || i >= V) return 0.0;
     const float s = t_is_one ? xv : __fdiv_rn(xv, Tm);
     const float d = s - m;
-    if (d < dA) {
-      if (!(d >= dB)) return 0.0;
+    if (xs ? (cut_on && !(xv >= xA)) : (d < dA)) {
+      if (xs ? !(xv >= xB) : !(d >= dB)) return 0.0;
       const unsigned long long k = zone_key(d, i, mode);
       if (!(k < cut_key || (cut_incl && k == cut_key))) return 0.0;
     }
@@ -952,7 +1477,6 @@ __device__ void wide_row(const BatchArgs& BA, const int64_t row_id, unsigned cha
     if (u - run_end / Re <= 1e-6) flags |= FLAG_BOUNDARY;
   }
   stamp(5);
-  { uint32_t smid; asm volatile("mov.u32 %0, %smid;" : "=r"(smid)); dbg.cycles[7] = smid; }
   write_row(id, flags);
 }
 

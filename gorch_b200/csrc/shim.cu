@@ -79,13 +79,14 @@ struct Ctx {
 // Work lists for gorch_cuda_sample_dev_static: fixed storage inside the loaded module, so the
 // entry point never allocates. Every GPU that loads the library holds one copy (about 16 KB)
 // until the process exits. In host code this name is only a handle for cudaGetSymbolAddress;
-// the device address is looked up once per device (static_lists_ptr) and passed to the kernels.
+// the device address is looked up once per device (static_lists_ptr, called by gorch_cuda_create_ctx with
+// that device current) and passed to the kernels.
 constexpr int64_t kStaticMaxRows = 4096;
 static __device__ __align__(256) int32_t g_static_worklists[16 + kStaticMaxRows + 1];
 constexpr int kMaxDevices = 64;
 int32_t* g_static_ptr[kMaxDevices] = {};
 
-// Device address of g_static_worklists on the CURRENT device (looked up on first use there).
+// Device address of g_static_worklists on the CURRENT device (looked up once per device).
 int static_lists_ptr(int device, int32_t** out, char** errOut);
 
 void set_err(char** errOut, const char* fmt, ...) {
@@ -165,7 +166,9 @@ size_t elem_size(int dtype) { return dtype == GORCH_CUDA_BF16 ? 2 : 4; }
 int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int64_t row_stride,
                 const GorchSampleCfg* cfgs, const double* uniforms, int32_t* out_ids,
                 uint32_t* out_flags, double* out_probs, GorchSampleDebug* out_debug,
-                int force_greedy, char** errOut) {
+                int force_greedy, char** errOut, int32_t* fixed_lists = nullptr) {
+  // fixed_lists: caller-provided storage for the row work lists (16 + B + 1 words) instead of the
+  // context's grow-only allocation; with it nothing in here allocates.
   if (B == 0) return GORCH_CUDA_OK;
   static_assert(sizeof(GorchSampleCfg) == sizeof(gs::RowCfg), "cfg layout");
   static_assert(sizeof(GorchSampleDebug) == sizeof(gs::RowDebug), "debug layout");
@@ -198,9 +201,12 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
   if (batch_mode) {
     // narrow (greedy / top-k) beside wide (top-k off), then single-CTA (whatever was handed over)
     const size_t ints = 16 + static_cast<size_t>(B) + 1;
-    int rc = ensure(c->worklist, ints * sizeof(int32_t), errOut);
-    if (rc) return rc;
-    int32_t* base = static_cast<int32_t*>(c->worklist.ptr);
+    int32_t* base = fixed_lists;
+    if (!base) {
+      int rc = ensure(c->worklist, ints * sizeof(int32_t), errOut);
+      if (rc) return rc;
+      base = static_cast<int32_t*>(c->worklist.ptr);
+    }
     gs::BatchArgs ba;
     ba.k = a;
     ba.eb_table = c->eb_table;
@@ -220,21 +226,21 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
     gs::KernelArgs aw = a;
     aw.worklist = ba.list_single;
     // The narrow and the wide kernel work on disjoint rows: the wide one runs on a side stream
-    // (fork after the classification, join before the hand-over kernel), so that a mixed batch
+    // (fork before, join before the hand-over kernel), so that a mixed batch
     // does not pay for them one after the other.
     if (!force_greedy) {
       CUDA_TRY(cudaEventRecord(c->ev_fork, c->stream), errOut);
       CUDA_TRY(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0), errOut);
+      if (dtype == GORCH_CUDA_F32) {
+        if (wide_big_ctas) gs::w1024::wide_rows_kernel<float><<<gw, gs::w1024::W_NT, gs::w1024::W_DYN_BYTES, c->side_stream>>>(ba);
+        else gs::w256::wide_rows_kernel<float><<<gw, gs::w256::W_NT, gs::w256::W_DYN_BYTES, c->side_stream>>>(ba);
+      } else {
+        if (wide_big_ctas) gs::w1024::wide_rows_kernel<uint16_t><<<gw, gs::w1024::W_NT, gs::w1024::W_DYN_BYTES, c->side_stream>>>(ba);
+        else gs::w256::wide_rows_kernel<uint16_t><<<gw, gs::w256::W_NT, gs::w256::W_DYN_BYTES, c->side_stream>>>(ba);
+      }
     }
-    if (dtype == GORCH_CUDA_F32) {
-      if (!force_greedy && wide_big_ctas) gs::w1024::wide_rows_kernel<float><<<gw, gs::w1024::W_NT, gs::w1024::W_DYN_BYTES, c->side_stream>>>(ba);
-      else if (!force_greedy) gs::w256::wide_rows_kernel<float><<<gw, gs::w256::W_NT, gs::w256::W_DYN_BYTES, c->side_stream>>>(ba);
-      gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-    } else {
-      if (!force_greedy && wide_big_ctas) gs::w1024::wide_rows_kernel<uint16_t><<<gw, gs::w1024::W_NT, gs::w1024::W_DYN_BYTES, c->side_stream>>>(ba);
-      else if (!force_greedy) gs::w256::wide_rows_kernel<uint16_t><<<gw, gs::w256::W_NT, gs::w256::W_DYN_BYTES, c->side_stream>>>(ba);
-      gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-    }
+    if (dtype == GORCH_CUDA_F32) gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
+    else gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
     if (!force_greedy) {
       CUDA_TRY(cudaEventRecord(c->ev_join, c->side_stream), errOut);
       CUDA_TRY(cudaStreamWaitEvent(c->stream, c->ev_join, 0), errOut);
@@ -273,14 +279,18 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
       }
       CUDA_TRY(cudaGetLastError(), errOut);
     } else {
-      int rc = ensure(c->worklist, (static_cast<size_t>(B) + 1) * sizeof(int32_t), errOut);
-      if (rc) return rc;
-      CUDA_TRY(cudaMemsetAsync(c->worklist.ptr, 0, sizeof(int32_t), c->stream), errOut);
+      int32_t* wl = fixed_lists;
+      if (!wl) {
+        int rc = ensure(c->worklist, (static_cast<size_t>(B) + 1) * sizeof(int32_t), errOut);
+        if (rc) return rc;
+        wl = static_cast<int32_t*>(c->worklist.ptr);
+      }
+      CUDA_TRY(cudaMemsetAsync(wl, 0, sizeof(int32_t), c->stream), errOut);
       gs::ClusterArgs ca;
       ca.k = a;
       ca.slice_bytes = static_cast<int32_t>(need > gs::MIN_SLICE_BYTES ? need : gs::MIN_SLICE_BYTES);
       ca.eb_table = c->eb_table;
-      ca.worklist = static_cast<int32_t*>(c->worklist.ptr);
+      ca.worklist = wl;
       const size_t dyn = static_cast<size_t>(ca.slice_bytes) + gs::REGION_A + gs::REGION_B;
       cudaLaunchConfig_t lc = {};
       lc.gridDim = dim3(static_cast<unsigned>(B * C));
@@ -432,6 +442,16 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   if ((e = cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming)) != cudaSuccess) return fail("cudaEventCreate", e);
   if ((e = cudaEventCreate(&c->ev0)) != cudaSuccess) return fail("cudaEventCreate", e);
   if ((e = cudaEventCreate(&c->ev1)) != cudaSuccess) return fail("cudaEventCreate", e);
+  {
+    // device address of the fixed work-list array of gorch_cuda_sample_dev_static on this device
+    int32_t* unused = nullptr;
+    char* msg = nullptr;
+    if (static_lists_ptr(device, &unused, &msg) != GORCH_CUDA_OK) {
+      if (errOut) *errOut = msg; else free(msg);
+      gorch_cuda_release(c);
+      return nullptr;
+    }
+  }
   double tab[256];
   for (int j = 0; j < 256; j++) tab[j] = static_cast<double>(exp2l(static_cast<long double>(j) / 256.0L));
   if ((e = cudaMalloc(&c->exp_table, sizeof tab)) != cudaSuccess) return fail("cudaMalloc(exp table)", e);
@@ -449,11 +469,11 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   if ((e = cudaFuncSetAttribute(gs::multinomial_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::MN_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::vocab_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::VM_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::w256::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w256::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::w1024::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w1024::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::w1024::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w1024::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::row_softmax_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::RS_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::row_softmax_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::RS_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
-  if ((e = cudaFuncSetAttribute(gs::w1024::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w1024::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::w256::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w256::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
-  if ((e = cudaFuncSetAttribute(gs::w1024::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w1024::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   return c;
 }
 
@@ -770,7 +790,7 @@ static int launch_generate_control(Ctx* c, const int32_t* ids, const uint32_t* f
   a.window_start = gc->window_start; a.live_count = gc->live_count;
   for (int i = 0; i < GORCH_GEN_MAX_STOPS; i++) a.stops[i] = (i < gc->n_stop && gc->stop_tokens[i] >= 0) ? gc->stop_tokens[i] : -1;
   a.n_stop = gc->n_stop; a.max_new = gc->max_new; a.max_seq = gc->max_seq; a.cached = gc->cached ? 1 : 0;
-  a.bad_flags = GORCH_FLAG_INTERNAL | GORCH_FLAG_BAD_CFG | GORCH_FLAG_TIMEOUT;
+  a.bad_flags = GORCH_FLAG_INTERNAL | GORCH_FLAG_BAD_CFG;
   a.B = static_cast<int>(B);
   gs::generate_control_kernel<<<1, gs::GC_NT, 0, c->stream>>>(a);
   CUDA_TRY(cudaGetLastError(), errOut);
@@ -961,52 +981,11 @@ int gorch_cuda_sample_dev_static(GorchCudaCtxRef ctx, const void* logits, int dt
   }
   CUDA_TRY(cudaSetDevice(c->device), errOut);
   int32_t* base = nullptr;
-  if ((rc = static_lists_ptr(c->device, &base, errOut))) return rc;   // first call per device: symbol lookup
-  gs::BatchArgs ba;
-  ba.k.logits = logits;
-  ba.k.row_stride = row_stride;
-  ba.k.V = static_cast<int32_t>(V);
-  ba.k.force_greedy = 0;
-  ba.k.cfgs = reinterpret_cast<const gs::RowCfg*>(cfgs);
-  ba.k.uniforms = uniforms;
-  ba.k.out_ids = out_ids;
-  ba.k.out_flags = out_flags;
-  ba.k.out_probs = nullptr;
-  ba.k.out_debug = nullptr;
-  ba.k.vs_records = nullptr;
-  ba.k.vs_col_offset = 0;
-  ba.k.tk_values = nullptr;
-  ba.k.tk_indices = nullptr;
-  ba.k.tk_k = 0;
-  ba.k.exp_table = c->exp_table;
-  ba.k.row_offset = 0;
-  ba.k.worklist = nullptr;
-  ba.eb_table = c->eb_table;
-  ba.hdr = base;
-  ba.list_single = base + 15;
-  ba.B = B;
-  // the array keeps the previous call's contents: the cursors and the hand-over count (the
-  // header's 16 words) must start at zero
-  CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
-  const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
-  const unsigned gw = static_cast<unsigned>(B < gs::w256::W_CTAS * c->sm_count ? B : gs::w256::W_CTAS * c->sm_count);
-  const unsigned gsgl = static_cast<unsigned>(B < 2 * c->sm_count ? B : 2 * c->sm_count);
-  gs::KernelArgs aw = ba.k;
-  aw.worklist = ba.list_single;
-  if (dtype == GORCH_CUDA_F32) {
-    gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-    gs::w256::wide_rows_kernel<float><<<gw, gs::w256::W_NT, gs::w256::W_DYN_BYTES, c->stream>>>(ba);
-    gs::sample_rows_kernel<float><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
-  } else {
-    gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-    gs::w256::wide_rows_kernel<uint16_t><<<gw, gs::w256::W_NT, gs::w256::W_DYN_BYTES, c->stream>>>(ba);
-    gs::sample_rows_kernel<uint16_t><<<gsgl, gs::NT, gs::POOL_BYTES, c->stream>>>(aw);
-  }
-  CUDA_TRY(cudaGetLastError(), errOut);
-  c->counters.kernel_launches += 3;
-  c->counters.sample_launches++;
-  c->counters.rows += static_cast<uint64_t>(B);
-  return GORCH_CUDA_OK;
+  if ((rc = static_lists_ptr(c->device, &base, errOut))) return rc;   // looked up when the context was created
+  // the same dispatch as gorch_cuda_sample_dev, with the work lists in the fixed array (it keeps the
+  // previous call's contents: the dispatch clears the cursors and counts it uses before every launch)
+  return launch_rows(c, logits, dtype, B, V, row_stride, cfgs, uniforms, out_ids, out_flags, nullptr, nullptr, 0,
+                     errOut, base);
 }
 
 }  // extern "C"

@@ -25,7 +25,7 @@ from .config import (CFG_DTYPE, DTYPE_BF16, DTYPE_F32, MODE_A, MODE_B, GenerateC
 DEBUG_DTYPE = np.dtype(
     [("sum_exp", "<f8"), ("resum", "<f8"), ("edge_lo", "<f8"), ("edge_hi", "<f8"),
      ("kept", "<i4"), ("max_scaled", "<f4"), ("threshold", "<f4"), ("path", "<i4"),
-     ("cycles", "<u4", (8,))]
+     ("reserved", "<u4", (8,))]
 )
 
 

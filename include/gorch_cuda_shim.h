@@ -31,7 +31,6 @@ typedef void* GorchCudaBufferRef; /* device allocation; cf. MTLBufferRef */
 #define GORCH_CUDA_ERR_BAD_ARG 1
 #define GORCH_CUDA_ERR_CUDA 2
 #define GORCH_CUDA_ERR_NCCL 3
-#define GORCH_CUDA_ERR_TIMEOUT 4
 #define GORCH_CUDA_ERR_LIMIT 5
 
 /* Element types of a logits tensor. bf16 rows are upcast in-kernel by
@@ -48,7 +47,6 @@ typedef void* GorchCudaBufferRef; /* device allocation; cf. MTLBufferRef */
 #define GORCH_FLAG_FALLBACK 0x002u     /* walk fell through: id = V-1 (model/generate.go:239) */
 #define GORCH_FLAG_NONFINITE 0x004u    /* NaN/Inf poisoned the softmax; id = V-1 as upstream */
 #define GORCH_FLAG_TIE_CUT 0x008u      /* mode B cut separates equal probabilities */
-#define GORCH_FLAG_TIMEOUT 0x010u      /* a bounded device-side wait gave up */
 #define GORCH_FLAG_TOPP_EDGE 0x020u    /* top-p stop test decided within 1e-12 of its threshold */
 #define GORCH_FLAG_GENERAL_PATH 0x040u /* informational: row took the full-row path */
 #define GORCH_FLAG_INTERNAL 0x080u     /* an internal invariant failed; id = -1 or unreliable */
@@ -75,7 +73,7 @@ typedef struct {
   float max_scaled; /* max of logits/T (generate.go:167-172) */
   float threshold;  /* top-k threshold (generate.go:158); NaN when inactive */
   int32_t path;     /* 0 greedy, 1 small-set path, 2 full-row path */
-  uint32_t cycles[8]; /* SM clock ticks per phase of the row (rank 0 of the cluster) */
+  uint32_t reserved[8]; /* unspecified */
 } GorchSampleDebug;
 
 typedef struct {
@@ -104,14 +102,14 @@ int gorch_cuda_set_stream(GorchCudaCtxRef ctx, void* stream, int external, char*
 /* Record device time of each call into counters.last_kernel_ms (adds a sync). */
 int gorch_cuda_set_timing(GorchCudaCtxRef ctx, int on);
 int gorch_cuda_get_counters(GorchCudaCtxRef ctx, GorchCudaCounters* out);
-/* Which kernels serve the sampling calls. variant 0 (default): by batch size
- * (large batches: the narrow and wide kernels, each taking the rows of its
- * kind; small ones: one thread-block cluster per row); 1: one CTA per row
- * re-reading global memory (an independent second implementation); 2: force the
- * large-batch kernels; 3: force the cluster kernel; 4 / 5: as 2, with the wide
- * kernel's 256-thread (four CTAs per SM) / 1024-thread (one CTA per SM)
- * instance forced instead of chosen by batch size. cluster_size 0 picks the
- * cluster size from the shape; 1, 2, 4, 8 force it. */
+/* Test hook, not part of the drop-in surface: which kernels serve the sampling calls, so that the
+ * parity tests can run every kernel on every case. variant 0 (default): by batch size (large
+ * batches: the narrow and wide kernels, each taking the rows of its kind; small ones: one
+ * thread-block cluster per row with the row held in shared memory); 1: one CTA per row re-reading
+ * global memory (an independent second implementation); 2: force the large-batch kernels; 3: force
+ * the shared-memory cluster kernel; 4 / 5: as 2, with the wide kernel's 256-thread (four CTAs per
+ * SM) / 1024-thread (one CTA per SM) instance forced instead of chosen by batch size. cluster_size
+ * 0 picks the cluster size of variant 3 from the shape; 1, 2, 4, 8 force it. */
 int gorch_cuda_set_kernel_variant(GorchCudaCtxRef ctx, int variant, int cluster_size, char** errOut);
 
 /* ---- device buffers: replaces metal_create_shared_buffer /
@@ -154,20 +152,20 @@ int gorch_cuda_sample_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, in
                           const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
                           double* out_probs, GorchSampleDebug* out_debug, char** errOut);
 
-/* No counterpart in the reference. Same work and same results as gorch_cuda_sample_dev
- * (without the optional probability / diagnostic outputs), for callers that must not
- * trigger a device allocation: a decode loop that is being recorded into a CUDA stream
- * capture, where cudaMalloc is not permitted, or a serving process whose memory budget is
- * fixed up front and that treats any later cudaMalloc (which also synchronises the device)
- * as a fault. The row work lists that the other entry point keeps in a grow-only
- * cudaMalloc'd buffer live here in a fixed array inside the library image: about 16 KB of
- * device memory on every GPU that loads the library, held until the process exits.
+/* No counterpart in the reference. Same work, same dispatch and same results as
+ * gorch_cuda_sample_dev (without the optional probability / diagnostic outputs), for callers that
+ * must not trigger a device allocation: a decode loop that is being recorded into a CUDA stream
+ * capture, where cudaMalloc is not permitted, or a serving process whose memory budget is fixed up
+ * front and that treats any later cudaMalloc (which also synchronises the device) as a fault. The
+ * row work lists that the other entry point keeps in a grow-only cudaMalloc'd buffer live here in
+ * a fixed array inside the library image: about 16 KB of device memory on every GPU that loads the
+ * library, held until the process exits.
  *   - at most 4096 rows per call; more is refused with GORCH_CUDA_ERR_LIMIT;
- *   - the first call on a device looks up the array's device address
- *     (cudaGetSymbolAddress); make that first call before starting a stream capture;
- *   - all calls on a device share the one array: two calls whose kernels overlap on the
- *     GPU (different streams or contexts) race on it. Calls on one stream are safe: the
- *     counters are cleared at the start of every call;
+ *   - the array's device address is looked up (cudaGetSymbolAddress) when a context is created
+ *     on the device, not inside this call;
+ *   - all calls on a device share the one array: two calls whose kernels overlap on the GPU
+ *     (different streams or contexts) race on it. Calls on one stream are safe: the cursors and
+ *     counts are cleared at the start of every call;
  *   - neither this function nor anything it calls uses cudaMalloc or cudaFree. */
 int gorch_cuda_sample_dev_static(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
                                  int64_t V, int64_t row_stride, const GorchSampleCfg* cfgs,
@@ -226,8 +224,8 @@ int gorch_cuda_multinomial_dev(GorchCudaCtxRef ctx, const float* probs, int64_t 
  * => GORCH_GEN_MAX_SEQ (generate.go:121-123), else next_input[b] = id and cache_len[b]++;
  * cached == 0: next_input[b] = id and window_start[b] (may be NULL) = start of the last max_seq
  * tokens of the row (generate.go:62-65). A row whose max_new-th token was just appended becomes
- * GORCH_GEN_MAX_NEW at once. An id < 0, a sampler flag in GORCH_FLAG_INTERNAL | GORCH_FLAG_BAD_CFG |
- * GORCH_FLAG_TIMEOUT (flags may be NULL) or a full token buffer => GORCH_GEN_ERROR, nothing appended.
+ * GORCH_GEN_MAX_NEW at once. An id < 0, a sampler flag in GORCH_FLAG_INTERNAL | GORCH_FLAG_BAD_CFG
+ * (flags may be NULL) or a full token buffer => GORCH_GEN_ERROR, nothing appended.
  * live_count[0] = rows still live after the step.
  *
  * Before the first step the caller fills tokens/lengths with the prompts (cached loops of

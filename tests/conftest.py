@@ -19,8 +19,9 @@ def oracle():
     return orc
 
 
-# every GPU test runs against each kernel configuration: the cluster kernel with
-# its automatic cluster size and with forced sizes, and the single-CTA kernel
+# every GPU test runs against each kernel configuration: the default dispatch, the large-batch
+# kernels (wide kernel instance chosen by the batch, or forced), the shared-memory cluster kernel
+# with its automatic and forced sizes, and the single-CTA kernel
 VARIANTS = {"auto": (0, 0), "batch": (2, 0), "batch_w256": (4, 0), "batch_w1024": (5, 0), "cluster1": (3, 1), "cluster2": (3, 2), "cluster4": (3, 4),
             "cluster8": (3, 8), "single_cta": (1, 0)}
 
