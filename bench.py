@@ -78,7 +78,7 @@ def workload_config(w, args, world):
     return {
         "workload": w.name, "rows_per_gpu": int(w.B), "vocab": int(w.V), "logits_dtype": w.dtype,
         "topp_mode": "A(model/generate.go)" if mode == 0 else "B(model/qwen/generate.go)",
-        "sharding": (f"vocab x{world}, one all-gather of {world}x{int(w.B)} records" if args.vocab_sharded
+        "sharding": (f"vocab x{world}, one ncclAllGather of {world}x{int(w.B)} records inside the library call" if args.vocab_sharded
                      else f"rows x{world}, no collective"),
         "l2": "inputs larger than L2" if w.logits.nbytes > L2_BYTES else "L2 flushed between steps",
     }
@@ -442,29 +442,18 @@ def main():
     phases = None
 
     if args.vocab_sharded:
+        from gorch_b200 import distributed
         lo, hi = workloads.shard_vocab(V, rank, world)
         d_slice = db.d_logits[:, lo:hi].contiguous()
         db.d_logits = None
-        rec_bytes = sampling.VS_RECORD_BYTES
-        d_rec = torch.empty((B, rec_bytes), dtype=torch.uint8, device="cuda")
-        d_all = torch.empty((world, B, rec_bytes), dtype=torch.uint8, device="cuda")
+        distributed.init_vocab_comm(smp, rank, world)       # the library's own NCCL communicator
+        max_k = int(w.cfgs["top_k"].max())
         if main_flush is None and d_slice.numel() * d_slice.element_size() <= L2_BYTES:
             main_flush = flush if flush is not None else torch.empty(256 * 2 ** 20, dtype=torch.uint8, device="cuda")
         torch.cuda.synchronize()
-        pe = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
 
         def step():  # noqa: F811
-            pe[0].record(stream)
-            smp.vocab_local_ptrs(d_slice.data_ptr(), dt_code, B, hi - lo, hi - lo, lo, db.d_cfgs.data_ptr(), d_rec.data_ptr())
-            pe[1].record(stream)
-            if world > 1:
-                dist.all_gather_into_tensor(d_all.view(-1), d_rec.view(-1))
-            else:
-                d_all[0].copy_(d_rec)
-            pe[2].record(stream)
-            smp.vocab_merge_ptrs(d_all.data_ptr(), world, B, V, db.d_cfgs.data_ptr(), db.d_uni.data_ptr(),
-                                 d_ids.data_ptr(), d_flags.data_ptr())
-            pe[3].record(stream)
+            distributed.sample_vocab_sharded_device(smp, d_slice, db.d_cfgs, db.d_uni, d_ids, d_flags, V, rank, world, max_k)
 
     def barrier():
         if world > 1:
@@ -493,8 +482,18 @@ def main():
     kernel_ms = [a.elapsed_time(b) for a, b in evs]
     total_ms = float(sum(kernel_ms))          # device time of the K steps (flush writes excluded)
     if args.vocab_sharded:
-        phases = {"local_us": round(pe[0].elapsed_time(pe[1]) * 1e3, 1), "all_gather_us": round(pe[1].elapsed_time(pe[2]) * 1e3, 1),
-                  "merge_us": round(pe[2].elapsed_time(pe[3]) * 1e3, 1), "of": "the last timed step on rank 0"}
+        # per-phase device times of one more step (the timing switch adds a sync, so not inside the timed region)
+        smp.set_timing(True)
+        step()
+        torch.cuda.synchronize()
+        cn = smp.counters()
+        smp.set_timing(False)
+        cand = ((max_k + max_k // 4 + 8 + 7) // 8) * 8 if 0 < max_k <= sampling.VS_CAND else sampling.VS_CAND
+        cand = min(cand, sampling.VS_CAND)
+        phases = {"local_us": round(cn["vs_local_ms"] * 1e3, 1), "all_gather_us": round(cn["vs_gather_ms"] * 1e3, 1),
+                  "merge_us": round(cn["vs_merge_ms"] * 1e3, 1), "record_bytes": 16 + 8 * cand,
+                  "gathered_bytes_per_rank": int(B * (16 + 8 * cand) * world),
+                  "of": "one extra step on rank 0, CUDA events inside the library call"}
     timed_ids, timed_flags = d_ids.cpu().numpy().copy(), d_flags.cpu().numpy().copy()
     # keep the load on for a moment if the timed region was too short for NVML to see it
     t_end = time.perf_counter() + (0.0 if args.profile else max(0.0, 0.6 - total_ms / 1e3))

@@ -20,6 +20,7 @@ EXPORTS = [
     "gorch_cuda_sample_host", "gorch_cuda_sample_dev", "gorch_cuda_sample_dev_static", "gorch_cuda_sample_row",
     "gorch_cuda_argmax_host", "gorch_cuda_argmax_dev",
     "gorch_cuda_vocab_local_dev", "gorch_cuda_vocab_merge_dev",
+    "gorch_cuda_comm_unique_id", "gorch_cuda_comm_init", "gorch_cuda_comm_release", "gorch_cuda_sample_vocab_sharded_dev",
     "gorch_cuda_topk_dev", "gorch_cuda_multinomial_dev",
     "gorch_cuda_generate_control_dev", "gorch_cuda_generate_step_dev",
     "gorch_cuda_softmax_dev", "gorch_cuda_cross_entropy_fwd_dev", "gorch_cuda_cross_entropy_bwd_dev",
@@ -43,6 +44,7 @@ class Counters(C.Structure):
     _fields_ = [
         ("sample_launches", C.c_uint64), ("kernel_launches", C.c_uint64), ("argmax_launches", C.c_uint64), ("rows", C.c_uint64),
         ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64), ("last_kernel_ms", C.c_float),
+        ("vs_local_ms", C.c_float), ("vs_gather_ms", C.c_float), ("vs_merge_ms", C.c_float),
     ]
 
 
@@ -85,6 +87,10 @@ def load() -> C.CDLL:
         "gorch_cuda_argmax_dev": (i32, [p, p, i32, i64, i64, i64, p, err]),
         "gorch_cuda_vocab_local_dev": (i32, [p, p, i32, i64, i64, i64, i64, p, p, err]),
         "gorch_cuda_vocab_merge_dev": (i32, [p, p, i32, i64, i64, p, p, p, p, err]),
+        "gorch_cuda_comm_unique_id": (i32, [p, err]),
+        "gorch_cuda_comm_init": (i32, [p, i32, i32, p, err]),
+        "gorch_cuda_comm_release": (i32, [p, err]),
+        "gorch_cuda_sample_vocab_sharded_dev": (i32, [p, p, i32, i64, i64, i64, i64, i64, i32, p, p, p, p, err]),
         "gorch_cuda_topk_dev": (i32, [p, p, i32, i64, i64, i64, i64, p, p, p, err]),
         "gorch_cuda_multinomial_dev": (i32, [p, p, i64, i64, i64, p, p, p, err]),
         "gorch_cuda_softmax_dev": (i32, [p, p, i32, i64, i64, i64, p, i64, i32, err]),

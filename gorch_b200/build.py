@@ -10,7 +10,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libgorchcuda.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-shared", "-Xcompiler", "-fPIC",
+    "-shared", "-Xcompiler", "-fPIC", "-ldl",
 ]
 
 SOURCES = ["shim.cu"]

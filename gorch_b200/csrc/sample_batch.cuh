@@ -53,6 +53,13 @@ struct VsRecord {
   uint2 cand[VS_CAND];     // (logit bits, global index)
 };
 static_assert(sizeof(VsRecord) == 16 + 8 * VS_CAND, "record layout is part of the C ABI");
+// Record `row` of an array whose records hold `cand` candidates each (16 + 8 * cand bytes apart).
+__device__ __forceinline__ VsRecord& vs_record(void* base, int64_t row, int cand) {
+  return *reinterpret_cast<VsRecord*>(static_cast<unsigned char*>(base) + row * (16 + 8 * static_cast<int64_t>(cand)));
+}
+__device__ __forceinline__ const VsRecord& vs_record(const void* base, int64_t row, int cand) {
+  return *reinterpret_cast<const VsRecord*>(static_cast<const unsigned char*>(base) + row * (16 + 8 * static_cast<int64_t>(cand)));
+}
 
 struct BatchArgs {
   KernelArgs k;
@@ -283,7 +290,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     if (x0 != x0 && (!A.vs_records || A.vs_col_offset == 0)) id = 0;
     if (A.vs_records) {                                      // vocab-sharded: this slice's champion
       if (tid == 0) {
-        VsRecord& rec = static_cast<VsRecord*>(A.vs_records)[row_id];
+        VsRecord& rec = vs_record(A.vs_records, row_id, A.vs_cand);
         float xid = 0.f;
         rv.visit(rv.vec_of(id), [&](float x, int i) { if (i == id) xid = x; });
         rec.xmax = xid; rec.n = 1; rec.pad = 0;
@@ -301,7 +308,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   }
   auto vs_flag_only = [&](uint32_t fl) {
     if (tid == 0) {
-      VsRecord& rec = static_cast<VsRecord*>(A.vs_records)[row_id];
+      VsRecord& rec = vs_record(A.vs_records, row_id, A.vs_cand);
       rec.xmax = 0.f; rec.n = 0; rec.flags = fl; rec.pad = 0;
     }
   };
@@ -311,7 +318,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     write_row(-1, FLAG_BAD_CFG);
     return;
   }
-  if (A.vs_records && !(cfg.top_k > 0 && cfg.top_k <= VS_CAND)) {   // the merge needs a top-k to bound the lists
+  if (A.vs_records && !(cfg.top_k > 0 && cfg.top_k <= A.vs_cand)) {   // the merge needs a top-k to bound the lists
     vs_flag_only(VS_UNSUPPORTED);
     return;
   }
@@ -583,12 +590,12 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     return;
   }
   if (A.vs_records) {                                        // vocab-sharded: hand the list over instead of drawing
-    VsRecord& rec = static_cast<VsRecord*>(A.vs_records)[row_id];
+    VsRecord& rec = vs_record(A.vs_records, row_id, A.vs_cand);
     uint32_t fl = 0u;
     // a slice of -Inf only (a masked part of the vocabulary) is no verdict on the row: the merge
     // decides that from all slices; a slice given up early was not read to its end
     if (!giveup && (anynan || m == INFINITY || m != m)) fl |= VS_NONFINITE;
-    if (giveup || nk > VS_CAND) fl |= VS_OVERFLOW;
+    if (giveup || nk > A.vs_cand) fl |= VS_OVERFLOW;
     const int nout = (fl == 0u) ? nk : 0;
     if (tid == 0) { rec.xmax = xmax; rec.n = nout; rec.flags = fl; rec.pad = 0; }
     for (int j = tid; j < nout; j += N_NT) rec.cand[j] = make_uint2(cand[j].x, cand[j].y + static_cast<uint32_t>(A.vs_col_offset));

@@ -54,6 +54,7 @@ struct KernelArgs {
   const int32_t* worklist; // single-CTA kernel only: [0] = count, [1..] = rows to process (null: every row)
   void* vs_records;        // vocab-sharded local pass (narrow kernel only): [B] VsRecord to fill instead of drawing
   int32_t vs_col_offset;   // global index of this slice's first column
+  int32_t vs_cand;         // candidates per record (records are 16 + 8 * vs_cand bytes apart), at most VS_CAND
   float* tk_values;        // TopK op (narrow kernel only): [B, tk_k] values, descending; null otherwise
   int32_t* tk_indices;     // [B, tk_k] indices (ties: ascending index)
   int32_t tk_k;            // 0: not a TopK launch

@@ -24,8 +24,9 @@ constexpr int VM_DYN_BYTES = VM_LIST * 8 + 16384 + KEEP_MAX * 8;
 
 struct MergeArgs {
   KernelArgs k;             // V = whole vocabulary; logits unused
-  const VsRecord* records;  // [nranks][B]
+  const void* records;      // [nranks][B] records of 16 + 8 * cand bytes
   int32_t nranks;
+  int32_t cand;             // candidates per record
   int64_t B;
 };
 
@@ -63,8 +64,8 @@ __global__ void __launch_bounds__(VM_NT, 4) vocab_merge_kernel(MergeArgs M) {
     uint32_t fl_loc = 0u;
     unsigned long long mx = 0ull;
     for (int r = 0; r < M.nranks; r++) {
-      const VsRecord& rec = M.records[static_cast<int64_t>(r) * M.B + row];
-      const int n = min(max(rec.n, 0), VS_CAND);
+      const VsRecord& rec = vs_record(M.records, static_cast<int64_t>(r) * M.B + row, M.cand);
+      const int n = min(max(rec.n, 0), M.cand);
       fl_loc |= rec.flags;
       if (n > 0) { const unsigned long long k = okey(rec.xmax); mx = k > mx ? k : mx; }
       int base = 0;

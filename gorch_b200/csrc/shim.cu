@@ -6,6 +6,8 @@
 // runs the CUDA kernels or returns an error.
 
 #include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>     // types and prototypes only: the library is loaded at run time, on first use
 
 #include <cmath>
 #include <cstdarg>
@@ -68,6 +70,10 @@ struct Ctx {
   double* eb_table = nullptr;
   Scratch worklist;        // int32[1 + rows]: rows the cluster kernel leaves to the single-CTA kernel
   Scratch st_logits, st_cfgs, st_uniforms, st_ids, st_flags;
+  Scratch vs_local, vs_all;  // records of the vocab-sharded call: this rank's, and every rank's after the all-gather
+  ncclComm_t comm = nullptr; // set by gorch_cuda_comm_init
+  int comm_rank = 0, comm_nranks = 0;
+  cudaEvent_t ev_vs[4] = {nullptr, nullptr, nullptr, nullptr};
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int timing = 0;
   int variant = 0;        // 0: by batch size, 1: single-CTA kernel, 2: narrow/wide kernels, 3: cluster kernel,
@@ -105,6 +111,50 @@ void set_err(char** errOut, const char* fmt, ...) {
     if (e__ != cudaSuccess) {                                                    \
       set_err(errOut, "%s failed: %s", #expr, cudaGetErrorString(e__));          \
       return GORCH_CUDA_ERR_CUDA;                                                \
+    }                                                                            \
+  } while (0)
+
+// NCCL, loaded on first use (a process that never shards the vocabulary does not need it). Inside a
+// process that already holds a libnccl.so.2 (PyTorch's), the loader hands back that same copy.
+struct NcclApi {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+};
+NcclApi g_nccl;
+
+int load_nccl(char** errOut) {
+  if (g_nccl.handle) return GORCH_CUDA_OK;
+  void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) {
+    set_err(errOut, "gorch_cuda: cannot load libnccl.so.2: %s", dlerror());
+    return GORCH_CUDA_ERR_NCCL;
+  }
+  NcclApi a;
+  a.handle = h;
+  a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
+  a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
+  a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+  a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(h, "ncclAllGather"));
+  a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
+  if (!a.GetUniqueId || !a.CommInitRank || !a.CommDestroy || !a.AllGather || !a.GetErrorString) {
+    set_err(errOut, "gorch_cuda: libnccl.so.2 lacks a symbol this library needs");
+    return GORCH_CUDA_ERR_NCCL;
+  }
+  g_nccl = a;
+  return GORCH_CUDA_OK;
+}
+
+#define NCCL_TRY(expr, errOut)                                                   \
+  do {                                                                           \
+    ncclResult_t r__ = (expr);                                                   \
+    if (r__ != ncclSuccess) {                                                    \
+      set_err(errOut, "%s failed: %s", #expr, g_nccl.GetErrorString(r__));       \
+      return GORCH_CUDA_ERR_NCCL;                                                \
     }                                                                            \
   } while (0)
 
@@ -192,6 +242,7 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
   a.worklist = nullptr;
   a.vs_records = nullptr;
   a.vs_col_offset = 0;
+  a.vs_cand = gs::VS_CAND;
   a.tk_values = nullptr;
   a.tk_indices = nullptr;
   a.tk_k = 0;
@@ -488,6 +539,10 @@ void gorch_cuda_release(GorchCudaCtxRef ctx) {
   if (c->exp_table) cudaFree(c->exp_table);
   if (c->eb_table) cudaFree(c->eb_table);
   if (c->worklist.ptr) cudaFree(c->worklist.ptr);
+  if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
+  if (c->vs_local.ptr) cudaFree(c->vs_local.ptr);
+  if (c->vs_all.ptr) cudaFree(c->vs_all.ptr);
+  for (cudaEvent_t e : c->ev_vs) if (e) cudaEventDestroy(e);
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
   if (c->own_stream) cudaStreamDestroy(c->own_stream);
@@ -624,16 +679,17 @@ int gorch_cuda_sample_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, in
                      out_probs, out_debug, 0, errOut);
 }
 
-int gorch_cuda_vocab_local_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
-                               int64_t Vslice, int64_t row_stride, int64_t col_offset,
-                               const GorchSampleCfg* cfgs, void* records, char** errOut) {
-  Ctx* c = static_cast<Ctx*>(ctx);
-  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+static int vocab_local_launch(Ctx* c, const void* logits, int dtype, int64_t B, int64_t Vslice, int64_t row_stride,
+                              int64_t col_offset, const GorchSampleCfg* cfgs, void* records, int cand, char** errOut) {
   int rc = check_shape(dtype, B, Vslice, row_stride, errOut);
   if (rc) return rc;
   static_assert(sizeof(gs::VsRecord) == GORCH_VS_RECORD_BYTES, "record layout");
   if (col_offset < 0 || col_offset + Vslice > 0x7fffff00ll) {
     set_err(errOut, "gorch_cuda: column offset %lld out of range", (long long)col_offset);
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  if (cand < 1 || cand > gs::VS_CAND) {
+    set_err(errOut, "gorch_cuda: %d candidates per record outside 1..%d", cand, gs::VS_CAND);
     return GORCH_CUDA_ERR_BAD_ARG;
   }
   if (B == 0) return GORCH_CUDA_OK;
@@ -653,7 +709,7 @@ int gorch_cuda_vocab_local_dev(GorchCudaCtxRef ctx, const void* logits, int dtyp
   ba.k.force_greedy = 0; ba.k.cfgs = reinterpret_cast<const gs::RowCfg*>(cfgs); ba.k.uniforms = nullptr;
   ba.k.out_ids = nullptr; ba.k.out_flags = nullptr; ba.k.out_probs = nullptr; ba.k.out_debug = nullptr;
   ba.k.exp_table = c->exp_table; ba.k.row_offset = 0; ba.k.worklist = nullptr;
-  ba.k.vs_records = records; ba.k.vs_col_offset = static_cast<int32_t>(col_offset);
+  ba.k.vs_records = records; ba.k.vs_col_offset = static_cast<int32_t>(col_offset); ba.k.vs_cand = cand;
   ba.k.tk_values = nullptr; ba.k.tk_indices = nullptr; ba.k.tk_k = 0;
   ba.eb_table = c->eb_table;
   ba.hdr = base; ba.list_single = base + 15;
@@ -667,11 +723,9 @@ int gorch_cuda_vocab_local_dev(GorchCudaCtxRef ctx, const void* logits, int dtyp
   return GORCH_CUDA_OK;
 }
 
-int gorch_cuda_vocab_merge_dev(GorchCudaCtxRef ctx, const void* all_records, int nranks, int64_t B,
-                               int64_t V, const GorchSampleCfg* cfgs, const double* uniforms,
-                               int32_t* out_ids, uint32_t* out_flags, char** errOut) {
-  Ctx* c = static_cast<Ctx*>(ctx);
-  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+static int vocab_merge_launch(Ctx* c, const void* all_records, int nranks, int cand, int64_t B, int64_t V,
+                              const GorchSampleCfg* cfgs, const double* uniforms, int32_t* out_ids,
+                              uint32_t* out_flags, char** errOut) {
   if (nranks < 1 || nranks > gs::VM_MAX_RANKS) {
     set_err(errOut, "gorch_cuda: vocab merge takes 1..%d ranks, got %d", gs::VM_MAX_RANKS, nranks);
     return GORCH_CUDA_ERR_LIMIT;
@@ -686,9 +740,11 @@ int gorch_cuda_vocab_merge_dev(GorchCudaCtxRef ctx, const void* all_records, int
   m.k.cfgs = reinterpret_cast<const gs::RowCfg*>(cfgs); m.k.uniforms = uniforms;
   m.k.out_ids = out_ids; m.k.out_flags = out_flags; m.k.out_probs = nullptr; m.k.out_debug = nullptr;
   m.k.exp_table = c->exp_table; m.k.row_offset = 0; m.k.worklist = nullptr; m.k.vs_records = nullptr; m.k.vs_col_offset = 0;
+  m.k.vs_cand = cand;
   m.k.tk_values = nullptr; m.k.tk_indices = nullptr; m.k.tk_k = 0;
-  m.records = static_cast<const gs::VsRecord*>(all_records);
+  m.records = all_records;
   m.nranks = nranks;
+  m.cand = cand;
   m.B = B;
   const unsigned g = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
   gs::vocab_merge_kernel<<<g, gs::VM_NT, gs::VM_DYN_BYTES, c->stream>>>(m);
@@ -696,6 +752,114 @@ int gorch_cuda_vocab_merge_dev(GorchCudaCtxRef ctx, const void* all_records, int
   c->counters.kernel_launches += 1;
   c->counters.sample_launches += 1;
   c->counters.rows += B;
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_vocab_local_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
+                               int64_t Vslice, int64_t row_stride, int64_t col_offset,
+                               const GorchSampleCfg* cfgs, void* records, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  return vocab_local_launch(c, logits, dtype, B, Vslice, row_stride, col_offset, cfgs, records, gs::VS_CAND, errOut);
+}
+
+int gorch_cuda_vocab_merge_dev(GorchCudaCtxRef ctx, const void* all_records, int nranks, int64_t B,
+                               int64_t V, const GorchSampleCfg* cfgs, const double* uniforms,
+                               int32_t* out_ids, uint32_t* out_flags, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  return vocab_merge_launch(c, all_records, nranks, gs::VS_CAND, B, V, cfgs, uniforms, out_ids, out_flags, errOut);
+}
+
+int gorch_cuda_comm_unique_id(void* id_bytes, char** errOut) {
+  static_assert(sizeof(ncclUniqueId) == GORCH_CUDA_UNIQUE_ID_BYTES, "unique id size");
+  if (!id_bytes) { set_err(errOut, "gorch_cuda: null unique-id buffer"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = load_nccl(errOut);
+  if (rc) return rc;
+  ncclUniqueId id;
+  NCCL_TRY(g_nccl.GetUniqueId(&id), errOut);
+  memcpy(id_bytes, &id, sizeof id);
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_comm_init(GorchCudaCtxRef ctx, int rank, int nranks, const void* unique_id_bytes, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if (!unique_id_bytes || nranks < 1 || nranks > gs::VM_MAX_RANKS || rank < 0 || rank >= nranks) {
+    set_err(errOut, "gorch_cuda: comm_init needs a unique id and 0 <= rank < nranks <= %d (got rank %d of %d)",
+            gs::VM_MAX_RANKS, rank, nranks);
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  if (c->comm) { set_err(errOut, "gorch_cuda: the context already has a communicator"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = load_nccl(errOut);
+  if (rc) return rc;
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  ncclUniqueId id;
+  memcpy(&id, unique_id_bytes, sizeof id);
+  ncclComm_t comm = nullptr;
+  NCCL_TRY(g_nccl.CommInitRank(&comm, nranks, id, rank), errOut);
+  for (int i = 0; i < 4; i++) {
+    if (!c->ev_vs[i]) CUDA_TRY(cudaEventCreate(&c->ev_vs[i]), errOut);
+  }
+  c->comm = comm;
+  c->comm_rank = rank;
+  c->comm_nranks = nranks;
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_comm_release(GorchCudaCtxRef ctx, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if (!c->comm) return GORCH_CUDA_OK;
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  CUDA_TRY(cudaStreamSynchronize(c->stream), errOut);
+  ncclComm_t comm = c->comm;
+  c->comm = nullptr;
+  c->comm_nranks = 0;
+  NCCL_TRY(g_nccl.CommDestroy(comm), errOut);
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_sample_vocab_sharded_dev(GorchCudaCtxRef ctx, const void* logits_slice, int dtype, int64_t B,
+                                        int64_t Vslice, int64_t row_stride, int64_t col_offset, int64_t V,
+                                        int max_top_k, const GorchSampleCfg* cfgs, const double* uniforms,
+                                        int32_t* out_ids, uint32_t* out_flags, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if (!c->comm) { set_err(errOut, "gorch_cuda: no communicator: call gorch_cuda_comm_init first"); return GORCH_CUDA_ERR_NCCL; }
+  if (V < 1 || col_offset < 0 || col_offset + Vslice > V) {
+    set_err(errOut, "gorch_cuda: slice [%lld, %lld) outside the vocabulary of %lld", (long long)col_offset,
+            (long long)(col_offset + Vslice), (long long)V);
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  // candidates per record: the largest top_k of the batch plus room for ties at the local threshold,
+  // in steps of eight (0: the full record)
+  int cand = gs::VS_CAND;
+  if (max_top_k > 0 && max_top_k <= gs::VS_CAND) cand = ((max_top_k + max_top_k / 4 + 8 + 7) / 8) * 8;
+  if (cand > gs::VS_CAND) cand = gs::VS_CAND;
+  if (B == 0) return GORCH_CUDA_OK;
+  const size_t rec_bytes = 16 + 8 * static_cast<size_t>(cand);
+  int rc = ensure(c->vs_local, static_cast<size_t>(B) * rec_bytes, errOut);
+  if (rc) return rc;
+  rc = ensure(c->vs_all, static_cast<size_t>(B) * rec_bytes * static_cast<size_t>(c->comm_nranks), errOut);
+  if (rc) return rc;
+  if (c->timing) CUDA_TRY(cudaEventRecord(c->ev_vs[0], c->stream), errOut);
+  rc = vocab_local_launch(c, logits_slice, dtype, B, Vslice, row_stride, col_offset, cfgs, c->vs_local.ptr, cand, errOut);
+  if (rc) return rc;
+  if (c->timing) CUDA_TRY(cudaEventRecord(c->ev_vs[1], c->stream), errOut);
+  // ONE collective: every rank's records to every rank, in rank order, on the context's stream
+  NCCL_TRY(g_nccl.AllGather(c->vs_local.ptr, c->vs_all.ptr, static_cast<size_t>(B) * rec_bytes, ncclUint8, c->comm, c->stream), errOut);
+  if (c->timing) CUDA_TRY(cudaEventRecord(c->ev_vs[2], c->stream), errOut);
+  rc = vocab_merge_launch(c, c->vs_all.ptr, c->comm_nranks, cand, B, V, cfgs, uniforms, out_ids, out_flags, errOut);
+  if (rc) return rc;
+  if (c->timing) {
+    CUDA_TRY(cudaEventRecord(c->ev_vs[3], c->stream), errOut);
+    CUDA_TRY(cudaEventSynchronize(c->ev_vs[3]), errOut);
+    CUDA_TRY(cudaEventElapsedTime(&c->counters.vs_local_ms, c->ev_vs[0], c->ev_vs[1]), errOut);
+    CUDA_TRY(cudaEventElapsedTime(&c->counters.vs_gather_ms, c->ev_vs[1], c->ev_vs[2]), errOut);
+    CUDA_TRY(cudaEventElapsedTime(&c->counters.vs_merge_ms, c->ev_vs[2], c->ev_vs[3]), errOut);
+    CUDA_TRY(cudaEventElapsedTime(&c->counters.last_kernel_ms, c->ev_vs[0], c->ev_vs[3]), errOut);
+  }
   return GORCH_CUDA_OK;
 }
 

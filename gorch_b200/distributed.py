@@ -51,9 +51,13 @@ def sample_vocab_sharded(sampler, logits_slice, cfgs, uniforms, V: int, rank: in
     `sampler` offers vocab_local(logits_slice, cfgs, col_offset) -> records [B, R] (uint8)
     and vocab_merge(all_records [world, B, R], cfgs, uniforms, V) -> (ids, flags)
     (a CudaSampler). `gather(records)` stacks the ranks' arrays in rank order; by default
-    torch.distributed.all_gather over the default process group (one collective).
+    one torch.distributed.all_gather over the default process group, with the tensors on
+    the device the group's backend moves (NCCL: the GPU; gloo: the host).
     Rows the kernels cannot take (top_k == 0 or above the record capacity, ties that
-    overflow a record) come back with id -1 and FLAG_INTERNAL."""
+    overflow a record) come back with id -1 and FLAG_INTERNAL.
+
+    This is the host-array form (the records pass through host memory between the two
+    kernels); a GPU job keeps everything on the device with sample_vocab_sharded_device."""
     lo, hi = shard_vocab(V, rank, world)
     if logits_slice.shape[1] != hi - lo:
         raise ValueError(f"rank {rank} of {world} holds columns [{lo},{hi}) of V={V}, got {logits_slice.shape[1]} columns")
@@ -69,6 +73,34 @@ def _stack_default(local: np.ndarray) -> np.ndarray:
     import torch.distributed as dist
     world = dist.get_world_size()
     t = torch.from_numpy(np.ascontiguousarray(local))
+    if "nccl" in str(dist.get_backend()):        # NCCL moves device memory only
+        t = t.cuda()
     out = [torch.empty_like(t) for _ in range(world)]
     dist.all_gather(out, t)
-    return np.stack([o.numpy() for o in out])
+    return np.stack([o.cpu().numpy() for o in out])
+
+
+def init_vocab_comm(sampler, rank: int, world: int) -> None:
+    """Binds the library's own NCCL communicator to `sampler` (gorch_cuda_comm_init): rank 0 makes
+    the unique id, torch.distributed (any backend) carries its 128 bytes to the other ranks."""
+    import torch.distributed as dist
+    box = [sampler.comm_unique_id() if rank == 0 else None]
+    if world > 1:
+        dist.broadcast_object_list(box, src=0)
+    sampler.comm_init(rank, world, box[0])
+
+
+def sample_vocab_sharded_device(sampler, d_slice, d_cfgs, d_uniforms, d_ids, d_flags, V: int, rank: int, world: int,
+                                max_top_k: int = 0) -> None:
+    """The device-resident form: `d_slice` [B, hi - lo] (float32, or int16/uint16 holding bf16),
+    `d_cfgs` [B, 16] bytes, `d_uniforms` [B] float64, `d_ids` / `d_flags` [B] int32 are torch CUDA
+    tensors; local pass, ncclAllGather and merge all run on the sampler's stream inside
+    gorch_cuda_sample_vocab_sharded_dev (init_vocab_comm first). Asynchronous."""
+    import torch
+    lo, hi = shard_vocab(V, rank, world)
+    B = int(d_slice.shape[0])
+    if int(d_slice.shape[1]) != hi - lo or d_slice.stride(1) != 1:
+        raise ValueError(f"rank {rank} of {world} holds columns [{lo},{hi}) of V={V}")
+    code = 0 if d_slice.dtype == torch.float32 else 1
+    sampler.sample_vocab_sharded_ptrs(d_slice.data_ptr(), code, B, hi - lo, int(d_slice.stride(0)), lo, V, max_top_k,
+                                      d_cfgs.data_ptr(), d_uniforms.data_ptr(), d_ids.data_ptr(), d_flags.data_ptr())

@@ -59,6 +59,7 @@ def _logits_arg(logits: np.ndarray):
 
 VS_CAND = 128                      # GORCH_VS_CAND
 VS_RECORD_BYTES = 16 + 8 * VS_CAND  # GORCH_VS_RECORD_BYTES
+UNIQUE_ID_BYTES = 128              # GORCH_CUDA_UNIQUE_ID_BYTES
 
 
 class CudaSampler:
@@ -243,6 +244,36 @@ class CudaSampler:
         err = C.c_void_p()
         rc = self._lib.gorch_cuda_vocab_merge_dev(self._ctx, records_ptr, nranks, B, V, cfgs_ptr,
                                                   uniforms_ptr, ids_ptr, flags_ptr, C.byref(err))
+        _check(self._lib, rc, err)
+
+    # ---- the same three steps as one call, the all-gather inside the library (NCCL)
+    def comm_unique_id(self) -> bytes:
+        """gorch_cuda_comm_unique_id: rank 0 makes the id; every other rank needs the same bytes."""
+        buf = C.create_string_buffer(UNIQUE_ID_BYTES)
+        err = C.c_void_p()
+        _check(self._lib, self._lib.gorch_cuda_comm_unique_id(buf, C.byref(err)), err)
+        return buf.raw
+
+    def comm_init(self, rank: int, nranks: int, unique_id: bytes) -> None:
+        """gorch_cuda_comm_init (collective): binds a communicator of `nranks` ranks to this context."""
+        if len(unique_id) != UNIQUE_ID_BYTES:
+            raise ValueError(f"unique id must be {UNIQUE_ID_BYTES} bytes")
+        buf = C.create_string_buffer(unique_id, UNIQUE_ID_BYTES)
+        err = C.c_void_p()
+        _check(self._lib, self._lib.gorch_cuda_comm_init(self._ctx, int(rank), int(nranks), buf, C.byref(err)), err)
+
+    def comm_release(self) -> None:
+        err = C.c_void_p()
+        _check(self._lib, self._lib.gorch_cuda_comm_release(self._ctx, C.byref(err)), err)
+
+    def sample_vocab_sharded_ptrs(self, logits_ptr: int, dtype: int, B: int, Vslice: int, row_stride: int,
+                                  col_offset: int, V: int, max_top_k: int, cfgs_ptr: int, uniforms_ptr: int,
+                                  ids_ptr: int, flags_ptr: int | None = None) -> None:
+        """gorch_cuda_sample_vocab_sharded_dev: device pointers; local pass, all-gather, merge."""
+        err = C.c_void_p()
+        rc = self._lib.gorch_cuda_sample_vocab_sharded_dev(self._ctx, logits_ptr, dtype, B, Vslice, row_stride,
+                                                           col_offset, V, int(max_top_k), cfgs_ptr, uniforms_ptr,
+                                                           ids_ptr, flags_ptr, C.byref(err))
         _check(self._lib, rc, err)
 
     def vocab_local(self, logits_slice, cfgs, col_offset: int) -> np.ndarray:

@@ -84,6 +84,9 @@ typedef struct {
   uint64_t h2d_bytes;       /* cf. metal.go:64-101 byte counters */
   uint64_t d2h_bytes;
   float last_kernel_ms;     /* device time of the last timed call (0 when timing is off) */
+  float vs_local_ms;        /* phases of the last timed gorch_cuda_sample_vocab_sharded_dev: local pass, */
+  float vs_gather_ms;       /* all-gather, */
+  float vs_merge_ms;        /* merge */
 } GorchCudaCounters;
 
 /* ---- lifecycle: replaces metal_create_device / metal_create_command_queue /
@@ -192,6 +195,27 @@ int gorch_cuda_vocab_local_dev(GorchCudaCtxRef ctx, const void* logits, int dtyp
 int gorch_cuda_vocab_merge_dev(GorchCudaCtxRef ctx, const void* all_records, int nranks, int64_t B,
                                int64_t V, const GorchSampleCfg* cfgs, const double* uniforms,
                                int32_t* out_ids, uint32_t* out_flags, char** errOut);
+
+/* The three steps above as ONE call, with the collective inside the library (no counterpart in the
+ * reference): local pass -> ncclAllGather of the records on the context's stream -> merge. Every
+ * rank calls it with its own column slice of the same B rows and gets all B ids. The records that
+ * cross the link hold max_top_k plus a quarter (room for ties at the local threshold) candidates
+ * instead of GORCH_VS_CAND: max_top_k is the largest top_k among the batch's rows (0 or above
+ * GORCH_VS_CAND: full records). A failing NCCL call returns GORCH_CUDA_ERR_NCCL with its message.
+ *
+ * gorch_cuda_comm_unique_id: rank 0 makes the 128-byte id (ncclGetUniqueId) and hands it to the
+ * other ranks by whatever channel the host program has; gorch_cuda_comm_init (collective: every
+ * rank calls it) binds a communicator of `nranks` ranks to the context (ncclCommInitRank on the
+ * context's device); gorch_cuda_comm_release destroys it (gorch_cuda_release does too). libnccl.so.2
+ * is loaded at the first of these calls; a process that never calls them does not need it. */
+#define GORCH_CUDA_UNIQUE_ID_BYTES 128
+int gorch_cuda_comm_unique_id(void* id_bytes, char** errOut);
+int gorch_cuda_comm_init(GorchCudaCtxRef ctx, int rank, int nranks, const void* unique_id_bytes, char** errOut);
+int gorch_cuda_comm_release(GorchCudaCtxRef ctx, char** errOut);
+int gorch_cuda_sample_vocab_sharded_dev(GorchCudaCtxRef ctx, const void* logits_slice, int dtype, int64_t B,
+                                        int64_t Vslice, int64_t row_stride, int64_t col_offset, int64_t V,
+                                        int max_top_k, const GorchSampleCfg* cfgs, const double* uniforms,
+                                        int32_t* out_ids, uint32_t* out_flags, char** errOut);
 
 /* The reference's tensor-level index ops as batched device ops (device pointers, asynchronous on
  * the context's stream).

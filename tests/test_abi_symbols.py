@@ -57,3 +57,23 @@ def test_product_does_not_touch_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp", ".hpp")):
                 text = open(os.path.join(dirpath, f), errors="replace").read()
                 assert "oracle" not in text.lower(), os.path.join(dirpath, f)
+
+
+def test_comm_entry_points_fail_cleanly():
+    """The multi-GPU entry points without a context or a buffer: an error code and a message, never
+    a crash or a hang; making a unique id either works or reports an NCCL error (no GPU here)."""
+    lib = _lib.load()
+    err = C.c_void_p()
+    assert lib.gorch_cuda_comm_init(None, 0, 2, None, C.byref(err)) == 1          # GORCH_CUDA_ERR_BAD_ARG
+    assert b"null context" in C.string_at(err.value)
+    lib.gorch_cuda_free_string(err)
+    err = C.c_void_p()
+    assert lib.gorch_cuda_comm_release(None, C.byref(err)) == 1
+    lib.gorch_cuda_free_string(err)
+    err = C.c_void_p()
+    assert lib.gorch_cuda_comm_unique_id(None, C.byref(err)) == 1
+    lib.gorch_cuda_free_string(err)
+    err = C.c_void_p()
+    rc = lib.gorch_cuda_sample_vocab_sharded_dev(None, None, 0, 1, 1, 1, 0, 1, 0, None, None, None, None, C.byref(err))
+    assert rc == 1
+    lib.gorch_cuda_free_string(err)

@@ -19,14 +19,22 @@ def run_sharded(sampler, logits, cfgs, uniforms, world):
     return sampler.vocab_merge(np.stack(recs), cfgs, uniforms, V)
 
 
+def check_ids(oracle, logits, cfgs, uniforms, ids, flags):
+    """Ids against the oracle on whole rows. A differing id is excused only where the oracle itself
+    shows the row to be open (uniform within 1e-6 of a CDF edge, cut inside a group of equal
+    probabilities) or the kernel flagged the cut as decided within rounding: tests/parity.py."""
+    from tests.parity import compare
+    ora = oracle.sample_batch(logits, cfgs, uniforms, flags=oracle.FAST_KTH, threads=oracle.hw_threads())
+    assert not np.any(flags & FLAG_INTERNAL), "rows the kernels could not take"
+    rep = compare({"ids": ids, "flags": flags}, ora, uniforms, check_probs=False, allow_tie_cut=True)
+    assert rep["id_mismatch"] == rep["boundary_mismatch"]
+    assert rep["id_mismatch"] <= max(2, len(ids) // 50), f"{rep['id_mismatch']} of {len(ids)} rows differ (all excused, but too many)"
+    return rep
+
+
 def check(sampler, oracle, logits, cfgs, uniforms, world):
     ids, flags = run_sharded(sampler, logits, cfgs, uniforms, world)
-    want = oracle.sample_batch(logits, cfgs, uniforms, want_info=False, flags=oracle.FAST_KTH)["ids"]
-    excused = (flags & (FLAG_BOUNDARY | FLAG_TIE_CUT | FLAG_TOPP_EDGE)) != 0
-    assert not np.any(flags & FLAG_INTERNAL), "rows the kernels could not take"
-    bad = (ids != want) & ~excused
-    assert not bad.any(), f"rows {np.nonzero(bad)[0][:8]}: got {ids[bad][:8]} want {want[bad][:8]}"
-    return int(excused.sum())
+    return check_ids(oracle, logits, cfgs, uniforms, ids, flags)
 
 
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
@@ -118,3 +126,55 @@ def test_masked_slices(sampler, oracle, world):
     for b in range(B):
         cfgs[b] = [(0.9, 64, 0.95, 1), (1.0, 40, 0.0, 0), (0.0, 0, 0.0, 0)][b % 3]
     check(sampler, oracle, logits, cfgs, rng.random(B), world)
+
+
+def _fused_call(s, logits, cfgs, uniforms, max_top_k):
+    """gorch_cuda_sample_vocab_sharded_dev on this process's one rank (device buffers of the library)."""
+    from gorch_b200.config import DTYPE_BF16, DTYPE_F32
+    B, V = logits.shape
+    code = DTYPE_BF16 if logits.dtype == np.uint16 else DTYPE_F32
+    lib = s._lib
+    bufs = []
+    try:
+        b_log = s._buf(logits.nbytes); bufs.append(b_log)
+        b_cfg = s._buf(cfgs.nbytes); bufs.append(b_cfg)
+        b_uni = s._buf(uniforms.nbytes); bufs.append(b_uni)
+        b_ids = s._buf(B * 4); bufs.append(b_ids)
+        b_flg = s._buf(B * 4); bufs.append(b_flg)
+        s._upload(b_log, np.ascontiguousarray(logits)); s._upload(b_cfg, cfgs); s._upload(b_uni, uniforms)
+        ptr = lib.gorch_cuda_buffer_device_ptr
+        s.sample_vocab_sharded_ptrs(ptr(b_log), code, B, V, V, 0, V, max_top_k, ptr(b_cfg), ptr(b_uni), ptr(b_ids), ptr(b_flg))
+        s.sync()
+        ids = np.empty(B, dtype=np.int32); flags = np.empty(B, dtype=np.uint32)
+        s._download(b_ids, ids); s._download(b_flg, flags)
+    finally:
+        for b in bufs:
+            lib.gorch_cuda_buffer_free(b)
+    return ids, flags
+
+
+def test_collective_inside_the_library_one_rank(_sampler_session, oracle):
+    """The fused call (local pass, ncclAllGather, merge) with a communicator of one rank: NCCL is
+    loaded and driven by the library itself; records sized by the batch's largest top_k."""
+    from gorch_b200.sampling import GorchCudaError
+    s = _sampler_session
+    s.set_kernel_variant(0, 0)
+    w = workloads.vocab_sharded(96)
+    with pytest.raises(GorchCudaError, match="comm_init"):
+        _fused_call(s, w.logits, w.cfgs, w.uniforms, 64)            # no communicator yet
+    s.comm_init(0, 1, s.comm_unique_id())
+    try:
+        for max_k in (64, 0, 128):
+            ids, flags = _fused_call(s, w.logits, w.cfgs, w.uniforms, max_k)
+            check_ids(oracle, w.logits, w.cfgs, w.uniforms, ids, flags)
+        # a top_k above what the record was sized for is reported, not mis-sampled
+        ids, flags = _fused_call(s, w.logits, w.cfgs, w.uniforms, 16)
+        assert (ids == -1).all() and (flags & FLAG_INTERNAL).all()
+        # timing of the phases
+        s.set_timing(True)
+        _fused_call(s, w.logits, w.cfgs, w.uniforms, 64)
+        c = s.counters()
+        s.set_timing(False)
+        assert c["vs_local_ms"] > 0 and c["vs_merge_ms"] > 0 and c["vs_gather_ms"] >= 0
+    finally:
+        s.comm_release()
