@@ -22,6 +22,7 @@ EXPORTS = [
     "gorch_cuda_vocab_local_dev", "gorch_cuda_vocab_merge_dev",
     "gorch_cuda_comm_unique_id", "gorch_cuda_comm_init", "gorch_cuda_comm_release", "gorch_cuda_sample_vocab_sharded_dev",
     "gorch_cuda_topk_dev", "gorch_cuda_multinomial_dev",
+    "gorch_cuda_lm_head_logits_dev", "gorch_cuda_lm_head_status", "gorch_cuda_lm_head_sample_dev",
     "gorch_cuda_generate_control_dev", "gorch_cuda_generate_step_dev",
     "gorch_cuda_softmax_dev", "gorch_cuda_cross_entropy_fwd_dev", "gorch_cuda_cross_entropy_bwd_dev",
 ]
@@ -45,6 +46,7 @@ class Counters(C.Structure):
         ("sample_launches", C.c_uint64), ("kernel_launches", C.c_uint64), ("argmax_launches", C.c_uint64), ("rows", C.c_uint64),
         ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64), ("last_kernel_ms", C.c_float),
         ("vs_local_ms", C.c_float), ("vs_gather_ms", C.c_float), ("vs_merge_ms", C.c_float),
+        ("lm_head_refused_rows", C.c_uint64),
     ]
 
 
@@ -91,6 +93,9 @@ def load() -> C.CDLL:
         "gorch_cuda_comm_init": (i32, [p, i32, i32, p, err]),
         "gorch_cuda_comm_release": (i32, [p, err]),
         "gorch_cuda_sample_vocab_sharded_dev": (i32, [p, p, i32, i64, i64, i64, i64, i64, i32, p, p, p, p, err]),
+        "gorch_cuda_lm_head_logits_dev": (i32, [p, p, i64, p, i64, i64, i64, i64, p, i64, err]),
+        "gorch_cuda_lm_head_status": (i32, [p, C.POINTER(C.c_uint32), err]),
+        "gorch_cuda_lm_head_sample_dev": (i32, [p, p, i64, p, i64, i64, i64, i64, i32, p, p, p, p, err]),
         "gorch_cuda_topk_dev": (i32, [p, p, i32, i64, i64, i64, i64, p, p, p, err]),
         "gorch_cuda_multinomial_dev": (i32, [p, p, i64, i64, i64, p, p, p, err]),
         "gorch_cuda_softmax_dev": (i32, [p, p, i32, i64, i64, i64, p, i64, i32, err]),

@@ -28,6 +28,7 @@
 #include "index_ops.cuh"
 #include "generate_control.cuh"
 #include "row_softmax.cuh"
+#include "lm_head.cuh"
 
 namespace {
 
@@ -70,6 +71,8 @@ struct Ctx {
   double* eb_table = nullptr;
   Scratch worklist;        // int32[1 + rows]: rows the cluster kernel leaves to the single-CTA kernel
   Scratch st_logits, st_cfgs, st_uniforms, st_ids, st_flags;
+  Scratch lmh_scratch;       // status word, thresholds, candidate lists, sample logits of the LM-head path
+  Scratch lmh_logits;        // [B, V] f32 when rows need the unfused samplers
   Scratch vs_local, vs_all;  // records of the vocab-sharded call: this rank's, and every rank's after the all-gather
   ncclComm_t comm = nullptr; // set by gorch_cuda_comm_init
   int comm_rank = 0, comm_nranks = 0;
@@ -446,6 +449,73 @@ int host_run(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int64_
   return GORCH_CUDA_OK;
 }
 
+// ---- LM-head projection (lm_head.cuh) ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+
+int load_encode_tiled(char** errOut) {
+  if (g_encode_tiled) return GORCH_CUDA_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres), errOut);
+  if (!fn || qres != cudaDriverEntryPointSuccess) {
+    set_err(errOut, "gorch_cuda: the driver does not offer cuTensorMapEncodeTiled");
+    return GORCH_CUDA_ERR_CUDA;
+  }
+  g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  return GORCH_CUDA_OK;
+}
+
+// Tensor map of a row-major [rows, K] bf16 matrix: boxes of 64 columns x 128 rows, 128-byte swizzle,
+// zero fill outside the matrix.
+int make_bf16_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld, char** errOut) {
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(gs::LMH_BK), static_cast<cuuint32_t>(gs::LMH_BM)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_err(errOut, "gorch_cuda: cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r));
+    return GORCH_CUDA_ERR_CUDA;
+  }
+  return GORCH_CUDA_OK;
+}
+
+int check_lm_head(Ctx* c, const void* x, const void* w, int64_t B, int64_t V, int64_t K, int64_t ldx, int64_t ldw, char** errOut) {
+  if (B < 0 || V < 1 || K < gs::LMH_BK || (K % gs::LMH_BK) != 0 || ldx < K || ldw < K) {
+    set_err(errOut, "gorch_cuda: LM head needs B >= 0, V >= 1 and K a multiple of %d (got B=%lld V=%lld K=%lld)", gs::LMH_BK,
+            (long long)B, (long long)V, (long long)K);
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  if (B > 0x7fffffffll || V > 0x7fffff00ll || K > 0x7fffffffll) { set_err(errOut, "gorch_cuda: LM head shape beyond 31 bits"); return GORCH_CUDA_ERR_LIMIT; }
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!x || !w) { set_err(errOut, "gorch_cuda: null pointer argument"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(w) & 15u) || ((ldx * 2) & 15) || ((ldw * 2) & 15)) {
+    set_err(errOut, "gorch_cuda: LM head operands must be 16-byte aligned with row pitches that are multiples of 16 bytes");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  (void)c;
+  return GORCH_CUDA_OK;
+}
+
+// One launch of lm_head_kernel over the vocabulary tiles tile0 + i * step, i < ntile.
+int launch_lm_head(Ctx* c, gs::LmHeadArgs& a, char** errOut) {
+  const int64_t ntile_total = (static_cast<int64_t>(a.V) + gs::LMH_BN - 1) / gs::LMH_BN;
+  if (a.ntile < 1 || a.tile0 + static_cast<int64_t>(a.ntile - 1) * a.tile_step >= ntile_total) {
+    set_err(errOut, "gorch_cuda: LM head tile range outside the vocabulary");
+    return GORCH_CUDA_ERR_BAD_ARG;
+  }
+  const unsigned grid = static_cast<unsigned>(a.ntile < c->sm_count ? a.ntile : c->sm_count);
+  gs::lm_head_kernel<<<grid, gs::LMH_NT, gs::LMH_DYN_BYTES, c->stream>>>(a);
+  CUDA_TRY(cudaGetLastError(), errOut);
+  c->counters.kernel_launches += 1;
+  return GORCH_CUDA_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -522,6 +592,8 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   if ((e = cudaFuncSetAttribute(gs::w256::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w256::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::w1024::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w1024::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::w1024::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w1024::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::LMH_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::lmh_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::LMH_F_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::row_softmax_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::RS_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::row_softmax_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::RS_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::w256::wide_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w256::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
@@ -540,6 +612,8 @@ void gorch_cuda_release(GorchCudaCtxRef ctx) {
   if (c->eb_table) cudaFree(c->eb_table);
   if (c->worklist.ptr) cudaFree(c->worklist.ptr);
   if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
+  if (c->lmh_scratch.ptr) cudaFree(c->lmh_scratch.ptr);
+  if (c->lmh_logits.ptr) cudaFree(c->lmh_logits.ptr);
   if (c->vs_local.ptr) cudaFree(c->vs_local.ptr);
   if (c->vs_all.ptr) cudaFree(c->vs_all.ptr);
   for (cudaEvent_t e : c->ev_vs) if (e) cudaEventDestroy(e);
@@ -1119,6 +1193,138 @@ int gorch_cuda_argmax_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, in
   CUDA_TRY(cudaSetDevice(c->device), errOut);
   return launch_rows(c, logits, dtype, B, V, row_stride, nullptr, nullptr, out_ids, nullptr,
                      nullptr, nullptr, 1, errOut);
+}
+
+int gorch_cuda_lm_head_logits_dev(GorchCudaCtxRef ctx, const void* x, int64_t ldx, const void* w, int64_t ldw, int64_t B,
+                                  int64_t V, int64_t K, float* out_logits, int64_t ld_out, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = check_lm_head(c, x, w, B, V, K, ldx, ldw, errOut);
+  if (rc) return rc;
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!out_logits || ld_out < V) { set_err(errOut, "gorch_cuda: LM head output missing or its pitch below V"); return GORCH_CUDA_ERR_BAD_ARG; }
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  if ((rc = load_encode_tiled(errOut))) return rc;
+  if ((rc = ensure(c->lmh_scratch, 256, errOut))) return rc;
+  gs::LmHeadArgs a;
+  memset(&a, 0, sizeof a);
+  if ((rc = make_bf16_map(&a.map_x, x, B, K, ldx, errOut))) return rc;
+  if ((rc = make_bf16_map(&a.map_w, w, V, K, ldw, errOut))) return rc;
+  a.B = static_cast<int32_t>(B); a.V = static_cast<int32_t>(V); a.K = static_cast<int32_t>(K);
+  a.tile0 = 0; a.tile_step = 1; a.ntile = static_cast<int32_t>((V + gs::LMH_BN - 1) / gs::LMH_BN);
+  a.out_logits = out_logits; a.ld_out = ld_out; a.compact = 0;
+  a.status = static_cast<uint32_t*>(c->lmh_scratch.ptr);
+  CUDA_TRY(cudaMemsetAsync(a.status, 0, sizeof(uint32_t), c->stream), errOut);
+  return launch_lm_head(c, a, errOut);
+}
+
+int gorch_cuda_lm_head_sample_dev(GorchCudaCtxRef ctx, const void* x, int64_t ldx, const void* w, int64_t ldw, int64_t B,
+                                  int64_t V, int64_t K, int fuse_top_k, const GorchSampleCfg* cfgs, const double* uniforms,
+                                  int32_t* out_ids, uint32_t* out_flags, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = check_lm_head(c, x, w, B, V, K, ldx, ldw, errOut);
+  if (rc) return rc;
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!cfgs || !uniforms || !out_ids) { set_err(errOut, "gorch_cuda: null pointer argument"); return GORCH_CUDA_ERR_BAD_ARG; }
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  if ((rc = load_encode_tiled(errOut))) return rc;
+  gs::LmHeadArgs a;
+  memset(&a, 0, sizeof a);
+  if ((rc = make_bf16_map(&a.map_x, x, B, K, ldx, errOut))) return rc;
+  if ((rc = make_bf16_map(&a.map_w, w, V, K, ldw, errOut))) return rc;
+  a.B = static_cast<int32_t>(B); a.V = static_cast<int32_t>(V); a.K = static_cast<int32_t>(K);
+  const int ntile = static_cast<int>((V + gs::LMH_BN - 1) / gs::LMH_BN);
+  // the unfused form: logits to scratch, then the ordinary sampling kernels
+  auto unfused = [&]() -> int {
+    const int64_t ld = (V + 3) & ~3ll;
+    int r2 = ensure(c->lmh_logits, static_cast<size_t>(B) * ld * sizeof(float), errOut);
+    if (r2) return r2;
+    if ((r2 = ensure(c->lmh_scratch, 256, errOut))) return r2;
+    gs::LmHeadArgs u = a;
+    u.tile0 = 0; u.tile_step = 1; u.ntile = ntile;
+    u.out_logits = static_cast<float*>(c->lmh_logits.ptr); u.ld_out = ld; u.compact = 0;
+    u.thr = nullptr; u.cand = nullptr; u.cand_cnt = nullptr; u.rowmax_key = nullptr; u.row_nan = nullptr;
+    u.status = static_cast<uint32_t*>(c->lmh_scratch.ptr);
+    CUDA_TRY(cudaMemsetAsync(u.status, 0, sizeof(uint32_t), c->stream), errOut);
+    if ((r2 = launch_lm_head(c, u, errOut))) return r2;
+    return launch_rows(c, c->lmh_logits.ptr, GORCH_CUDA_F32, B, V, ld, cfgs, uniforms, out_ids, out_flags, nullptr, nullptr, 0, errOut);
+  };
+  if (fuse_top_k < 1 || fuse_top_k > gs::KFAST || ntile < 4 * gs::LMH_SAMPLE_TILES_MIN) return unfused();
+  int stiles = ntile / 32;
+  if (stiles < gs::LMH_SAMPLE_TILES_MIN) stiles = gs::LMH_SAMPLE_TILES_MIN;
+  if (stiles > gs::LMH_SAMPLE_TILES_MAX) stiles = gs::LMH_SAMPLE_TILES_MAX;
+
+  // ---- the fused form: scratch = [status, nfail | thr | rowmax | nan | count | sample logits | candidates]
+  const int nsample = stiles * gs::LMH_BN;
+  const size_t off_thr = 256, off_max = off_thr + 4 * B, off_nan = off_max + 4 * B, off_cnt = off_nan + 4 * B;
+  const size_t off_smp = (off_cnt + 4 * B + 255) & ~static_cast<size_t>(255);
+  const size_t off_cand = (off_smp + sizeof(float) * B * nsample + 255) & ~static_cast<size_t>(255);
+  const size_t total = off_cand + sizeof(uint2) * static_cast<size_t>(B) * gs::LMH_CAND_CAP;
+  if ((rc = ensure(c->lmh_scratch, total, errOut))) return rc;
+  unsigned char* base = static_cast<unsigned char*>(c->lmh_scratch.ptr);
+  CUDA_TRY(cudaMemsetAsync(base, 0, off_smp, c->stream), errOut);          // status, nfail, maxima, NaN bits, counts
+  // 1. a sample of the vocabulary's tiles (all of them full tiles)
+  gs::LmHeadArgs sa = a;
+  sa.tile0 = 0; sa.tile_step = (ntile - 1) / stiles; sa.ntile = stiles;
+  sa.out_logits = reinterpret_cast<float*>(base + off_smp); sa.ld_out = nsample; sa.compact = 1;
+  sa.status = reinterpret_cast<uint32_t*>(base);
+  if ((rc = launch_lm_head(c, sa, errOut))) return rc;
+  // 2. thresholds
+  gs::LmhSampleArgs fa;
+  memset(&fa, 0, sizeof fa);
+  fa.k.V = static_cast<int32_t>(V); fa.k.row_stride = V;
+  fa.k.cfgs = reinterpret_cast<const gs::RowCfg*>(cfgs); fa.k.uniforms = uniforms;
+  fa.k.out_ids = out_ids; fa.k.out_flags = out_flags; fa.k.exp_table = c->exp_table; fa.k.vs_cand = gs::VS_CAND;
+  fa.sample = reinterpret_cast<const float*>(base + off_smp); fa.nsample = nsample; fa.fuse_top_k = fuse_top_k;
+  fa.thr = reinterpret_cast<float*>(base + off_thr);
+  fa.cand = reinterpret_cast<const uint2*>(base + off_cand);
+  fa.cand_cnt = reinterpret_cast<const int32_t*>(base + off_cnt);
+  fa.rowmax_key = reinterpret_cast<const uint32_t*>(base + off_max);
+  fa.row_nan = reinterpret_cast<const int32_t*>(base + off_nan);
+  fa.nfail = reinterpret_cast<int32_t*>(base + 4);
+  fa.B = B;
+  const unsigned g = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
+  gs::lmh_threshold_kernel<<<g, gs::LMH_F_NT, 0, c->stream>>>(fa);
+  // 3. the whole vocabulary, candidates out of the epilogue
+  gs::LmHeadArgs ma = a;
+  ma.tile0 = 0; ma.tile_step = 1; ma.ntile = ntile;
+  ma.out_logits = nullptr; ma.ld_out = 0; ma.compact = 0;
+  ma.thr = fa.thr; ma.cand = reinterpret_cast<uint2*>(base + off_cand); ma.cand_cnt = reinterpret_cast<int32_t*>(base + off_cnt);
+  ma.rowmax_key = reinterpret_cast<uint32_t*>(base + off_max); ma.row_nan = reinterpret_cast<int32_t*>(base + off_nan);
+  ma.status = reinterpret_cast<uint32_t*>(base);
+  if ((rc = launch_lm_head(c, ma, errOut))) return rc;
+  // 4. finish every row from its candidates
+  gs::lmh_finish_kernel<<<g, gs::LMH_F_NT, gs::LMH_F_DYN_BYTES, c->stream>>>(fa);
+  CUDA_TRY(cudaGetLastError(), errOut);
+  c->counters.kernel_launches += 2;
+  c->counters.sample_launches += 1;
+  c->counters.rows += static_cast<uint64_t>(B);
+  // rows the fused form could not finish (their estimate failed, or their config is not served): the
+  // count comes back to the host, which then recomputes the batch through the unfused form
+  int32_t host_word[2] = {0, 0};
+  CUDA_TRY(cudaMemcpyAsync(host_word, base, sizeof host_word, cudaMemcpyDeviceToHost, c->stream), errOut);
+  CUDA_TRY(cudaStreamSynchronize(c->stream), errOut);
+  if (host_word[0] != 0) {
+    set_err(errOut, "gorch_cuda: the LM-head kernel gave up a bounded wait (status %d)", host_word[0]);
+    return GORCH_CUDA_ERR_CUDA;
+  }
+  if (host_word[1] > 0) {
+    c->counters.lm_head_refused_rows += static_cast<uint64_t>(host_word[1]);
+    return unfused();
+  }
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_lm_head_status(GorchCudaCtxRef ctx, uint32_t* status, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c || !status) { set_err(errOut, "gorch_cuda: null argument"); return GORCH_CUDA_ERR_BAD_ARG; }
+  *status = 0;
+  if (!c->lmh_scratch.ptr) return GORCH_CUDA_OK;
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  CUDA_TRY(cudaMemcpyAsync(status, c->lmh_scratch.ptr, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream), errOut);
+  CUDA_TRY(cudaStreamSynchronize(c->stream), errOut);
+  return GORCH_CUDA_OK;
 }
 
 int gorch_cuda_sample_dev_static(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,

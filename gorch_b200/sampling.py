@@ -326,6 +326,29 @@ class CudaSampler:
                 self._lib.gorch_cuda_buffer_free(b)
         return ids, flags
 
+    # ---- the LM-head projection in front of the sampling step (model/qwen/qwen.go:80-85)
+    def lm_head_logits_ptrs(self, x_ptr: int, ldx: int, w_ptr: int, ldw: int, B: int, V: int, K: int,
+                            out_ptr: int, ld_out: int) -> None:
+        """gorch_cuda_lm_head_logits_dev: logits [B, V] f32 = x [B, K] bf16 @ w [V, K] bf16 ^T; device pointers."""
+        err = C.c_void_p()
+        rc = self._lib.gorch_cuda_lm_head_logits_dev(self._ctx, x_ptr, ldx, w_ptr, ldw, B, V, K, out_ptr, ld_out, C.byref(err))
+        _check(self._lib, rc, err)
+
+    def lm_head_sample_ptrs(self, x_ptr: int, ldx: int, w_ptr: int, ldw: int, B: int, V: int, K: int, fuse_top_k: int,
+                            cfgs_ptr: int, uniforms_ptr: int, ids_ptr: int, flags_ptr: int | None = None) -> None:
+        """gorch_cuda_lm_head_sample_dev: projection + sampling in one call; device pointers."""
+        err = C.c_void_p()
+        rc = self._lib.gorch_cuda_lm_head_sample_dev(self._ctx, x_ptr, ldx, w_ptr, ldw, B, V, K, int(fuse_top_k),
+                                                     cfgs_ptr, uniforms_ptr, ids_ptr, flags_ptr, C.byref(err))
+        _check(self._lib, rc, err)
+
+    def lm_head_status(self) -> int:
+        """Status word of the last LM-head call (blocking): 0, or bit 0 when a bounded device wait ran out."""
+        st = C.c_uint32(0)
+        err = C.c_void_p()
+        _check(self._lib, self._lib.gorch_cuda_lm_head_status(self._ctx, C.byref(st), C.byref(err)), err)
+        return int(st.value)
+
     # ---- tensor-level index ops (index_ops.go:153-227)
     def topk(self, x, k: int):
         """gorch.TopK over the last axis of x [B,V] (f32, or uint16 holding bf16): (values [B,k]

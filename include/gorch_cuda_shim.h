@@ -87,6 +87,7 @@ typedef struct {
   float vs_local_ms;        /* phases of the last timed gorch_cuda_sample_vocab_sharded_dev: local pass, */
   float vs_gather_ms;       /* all-gather, */
   float vs_merge_ms;        /* merge */
+  uint64_t lm_head_refused_rows; /* rows gorch_cuda_lm_head_sample_dev's fused form handed back (the batch was then redone unfused) */
 } GorchCudaCounters;
 
 /* ---- lifecycle: replaces metal_create_device / metal_create_command_queue /
@@ -311,6 +312,31 @@ int gorch_cuda_cross_entropy_bwd_dev(GorchCudaCtxRef ctx, const void* logits, in
                                      int64_t V, int64_t row_stride, const int32_t* targets,
                                      const float* row_lse, float scale, float* dx,
                                      int64_t dx_stride, char** errOut);
+
+/* The LM-head projection that produces the logits: logits[b, v] = sum_k x[b, k] * w[v, k], i.e.
+ * MatMulTransB(last, m.Embed.Weight) of model/qwen/qwen.go:80-85 (GPT-2: nn/gpt.go:119-120; the CPU
+ * loop is nn/extembed.go:152-195), for x [B, K] and w [V, K] in bf16 (bit patterns, row pitches ldx /
+ * ldw in elements) with f32 accumulation on the tensor cores. K must be a multiple of 64; pointers and
+ * row pitches multiples of 16 bytes. Device pointers, asynchronous on the context's stream.
+ * gorch_cuda_lm_head_status (blocking) reads the status word of the last LM-head call: 0, or bit 0 when
+ * a bounded device-side wait ran out (the output is then incomplete). */
+int gorch_cuda_lm_head_logits_dev(GorchCudaCtxRef ctx, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                                  int64_t B, int64_t V, int64_t K, float* out_logits, int64_t ld_out,
+                                  char** errOut);
+int gorch_cuda_lm_head_status(GorchCudaCtxRef ctx, uint32_t* status, char** errOut);
+/* The projection and the sampling step in one call: out_ids[b] = the token sampled from row b of
+ * x @ w^T under cfgs[b] with uniforms[b], as gorch_cuda_sample_dev would return on the materialised
+ * logits. fuse_top_k in 1..256: the batch's largest top_k; rows with temperature 0 or 0 < top_k <=
+ * fuse_top_k (DefaultGenerateConfig: T = 0.8, k = 40) are finished from candidate lists that the
+ * projection's epilogue fills, and the [B, V] logits are never written; the call then blocks until
+ * the ids are there, and if a row could not be finished that way (top_k off or above fuse_top_k, or
+ * a row whose largest logits a sample of the vocabulary misjudged) the whole batch is redone through
+ * the unfused form. fuse_top_k == 0 (or a vocabulary below 4096 columns): the unfused form at once:
+ * logits into scratch memory of the context, then the kernels of gorch_cuda_sample_dev
+ * (asynchronous). */
+int gorch_cuda_lm_head_sample_dev(GorchCudaCtxRef ctx, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                                  int64_t B, int64_t V, int64_t K, int fuse_top_k, const GorchSampleCfg* cfgs,
+                                  const double* uniforms, int32_t* out_ids, uint32_t* out_flags, char** errOut);
 
 /* One row, the exact shape of the reference's calls: sample(logits,
  * temperature, topK, topP) (generate.go:147) with the uniform passed in, and
