@@ -55,7 +55,7 @@ def parse():
                     help="short run for ncu: no e2e leg, no CPU baseline, no clock hold, no extra legs")
     ap.add_argument("--no-configs", action="store_true", help="skip the leg that times the other configs")
     ap.add_argument("--no-ops", action="store_true", help="skip the leg that times the row ops")
-    ap.add_argument("--op", default=None, choices=["softmax", "log_softmax", "ce_fwd", "ce_bwd", "topk", "multinomial"],
+    ap.add_argument("--op", default=None, choices=["softmax", "log_softmax", "ce_fwd", "ce_bwd", "topk", "multinomial", "lm_head"],
                     help="time one row op only (a small case for a profiler), print its line and exit")
     ap.add_argument("--op-rows", type=int, default=512)
     ap.add_argument("--op-vocab", type=int, default=151936)
@@ -385,6 +385,46 @@ def ops_leg(torch, smp, stream, flush, peak, only=None, rows=512, vocab=151936, 
     return res
 
 
+def lm_head_leg(torch, smp, stream, flush, peak, batches=(64, 512), V=151936, K=1024, iters=20, warmup=3):
+    """The projection in front of the sampling step (model/qwen/qwen.go:80-85) under the reference's
+    DefaultGenerateConfig (T = 0.8, top_k = 40): random bf16 activations and weights of the Qwen3-0.6B
+    LM head's shape. Times the projection alone (logits written), projection + sampling unfused (logits
+    through HBM) and fused (no logits written); GB/s = the weight matrix read once / time."""
+    from gorch_b200.config import CFG_DTYPE
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    w = (torch.randn(V, K, device="cuda", generator=gen) * 0.08).to(torch.bfloat16)
+    res = {}
+    for B in batches:
+        x = (torch.randn(B, K, device="cuda", generator=gen) * 0.5).to(torch.bfloat16)
+        out = torch.empty(B, V, device="cuda", dtype=torch.float32)
+        cfgs = np.zeros(B, dtype=CFG_DTYPE)
+        cfgs["temperature"], cfgs["top_k"] = 0.8, 40
+        dc = torch.from_numpy(cfgs.view(np.uint8).reshape(B, 16).copy()).cuda()
+        du = torch.rand(B, device="cuda", dtype=torch.float64, generator=gen)
+        ids = torch.empty(B, device="cuda", dtype=torch.int32)
+        fl = torch.empty(B, device="cuda", dtype=torch.int32)
+        ids_u = torch.empty(B, device="cuda", dtype=torch.int32)
+        proj = lambda: smp.lm_head_logits_ptrs(x.data_ptr(), K, w.data_ptr(), K, B, V, K, out.data_ptr(), V)
+        unf = lambda: smp.lm_head_sample_ptrs(x.data_ptr(), K, w.data_ptr(), K, B, V, K, 0, dc.data_ptr(), du.data_ptr(),
+                                              ids_u.data_ptr(), fl.data_ptr())
+        fus = lambda: smp.lm_head_sample_ptrs(x.data_ptr(), K, w.data_ptr(), K, B, V, K, 40, dc.data_ptr(), du.data_ptr(),
+                                              ids.data_ptr(), fl.data_ptr())
+        refused0 = smp.counters()["lm_head_refused_rows"]
+        t_proj, _ = time_steps(torch, stream, proj, iters, warmup, flush)
+        t_unf, _ = time_steps(torch, stream, unf, iters, warmup, flush)
+        t_fus, _ = time_steps(torch, stream, fus, iters, warmup, flush)
+        wbytes = V * K * 2
+        res[f"b{B}"] = {"rows": B, "vocab": V, "hidden": K, "config": "T=0.8 top_k=40",
+                        "projection_us": round(t_proj * 1e3, 1), "unfused_us": round(t_unf * 1e3, 1),
+                        "fused_us": round(t_fus * 1e3, 1),
+                        "fused_weight_gbs": round(wbytes / (t_fus / 1e3) / 1e9, 1),
+                        "fused_frac_of_hbm_peak": round(wbytes / (t_fus / 1e3) / 1e9 / peak, 4),
+                        "projection_tflops": round(2.0 * B * V * K / (t_proj / 1e3) / 1e12, 1),
+                        "fused_equals_unfused_ids": bool(torch.equal(ids, ids_u)),
+                        "rows_redone_unfused": int(smp.counters()["lm_head_refused_rows"] - refused0)}
+    return res
+
+
 def main():
     args = parse()
     if args.profile:
@@ -414,6 +454,13 @@ def main():
 
     if args.op is not None:                  # one row op, for a profiler
         flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device="cuda")
+        if args.op == "lm_head":
+            res = lm_head_leg(torch, smp, stream, flush, peak, batches=(args.op_rows,), V=args.op_vocab,
+                              iters=max(1, args.steps if args.steps < 200 else 20), warmup=max(1, args.warmup))
+            print(json.dumps({"op": "lm_head", **res[f"b{args.op_rows}"]}), flush=True)
+            smp.set_stream(None)
+            smp.release()
+            return
         res = ops_leg(torch, smp, stream, flush, peak, only=args.op, rows=args.op_rows, vocab=args.op_vocab,
                       dtype=args.op_dtype, topk=args.op_topk, iters=max(1, args.steps if args.steps < 200 else 20),
                       warmup=max(1, args.warmup))
@@ -565,6 +612,7 @@ def main():
                                               skip=args.workload if args.rows is None and args.mode is None else None)
             if not args.no_ops:
                 line["ops"] = ops_leg(torch, smp, stream, flush, peak)
+                line["lm_head"] = lm_head_leg(torch, smp, stream, flush, peak)
         if world == 1 and not args.no_cpu_baseline:
             from oracle import oracle as orc
             threads = orc.hw_threads()

@@ -36,7 +36,8 @@ constexpr int LMH_BK = 64;               // K per stage: 64 bf16 = one 128-byte 
 constexpr int LMH_STAGES = 5;
 constexpr int LMH_NT = 192;              // warp 0 producer, warp 1 issuer, warps 2-5 epilogue
 constexpr int LMH_STAGE_BYTES = (LMH_BM + LMH_BN) * LMH_BK * 2;     // 32 KB
-constexpr int LMH_DYN_BYTES = LMH_STAGES * LMH_STAGE_BYTES + 1024;  // + room to align the ring to 1024 bytes
+constexpr int LMH_ROWS_S = 8192;         // rows whose running maximum a CTA keeps in shared memory
+constexpr int LMH_DYN_BYTES = LMH_STAGES * LMH_STAGE_BYTES + 1024 + LMH_ROWS_S * 8;  // ring (+ room to align it to 1024 bytes) + row maxima and NaN bits
 constexpr int LMH_TMEM_COLS = 256;       // two accumulators of 128 f32 columns
 constexpr uint32_t LMH_WAIT_LIMIT = 4000000u;
 constexpr int LMH_CAND_CAP = 2048;       // candidates per row of the fused sampling path (entries of 8 bytes)
@@ -129,6 +130,12 @@ __global__ void __launch_bounds__(LMH_NT, 1) lm_head_kernel(const __grid_constan
   __shared__ int abort_s;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t ring = (smem_addr(lmh_dyn) + 1023u) & ~1023u;          // the swizzled tiles need 1024-byte alignment
+  // per-row running maximum and NaN bits of this CTA's tiles (a row always belongs to the same epilogue
+  // thread, so no atomics here); flushed to global memory once at the end
+  float* rowmax_s = reinterpret_cast<float*>(lmh_dyn + LMH_STAGES * LMH_STAGE_BYTES + 1024);
+  int* rownan_s = reinterpret_cast<int*>(rowmax_s + LMH_ROWS_S);
+  const bool rows_in_smem = A.rowmax_key != nullptr && A.B <= LMH_ROWS_S;
+  if (rows_in_smem) for (int r = tid; r < A.B; r += LMH_NT) { rowmax_s[r] = -INFINITY; rownan_s[r] = 0; }
   volatile int* abort_flag = &abort_s;
   const int nkc = A.K / LMH_BK;                                        // K chunks per tile
   const int nbt = (A.B + LMH_BM - 1) / LMH_BM;                         // batch tiles
@@ -231,10 +238,19 @@ __global__ void __launch_bounds__(LMH_NT, 1) lm_head_kernel(const __grid_constan
               }
             }
             if (A.rowmax_key) {
+              // the chunk's maximum first (NaN-propagating): only a chunk that holds a candidate, a NaN
+              // or columns past the vocabulary is looked at logit by logit
+              float cm = max3nan(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
 #pragma unroll
-              for (int j = 0; j < 32; j++) {
-                const float x = __uint_as_float(r[j]);
-                if (j < nvalid) {
+              for (int j = 3; j + 1 < 32; j += 2) cm = max3nan(cm, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+              cm = maxnan(cm, __uint_as_float(r[31]));
+              if (nvalid == 32 && cm < thr) {                          // (false for a NaN maximum)
+                vmax = fmaxf(vmax, cm);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                  const float x = __uint_as_float(r[j]);
+                  if (j >= nvalid) continue;
                   if (x != x) nan_bits |= (v0 + c + j == 0) ? 3 : 1;
                   vmax = fmaxf(vmax, x);
                   if (x >= thr) {
@@ -251,8 +267,13 @@ __global__ void __launch_bounds__(LMH_NT, 1) lm_head_kernel(const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_addr(&acc_empty[acc]));
         if (A.rowmax_key && live) {
-          atomicMax(&A.rowmax_key[row], okey(vmax));
-          if (nan_bits) atomicOr(&A.row_nan[row], nan_bits);
+          if (rows_in_smem) {
+            rowmax_s[row] = fmaxf(rowmax_s[row], vmax);
+            rownan_s[row] |= nan_bits;
+          } else {
+            atomicMax(&A.rowmax_key[row], okey(vmax));
+            if (nan_bits) atomicOr(&A.row_nan[row], nan_bits);
+          }
         }
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
@@ -261,6 +282,13 @@ __global__ void __launch_bounds__(LMH_NT, 1) lm_head_kernel(const __grid_constan
   // ---- teardown
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (rows_in_smem) {
+    for (int r = tid; r < A.B; r += LMH_NT) {
+      const float v = rowmax_s[r];
+      if (v > -INFINITY) atomicMax(&A.rowmax_key[r], okey(v));
+      if (rownan_s[r]) atomicOr(&A.row_nan[r], rownan_s[r]);
+    }
+  }
   if (abort_s) {
     // a wait ran out: give the copies and MMAs still in flight time to land before the shared and
     // tensor memory they target is given back (bounded: about a millisecond)
