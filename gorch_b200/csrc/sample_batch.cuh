@@ -69,8 +69,9 @@ struct BatchArgs {
   int64_t B;
 };
 
-// 0: narrow kernel, 1: wide kernel, 2: single-CTA kernel
+// 0: narrow kernel, 1: wide kernel, 2: single-CTA kernel, 3: nobody (the row's sequence has ended)
 __device__ __forceinline__ int row_kind(const KernelArgs& A, int64_t b) {
+  if (A.row_done && A.row_done[b] != 0) return 3;
   if (A.force_greedy || A.vs_records || A.tk_k > 0) return 0;
   const RowCfg c = A.cfgs[b];
   const float T = c.temperature;

@@ -207,6 +207,8 @@ __global__ void __launch_bounds__(NT, 2) sample_cluster_kernel(ClusterArgs CA) {
   __shared__ uint32_t s_sel[256];
 
   cg::cluster_group cluster = cg::this_cluster();
+  // a row whose sequence has ended (model/generate.go:82-84) is skipped by its whole cluster, before any barrier
+  if (CA.k.row_done && CA.k.row_done[CA.k.row_offset + blockIdx.x / cluster.num_blocks()] != 0) return;
   cluster.barrier_arrive();          // matched by the wait before the first remote store
   const int C = static_cast<int>(cluster.num_blocks());
   const int rank = static_cast<int>(cluster.block_rank());

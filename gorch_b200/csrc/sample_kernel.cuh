@@ -58,6 +58,7 @@ struct KernelArgs {
   float* tk_values;        // TopK op (narrow kernel only): [B, tk_k] values, descending; null otherwise
   int32_t* tk_indices;     // [B, tk_k] indices (ties: ascending index)
   int32_t tk_k;            // 0: not a TopK launch
+  const int32_t* row_done; // generate loops: rows whose entry is non-zero have ended and are skipped (null: none)
 };
 
 template <typename T> struct Elem;
@@ -1228,7 +1229,9 @@ __global__ void __launch_bounds__(NT, 2) sample_rows_kernel(KernelArgs A) {
       __syncthreads();
     }
   } else {
-    single_cta_row<T>(A, A.row_offset + blockIdx.x, pool);
+    const int64_t row = A.row_offset + blockIdx.x;
+    if (A.row_done && A.row_done[row] != 0) return;        // the sequence has ended (model/generate.go:82-84)
+    single_cta_row<T>(A, row, pool);
   }
 }
 

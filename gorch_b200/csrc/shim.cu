@@ -219,7 +219,7 @@ size_t elem_size(int dtype) { return dtype == GORCH_CUDA_BF16 ? 2 : 4; }
 int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int64_t row_stride,
                 const GorchSampleCfg* cfgs, const double* uniforms, int32_t* out_ids,
                 uint32_t* out_flags, double* out_probs, GorchSampleDebug* out_debug,
-                int force_greedy, char** errOut, int32_t* fixed_lists = nullptr) {
+                int force_greedy, char** errOut, int32_t* fixed_lists = nullptr, const int32_t* row_done = nullptr) {
   // fixed_lists: caller-provided storage for the row work lists (16 + B + 1 words) instead of the
   // context's grow-only allocation; with it nothing in here allocates.
   if (B == 0) return GORCH_CUDA_OK;
@@ -246,6 +246,7 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
   a.vs_records = nullptr;
   a.vs_col_offset = 0;
   a.vs_cand = gs::VS_CAND;
+  a.row_done = row_done;
   a.tk_values = nullptr;
   a.tk_indices = nullptr;
   a.tk_k = 0;
@@ -784,7 +785,7 @@ static int vocab_local_launch(Ctx* c, const void* logits, int dtype, int64_t B, 
   ba.k.out_ids = nullptr; ba.k.out_flags = nullptr; ba.k.out_probs = nullptr; ba.k.out_debug = nullptr;
   ba.k.exp_table = c->exp_table; ba.k.row_offset = 0; ba.k.worklist = nullptr;
   ba.k.vs_records = records; ba.k.vs_col_offset = static_cast<int32_t>(col_offset); ba.k.vs_cand = cand;
-  ba.k.tk_values = nullptr; ba.k.tk_indices = nullptr; ba.k.tk_k = 0;
+  ba.k.tk_values = nullptr; ba.k.tk_indices = nullptr; ba.k.tk_k = 0; ba.k.row_done = nullptr;
   ba.eb_table = c->eb_table;
   ba.hdr = base; ba.list_single = base + 15;
   ba.B = B;
@@ -815,7 +816,7 @@ static int vocab_merge_launch(Ctx* c, const void* all_records, int nranks, int c
   m.k.out_ids = out_ids; m.k.out_flags = out_flags; m.k.out_probs = nullptr; m.k.out_debug = nullptr;
   m.k.exp_table = c->exp_table; m.k.row_offset = 0; m.k.worklist = nullptr; m.k.vs_records = nullptr; m.k.vs_col_offset = 0;
   m.k.vs_cand = cand;
-  m.k.tk_values = nullptr; m.k.tk_indices = nullptr; m.k.tk_k = 0;
+  m.k.tk_values = nullptr; m.k.tk_indices = nullptr; m.k.tk_k = 0; m.k.row_done = nullptr;
   m.records = all_records;
   m.nranks = nranks;
   m.cand = cand;
@@ -965,7 +966,7 @@ int gorch_cuda_topk_dev(GorchCudaCtxRef ctx, const void* x, int dtype, int64_t B
   ba.k.out_ids = nullptr; ba.k.out_flags = out_flags; ba.k.out_probs = nullptr; ba.k.out_debug = nullptr;
   ba.k.exp_table = c->exp_table; ba.k.row_offset = 0; ba.k.worklist = nullptr;
   ba.k.vs_records = nullptr; ba.k.vs_col_offset = 0;
-  ba.k.tk_values = out_values; ba.k.tk_indices = out_indices; ba.k.tk_k = static_cast<int32_t>(k);
+  ba.k.tk_values = out_values; ba.k.tk_indices = out_indices; ba.k.tk_k = static_cast<int32_t>(k); ba.k.row_done = nullptr;
   ba.eb_table = c->eb_table;
   ba.hdr = base; ba.list_single = base + 15;
   ba.B = B;
@@ -1048,10 +1049,24 @@ int gorch_cuda_generate_step_dev(GorchCudaCtxRef ctx, const void* logits, int dt
                                  int64_t V, int64_t row_stride, const GorchSampleCfg* cfgs,
                                  const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
                                  const GorchGenControl* gc, char** errOut) {
-  int rc = gorch_cuda_sample_dev(ctx, logits, dtype, B, V, row_stride, cfgs, uniforms, out_ids, out_flags,
-                                 nullptr, nullptr, errOut);
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if (!gc) { set_err(errOut, "gorch_cuda: null generate-control record"); return GORCH_CUDA_ERR_BAD_ARG; }
+  int rc = check_shape(dtype, B, V, row_stride, errOut);
   if (rc) return rc;
-  return launch_generate_control(static_cast<Ctx*>(ctx), out_ids, out_flags, gc, B, errOut);
+  if (B > 0) {
+    if (!logits || !cfgs || !uniforms || !out_ids || !gc->done) {
+      set_err(errOut, "gorch_cuda: null pointer argument");
+      return GORCH_CUDA_ERR_BAD_ARG;
+    }
+    CUDA_TRY(cudaSetDevice(c->device), errOut);
+    // rows whose sequence has ended are skipped by the sampling kernels (the reference leaves its loop,
+    // model/generate.go:82-84); their out_ids / out_flags entries keep what they held
+    rc = launch_rows(c, logits, dtype, B, V, row_stride, cfgs, uniforms, out_ids, out_flags, nullptr, nullptr, 0, errOut,
+                     nullptr, gc->done);
+    if (rc) return rc;
+  }
+  return launch_generate_control(c, out_ids, out_flags, gc, B, errOut);
 }
 
 static int launch_row_softmax(Ctx* c, int dtype, const gs::RowSoftmaxArgs& a, char** errOut) {

@@ -283,7 +283,9 @@ typedef struct {
 int gorch_cuda_generate_control_dev(GorchCudaCtxRef ctx, const int32_t* ids, const uint32_t* flags,
                                     const GorchGenControl* gc, int64_t B, char** errOut);
 /* gorch_cuda_sample_dev followed by the control step in one call: out_ids / out_flags receive the
- * sampled ids as usual (rows that are no longer live are sampled too and ignored). */
+ * sampled ids of the live rows; rows that have ended (done[b] != GORCH_GEN_LIVE) are skipped by the
+ * sampling kernels, as the reference leaves its loop (model/generate.go:82-84), and their entries
+ * of out_ids / out_flags keep what they held. */
 int gorch_cuda_generate_step_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, int64_t B,
                                  int64_t V, int64_t row_stride, const GorchSampleCfg* cfgs,
                                  const double* uniforms, int32_t* out_ids, uint32_t* out_flags,

@@ -10,6 +10,7 @@ from gorch_b200.config import CFG_DTYPE, DTYPE_BF16, DTYPE_F32, MODE_A, MODE_B, 
 from gorch_b200.generate import (GEN_ERROR, GEN_LIVE, LOOP_CACHED, LOOP_QWEN, LOOP_UNCACHED,
                                  DeviceGenerateState, generate_on_device)
 from gorch_b200.sampling import GorchCudaError, generate_with_config, qwen_generate
+from tests.parity import compare
 
 pytestmark = pytest.mark.gpu
 
@@ -229,3 +230,53 @@ def test_batched_generation_on_device_matches_the_host_loops(_sampler_session, o
         assert got["tokens"][b] == want, (loop, b)
         ended.add(int(got["done"][b]))
     assert GEN_LIVE not in ended and len(ended) >= 2       # the batch exercises more than one way to end
+
+
+@pytest.mark.parametrize("B,bf16", [(6, False), (40, True), (300, False)])
+def test_rows_that_have_ended_are_not_sampled(sampler, oracle, B, bf16):
+    """gorch_cuda_generate_step_dev hands the loop's own end marks to the sampling kernels: a row
+    whose sequence has ended keeps what out_ids / out_flags held, the live rows get exactly the ids
+    the oracle draws, and the loop appends to the live rows only. Every dispatch (small-batch
+    cluster kernel, batch kernels, single-CTA kernel) and every row kind."""
+    from gorch_b200 import workloads
+    s = sampler
+    rng = np.random.default_rng(900 + B)
+    V = 5000
+    x = (rng.standard_normal((B, V)) * 2.5).astype(np.float32)
+    logits = workloads.f32_to_bf16_bits(x) if bf16 else x
+    cfgs = np.zeros(B, dtype=CFG_DTYPE)
+    for b in range(B):
+        cfgs[b] = [(0.0, 0, 0.0, MODE_A), (0.8, 40, 0.0, MODE_A), (1.1, 0, 0.9, MODE_B), (0.7, 50, 0.95, MODE_B),
+                   (0.9, 700, 0.9, MODE_B)][b % 5]
+    u = rng.random(B)
+    ended = rng.random(B) < 0.4
+    ended[0], ended[B - 1] = True, False
+    prompts = [[1, 2, 3] for _ in range(B)]
+    st = DeviceGenerateState(s, prompts, 4, 64, [], LOOP_QWEN)
+    bufs = []
+    try:
+        done = np.where(ended, 2, GEN_LIVE).astype(np.int32)
+        s._upload(st._bufs["done"], done)
+        s._upload(st._bufs["ids"], np.full(B, -7, dtype=np.int32))
+        s._upload(st._bufs["flags"], np.full(B, 0x7777, dtype=np.int32))
+        ptr = s._lib.gorch_cuda_buffer_device_ptr
+        for arr in (np.ascontiguousarray(logits), cfgs, np.ascontiguousarray(u)):
+            b_ = s._buf(arr.nbytes); bufs.append(b_); s._upload(b_, arr)
+        st.step(ptr(bufs[0]), DTYPE_BF16 if bf16 else DTYPE_F32, V, V, ptr(bufs[1]), ptr(bufs[2]))
+        ids = st._get("ids", B)
+        flags = st._get("flags", B)
+        r = st.results()
+    finally:
+        for b_ in bufs:
+            s._lib.gorch_cuda_buffer_free(b_)
+        st.release()
+    assert np.all(ids[ended] == -7) and np.all(flags[ended] == 0x7777)
+    live = np.nonzero(~ended)[0]
+    want = oracle.sample_batch(np.ascontiguousarray(logits[live]), np.ascontiguousarray(cfgs[live]),
+                               np.ascontiguousarray(u[live]), flags=oracle.FAST_KTH, threads=oracle.hw_threads())
+    rep = compare({"ids": ids[live], "flags": flags[live].view(np.uint32)}, want, u[live], check_probs=False,
+                  allow_tie_cut=True)
+    assert rep["id_mismatch"] == rep["boundary_mismatch"]
+    for b in range(B):
+        assert r["tokens"][b] == ([1, 2, 3] if ended[b] else [1, 2, 3, int(ids[b])])
+        assert r["done"][b] == (2 if ended[b] else GEN_LIVE)
