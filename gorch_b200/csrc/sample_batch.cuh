@@ -33,10 +33,18 @@ namespace gs {
 
 constexpr int N_NT = 256;               // narrow kernel threads
 constexpr int N_NW = N_NT / 32;
-constexpr int N_CAP = 4096;             // candidate capacity (entries of 8 B)
+constexpr int N_CAP = 3072;             // candidate capacity (entries of 8 B)
 constexpr int N_KEEP = 1536;            // a prune must get below this
 constexpr int N_WARM_ELEMS = 4096;      // logits of the warm-up chunk
-constexpr int N_DYN_BYTES = 16384 + N_CAP * 8;
+constexpr int N_HITS = 2048;            // hit list: positions of lane-steps that hold a candidate (4 B each)
+constexpr int N_DYN_BYTES = 16384 + N_CAP * 8 + N_HITS * 4;
+#ifndef GS_N_NQ_BF16
+#define GS_N_NQ_BF16 2
+#endif
+#ifndef GS_N_NQ_F32
+#define GS_N_NQ_F32 2
+#endif
+constexpr int N_NQ_BF16 = GS_N_NQ_BF16, N_NQ_F32 = GS_N_NQ_F32;   // register loads in flight per lane, in steps
 
 
 // Vocab-sharded sampling: what one rank knows about one row of its column slice. cand holds every
@@ -221,6 +229,7 @@ __device__ void finish_small_set(const KernelArgs& A, int64_t row_id, const uint
     if (u - tot <= 1e-6) flags |= FLAG_BOUNDARY;
   }
   (void)bc_d;
+  dbg.reserved[4] = static_cast<uint32_t>(clock64());       // with reserved[3]: the row's whole time on its CTA
   write_row(id, flags);
 }
 
@@ -232,7 +241,7 @@ __device__ __forceinline__ uint4 mask_edges(const RowView<T>& rv, int v, uint4 r
 // ---------------------------------------------------------------------------
 template <typename T>
 __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned char* dyn, bu::Scratch& sc,
-                           uint32_t* s_sel, int* s_bc, double* s_bcd, int* s_cnt, float* s_thr, int* s_flag,
+                           uint32_t* s_sel, int* s_bc, double* s_bcd, int* s_cnt, int* s_hcnt, float* s_thr, int* s_flag,
                            const bool allow_tight, bool& redo) {
   const KernelArgs& A = BA.k;
   redo = false;
@@ -245,6 +254,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   rv.init(row, V);
   uint4* chunk = reinterpret_cast<uint4*>(dyn);              // warm-up vectors, 16 KB; later work arrays
   uint2* cand = reinterpret_cast<uint2*>(dyn + 16384);       // N_CAP entries
+  int* hits = reinterpret_cast<int*>(dyn + 16384 + N_CAP * 8);   // N_HITS entries
   const double QNAN = __longlong_as_double(0x7ff8000000000000ll);
 
   RowCfg cfg;
@@ -257,6 +267,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   dbg.max_scaled = 0; dbg.threshold = __int_as_float(0x7fc00000); dbg.path = 0;
   for (int q = 0; q < 8; q++) dbg.reserved[q] = 0;
   long long tprev = clock64();
+  dbg.reserved[3] = static_cast<uint32_t>(tprev);
   auto stamp = [&](int slot) { const long long now = clock64(); dbg.reserved[slot] = static_cast<uint32_t>(now - tprev); tprev = now; };
   auto write_row = [&](int id, uint32_t fl) {
     if (tid == 0) {
@@ -332,7 +343,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   // ---- warm-up chunk: park it, one running maximum per thread
   float xmax = -INFINITY, xmin = INFINITY;
   bool nan_seen = false;
-  if (tid == 0) { *s_cnt = 0; *s_flag = 0; }
+  if (tid == 0) { *s_cnt = 0; *s_hcnt = 0; *s_flag = 0; }
   const int warm = min(rv.nvec, WARM_VECS);
   {
     constexpr int G = WARM_VECS / N_NT;
@@ -343,61 +354,63 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
       if (v < warm) { r[g] = load_masked(rv, v, xmax, xmin, nan_seen); chunk[v] = r[g]; }
     }
   }
-  // thr: lower edge of the 16-bit key bin holding the k-th largest per-thread maximum. Never
-  // -Inf: a -Inf logit has probability 0 whether or not top-k keeps it, so it is never a candidate
-  // (a masked vocabulary would otherwise flood the list with ties at -Inf). A row with fewer than
+  // The stream's first loads go out now, so that they are in flight during the selection below.
+  constexpr int SV = 32 * (8 / VEC);
+  constexpr int NQ = (VEC == 8) ? N_NQ_BF16 : N_NQ_F32;      // steps in flight
+  const int lane = tid & 31, warp = tid >> 5;
+  const int rest = max(rv.nvec - warm, 0);
+  const int span = (((rest + N_NW - 1) / N_NW + SV - 1) / SV) * SV;
+  const WSpan sp = make_span<T>(rv, warm + warp * span, span, lane);
+  unsigned long long pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  uint4 qa[NQ], qb[NQ];
+#pragma unroll
+  for (int q = 0; q < NQ; q++) w_load<T, N_PF>(sp, q, pol, qa[q], qb[q]);
+  // Threshold from the 256 per-thread maxima of the chunk, each thread counting how many of them
+  // order before its own (one barrier; a radix select over so few keys costs several rounds of
+  // barriers and of shared atomics that all hit the same few bins).
+  //  * The top_k-th largest maximum is a BOUND: top_k threads each hold a logit at or above it, so
+  //    the top_k-th largest logit of the row is at or above it.
+  //  * The r-th largest maximum with r < top_k, r chosen so that about four times top_k logits of
+  //    the whole row are expected above it, is an ESTIMATE (`tight`). If the row ends with at
+  //    least top_k candidates, its top_k-th largest is among them and nothing was lost; if not
+  //    (the chunk was not typical of the row), the row is redone: by the single-CTA kernel when it
+  //    is a sampling row, by this kernel without the estimate (`redo`) when it is a TopK row or a
+  //    vocab-sharded slice, which that kernel does not serve.
+  // Either way the threshold is lowered to the edge of its class of equal quotients x / T (what
+  // ties with the k-th largest after the division is then collected too), and it is never -Inf:
+  // a -Inf logit has probability 0 whether or not top-k keeps it, so it is never a candidate (a
+  // masked vocabulary would otherwise flood the list with ties at -Inf); a row with fewer than
   // top_k finite logits simply ends with fewer candidates.
   constexpr float LOWEST = -3.402823466e+38f;
   float thr = LOWEST;
+  bool tight = false;
   {
-    uint32_t prefix = 0, mask = 0;
-    int need = topk;
+    int rank = topk;
+    if (allow_tight && rv.nvec > warm) {
+      const long long welems = static_cast<long long>(warm) * VEC;
+      const int r = static_cast<int>((4ll * topk * welems + V - 1) / V) + 4;
+      if (r < topk) { rank = r; tight = true; }
+    }
     const uint32_t mykey = okey(xmax);
-    bool have_thr = true;
-    for (int round = 0; round < 2; round++) {
-      const int sh = 24 - 8 * round;
-      __syncthreads();
-      s_sel[tid] = 0;
-      if (tid == 0) s_bc[0] = -1;
-      __syncthreads();
-      if ((mykey & mask) == prefix) atomicAdd(&s_sel[(mykey >> sh) & 255u], 1u);
-      __syncthreads();
-      if (tid < 32) {
-        int loc[8];
-        int s = 0;
-#pragma unroll
-        for (int j = 7; j >= 0; j--) { s += static_cast<int>(s_sel[tid * 8 + j]); loc[j] = s; }
-        int run = s;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int t = __shfl_down_sync(FULL, run, o);
-          if (tid + o < 32) run += t;
-        }
-        const int above = run - s;
-        if (above < need && above + s >= need) {
-#pragma unroll
-          for (int j = 7; j >= 0; j--) {
-            if (above + loc[j] >= need) {
-              s_bc[0] = tid * 8 + j;
-              s_bc[1] = need - (above + loc[j] - static_cast<int>(s_sel[tid * 8 + j]));
-              break;
-            }
-          }
-        }
-      }
-      __syncthreads();
-      if (s_bc[0] < 0) { have_thr = false; break; }
-      prefix |= static_cast<uint32_t>(s_bc[0]) << sh;
-      mask |= 255u << sh;
-      need = s_bc[1];
-    }
-    if (prefix <= 0x007fffffu) have_thr = false;             // bound at or below -Inf: keep everything
+    s_sel[tid] = mykey;
+    if (tid == 0) *s_thr = LOWEST;
     __syncthreads();
-    if (have_thr) {
-      if (tid == 0) *s_thr = quotient_class_floor(okey_to_float(prefix), Tm);
-      __syncthreads();
-      thr = fmaxf(*s_thr, LOWEST);
+    int before = 0;                                          // maxima that order before mine: larger, or equal at a lower thread
+    const uint4* k4 = reinterpret_cast<const uint4*>(s_sel);
+#pragma unroll 4
+    for (int j = 0; j < N_NT / 4; j++) {
+      const uint4 kk = k4[j];
+      before += (kk.x > mykey || (kk.x == mykey && 4 * j + 0 < tid)) ? 1 : 0;
+      before += (kk.y > mykey || (kk.y == mykey && 4 * j + 1 < tid)) ? 1 : 0;
+      before += (kk.z > mykey || (kk.z == mykey && 4 * j + 2 < tid)) ? 1 : 0;
+      before += (kk.w > mykey || (kk.w == mykey && 4 * j + 3 < tid)) ? 1 : 0;
     }
+    if (before == rank - 1 && mykey > 0x007fffffu)           // at or below -Inf: keep everything
+      *s_thr = fmaxf(quotient_class_floor(xmax, Tm), LOWEST);
+    __syncthreads();
+    thr = *s_thr;
+    if (thr == LOWEST) tight = false;
   }
   // candidates of the warm-up chunk
   for (int v = tid; v < warm; v += N_NT) {
@@ -409,51 +422,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
       const int i = i0 + c;
       if (x[c] >= thr && i >= 0 && i < V) {
         const int slot = atomicAdd(s_cnt, 1);
-        cand[slot] = make_uint2(__float_as_uint(x[c]), static_cast<uint32_t>(i));
-      }
-    }
-  }
-  __syncthreads();
-  // A tighter threshold for the rest of the row, taken as an estimate rather than a bound: the
-  // r-th largest logit of the warm-up chunk, with r chosen so that about four times top_k logits
-  // of the whole row are expected above it. If the row ends with at least top_k candidates, its
-  // top_k-th largest is among them and nothing was lost; if not (the chunk was not typical of
-  // the row), the row is redone: by the single-CTA kernel when it is a sampling row, by this kernel
-  // without the estimate (`redo`) when it is a TopK row or a vocab-sharded slice, which that kernel
-  // does not serve.
-  bool tight = false;
-  if (allow_tight && rv.nvec > warm) {
-    const int cnt0 = *s_cnt;
-    const long long welems = static_cast<long long>(warm) * VEC;
-    const int r = static_cast<int>((4ll * topk * welems + V - 1) / V) + 4;
-    if (r < cnt0) {                                          // uniform
-      const uint32_t rkey = bu::select_kth<N_NT>(cand, cnt0, r, s_sel, s_bc, tid);
-      // lower edge of its class of equal quotients x / T, like every threshold here: whatever ties
-      // with the k-th largest after the division is then collected too
-      const float t = quotient_class_floor(okey_to_float(rkey), Tm);
-      __syncthreads();
-      if (t > thr) {
-        // The list keeps only what passes the estimate, so that the count at the end of the row
-        // says whether top_k logits passed it (entries below it would hide a failed estimate, and
-        // a later prune would take its k-th largest from them).
-        uint2* tmp = reinterpret_cast<uint2*>(chunk);        // 2048 entries; the warm-up vectors are used up
-        if (tid == 0) *s_cnt = 0;
-        __syncthreads();
-        for (int j = tid; j < cnt0; j += N_NT) {
-          const uint2 e = cand[j];
-          if (__uint_as_float(e.x) >= t) { const int slot = atomicAdd(s_cnt, 1); if (slot < 2048) tmp[slot] = e; }
-        }
-        __syncthreads();
-        const int kept = *s_cnt;
-        __syncthreads();
-        if (kept <= 2048) {
-          for (int j = tid; j < kept; j += N_NT) cand[j] = tmp[j];
-          thr = t;
-          tight = true;
-        } else if (tid == 0) {
-          *s_cnt = cnt0;                                     // a long run of ties at the estimate: go on without it
-        }
-        __syncthreads();
+        if (slot < N_CAP) cand[slot] = make_uint2(__float_as_uint(x[c]), static_cast<uint32_t>(i));
       }
     }
   }
@@ -479,27 +448,40 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   };
   // ---- stream the rest of the row: every warp walks its own span of it, eight logits per lane
   // and step (two 16-byte vectors of f32, one of bf16), loaded NQ steps ahead in registers. No
-  // barrier per step: a warp that sees the list past TRIGGER raises *s_flag; every warp looks at
-  // the flag before each step and comes to the barrier below, where the list is pruned to the
-  // exact k-th largest, and then walks on. Between the flag going up and a warp seeing it that
-  // warp appends at most one step (256 entries, 2048 for the block): the room above TRIGGER.
-  constexpr int SV = 32 * (8 / VEC);
-  constexpr int NQ = 2;                                      // steps in flight
-  constexpr int TRIGGER = N_CAP - N_NW * 32 * 8;
-  static_assert(TRIGGER >= N_KEEP, "a pruned list must sit below the trigger");
-  const int lane = tid & 31, warp = tid >> 5;
-  const int rest = max(rv.nvec - warm, 0);
-  const int span = (((rest + N_NW - 1) / N_NW + SV - 1) / SV) * SV;
-  const WSpan sp = make_span<T>(rv, warm + warp * span, span, lane);
-  unsigned long long pol;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  // barrier per step. A lane whose eight logits hold one at or above the threshold only notes WHERE
+  // (its vector index, 4 bytes in the hit list): unpacking and appending on the spot would cost
+  // the whole warp some hundred instructions on nearly every other step. The noted vectors are read
+  // again (from L2, or HBM at worst) by all threads at once after the stream, or when the hit
+  // list fills: a warp that sees it past H_TRIGGER raises *s_flag; every warp looks at the flag
+  // before each step and comes to the barrier below, where the hits are resolved into the
+  // candidate list and that is pruned to the exact k-th largest; then the warps walk on. Between
+  // the flag going up and a warp seeing it, each of its lanes notes at most one more hit: the
+  // room above H_TRIGGER. Steps that hold the row's edges (at most two per warp) append their
+  // logits directly, masked by index.
+  constexpr int H_TRIGGER = N_HITS - N_NT;
   volatile int* vflag = s_flag;
   float run = xmax;                                          // NaN-propagating running maximum of this thread
   int st = 0;
-  uint4 qa[NQ], qb[NQ];
+  // hits -> candidates: every thread re-reads the vectors of its share of the noted lane-steps
+  auto resolve_hits = [&](int first_hit, int nh) {
+    for (int j = first_hit + tid; j < first_hit + nh; j += N_NT) {
+      const int gv = hits[j];
 #pragma unroll
-  for (int q = 0; q < NQ; q++) w_load<T, N_PF>(sp, q, pol, qa[q], qb[q]);
-  if (*s_cnt >= TRIGGER && tid == 0) *s_flag = 1;            // the warm-up chunk alone may have filled it
+      for (int h = 0; h < 8 / VEC; h++) {
+        const int g = gv + 32 * h;
+        float x[VEC];
+        Elem<T>::unpack(__ldg(rv.vbase + g), x);
+        const int i0 = g * VEC - rv.shift;
+#pragma unroll
+        for (int c = 0; c < VEC; c++) {
+          if (x[c] >= thr) {                                 // clean steps only: every index is inside the row
+            const int slot = atomicAdd(s_cnt, 1);
+            if (slot < N_CAP) cand[slot] = make_uint2(__float_as_uint(x[c]), static_cast<uint32_t>(i0 + c));
+          }
+        }
+      }
+    }
+  };
   __syncthreads();
   for (;;) {                                                 // uniform: one trip per prune, plus one
 #pragma unroll 1
@@ -508,13 +490,15 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
 #pragma unroll
       for (int q = 0; q + 1 < NQ; q++) { qa[q] = qa[q + 1]; qb[q] = qb[q + 1]; }
       w_load<T, N_PF>(sp, st + NQ, pol, qa[NQ - 1], qb[NQ - 1]);
-      const bool clean = st < sp.clean_hi;                   // else: the row's last vector, or past the end
-      float hi8 = -INFINITY;
-      if (clean) {
-        hi8 = step_max_nan<T>(ca, cb);
+      if (st < sp.clean_hi) {                                // no logit outside the row in this step
+        const float hi8 = step_max_nan<T>(ca, cb);
         run = maxnan(run, hi8);
-      }
-      if (!clean || hi8 >= thr) {                            // this lane holds a logit for the list (or an edge)
+        if (hi8 >= thr) {
+          const int slot = atomicAdd(s_hcnt, 1);
+          hits[min(slot, N_HITS - 1)] = sp.first + st * SV + lane;   // never past H_TRIGGER + N_NT: see above
+          if (slot >= H_TRIGGER) *vflag = 1;
+        }
+      } else {                                               // the row's last vector, or past the end
         float x[8];
         if (VEC == 4) { Elem<T>::unpack(ca, x); Elem<T>::unpack(cb, x + 4 * (8 / VEC - 1)); }
         else Elem<T>::unpack(ca, x);
@@ -523,12 +507,11 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
         for (int c = 0; c < 8; c++) {
           const int g = gv + 32 * (c / VEC);
           const int i = g * VEC - rv.shift + (c % VEC);
-          if (clean || (g < rv.nvec && i < V)) {
-            if (!clean) run = maxnan(run, x[c]);
+          if (g < rv.nvec && i < V) {
+            run = maxnan(run, x[c]);
             if (x[c] >= thr) {
               const int slot = atomicAdd(s_cnt, 1);
               if (slot < N_CAP) cand[slot] = make_uint2(__float_as_uint(x[c]), static_cast<uint32_t>(i));
-              if (slot >= TRIGGER) *vflag = 1;
             }
           }
         }
@@ -537,14 +520,29 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     }
     const int more = __syncthreads_or((st < sp.nst) ? 1 : 0);
     const int full = __syncthreads_or(*vflag);               // every thread reads it before anyone can raise it again
-    if (full) {
-      const int raw = *s_cnt;
+    if (full || !more) {
+      const int nh = min(*s_hcnt, N_HITS);                   // never above N_HITS: the trigger's room
       __syncthreads();
-      if (tid == 0) *s_flag = 0;
-      __syncthreads();
-      if (raw > N_CAP) { giveup = true; break; }             // entries were dropped
-      const int cnt = prune(raw);
-      if (cnt > N_KEEP) { giveup = true; break; }            // ties at the threshold fill the buffer
+      if (tid == 0) { *s_flag = 0; *s_hcnt = 0; }
+      // A hit stands for up to eight candidates, so the hits are resolved in portions that fit the
+      // candidate list, with a prune (which raises the threshold) between them. Ordinarily one
+      // portion takes them all; a row whose threshold is far too low (a start well below the rest
+      // of the row) notes a hit in every lane-step and needs a few.
+      int done = 0;
+      for (;;) {                                             // uniform
+        const int c0 = *s_cnt;
+        __syncthreads();
+        if (c0 > N_CAP) { giveup = true; break; }            // entries were dropped
+        const int take = min(nh - done, (N_CAP - c0) / 8);
+        resolve_hits(done, take);
+        done += take;
+        __syncthreads();
+        if (done >= nh && !full) break;
+        const int cnt = prune(*s_cnt);
+        if (cnt > N_KEEP) { giveup = true; break; }          // ties at the threshold fill the buffer
+        if (done >= nh) break;
+      }
+      if (giveup) break;
     }
     if (!more) break;
   }
@@ -625,6 +623,7 @@ __global__ void __launch_bounds__(N_NT, 4) narrow_rows_kernel(BatchArgs BA) {
   __shared__ int s_bc[4];
   __shared__ double s_bcd[4];
   __shared__ int s_cnt;
+  __shared__ int s_hcnt;
   __shared__ float s_thr;
   __shared__ int s_flag;
   __shared__ int s_row;
@@ -647,7 +646,7 @@ __global__ void __launch_bounds__(N_NT, 4) narrow_rows_kernel(BatchArgs BA) {
     if (row < 0) break;
     bool redo, allow_tight = true;
     for (;;) {                                               // at most twice: the second time without the estimate
-      narrow_row<T>(BA, row, dyn, sc, s_sel, s_bc, s_bcd, &s_cnt, &s_thr, &s_flag, allow_tight, redo);
+      narrow_row<T>(BA, row, dyn, sc, s_sel, s_bc, s_bcd, &s_cnt, &s_hcnt, &s_thr, &s_flag, allow_tight, redo);
       if (!redo) break;
       allow_tight = false;
       __syncthreads();
