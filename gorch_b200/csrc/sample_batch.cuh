@@ -33,18 +33,19 @@ namespace gs {
 
 constexpr int N_NT = 256;               // narrow kernel threads
 constexpr int N_NW = N_NT / 32;
-constexpr int N_CAP = 3072;             // candidate capacity (entries of 8 B)
-constexpr int N_KEEP = 1536;            // a prune must get below this
+constexpr int N_CAP = 2048;             // candidate capacity (entries of 8 B)
+constexpr int N_KEEP = 1024;            // a prune must get below this
 constexpr int N_WARM_ELEMS = 4096;      // logits of the warm-up chunk
 constexpr int N_HITS = 2048;            // hit list: positions of lane-steps that hold a candidate (4 B each)
-constexpr int N_DYN_BYTES = 16384 + N_CAP * 8 + N_HITS * 4;
-#ifndef GS_N_NQ_BF16
-#define GS_N_NQ_BF16 2
-#endif
-#ifndef GS_N_NQ_F32
-#define GS_N_NQ_F32 2
-#endif
-constexpr int N_NQ_BF16 = GS_N_NQ_BF16, N_NQ_F32 = GS_N_NQ_F32;   // register loads in flight per lane, in steps
+// Dynamic shared memory of the narrow kernel, 48 KB: [0, 24 KB) the ring the stream is staged
+// through; its upper 16 KB double as the work arrays of the phases that run while no copy is in
+// flight (prune, finish); then the candidate list and the hit list.
+constexpr int N_RING_BYTES = 24576;
+constexpr int N_WORK_OFF = 8192;
+constexpr int N_CAND_OFF = N_RING_BYTES;
+constexpr int N_HITS_OFF = N_CAND_OFF + N_CAP * 8;
+constexpr int N_DYN_BYTES = N_HITS_OFF + N_HITS * 4;
+static_assert(N_WORK_OFF + 16384 <= N_CAND_OFF, "work arrays end where the candidate list starts");
 
 
 // Vocab-sharded sampling: what one rank knows about one row of its column slice. cand holds every
@@ -233,6 +234,8 @@ __device__ void finish_small_set(const KernelArgs& A, int64_t row_id, const uint
   write_row(id, flags);
 }
 
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
 template <typename T>
 __device__ __forceinline__ uint4 mask_edges(const RowView<T>& rv, int v, uint4 raw);
 
@@ -252,9 +255,9 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   const T* row = static_cast<const T*>(A.logits) + row_id * A.row_stride;
   RowView<T> rv;
   rv.init(row, V);
-  uint4* chunk = reinterpret_cast<uint4*>(dyn);              // warm-up vectors, 16 KB; later work arrays
-  uint2* cand = reinterpret_cast<uint2*>(dyn + 16384);       // N_CAP entries
-  int* hits = reinterpret_cast<int*>(dyn + 16384 + N_CAP * 8);   // N_HITS entries
+  unsigned char* work = dyn + N_WORK_OFF;                    // 16 KB of work arrays (prune, finish)
+  uint2* cand = reinterpret_cast<uint2*>(dyn + N_CAND_OFF);  // N_CAP entries
+  int* hits = reinterpret_cast<int*>(dyn + N_HITS_OFF);      // N_HITS entries
   const double QNAN = __longlong_as_double(0x7ff8000000000000ll);
 
   RowCfg cfg;
@@ -340,32 +343,50 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   const double plim = (mode == 0) ? static_cast<double>(cfg.top_p) * 1.5 : static_cast<double>(cfg.top_p);
   dbg.path = 1;
 
-  // ---- warm-up chunk: park it, one running maximum per thread
+  // ---- warm-up chunk: 16 logits per thread, kept in registers; one running maximum per thread
   float xmax = -INFINITY, xmin = INFINITY;
   bool nan_seen = false;
   if (tid == 0) { *s_cnt = 0; *s_hcnt = 0; *s_flag = 0; }
   const int warm = min(rv.nvec, WARM_VECS);
-  {
-    constexpr int G = WARM_VECS / N_NT;
-    uint4 r[G];
+  constexpr int G = WARM_VECS / N_NT;
+  uint4 wr[G];                                               // logits outside the row come back as -Inf
+  constexpr uint32_t NEG_INF_BITS = (sizeof(T) == 4) ? 0xff800000u : 0xff80ff80u;
 #pragma unroll
-    for (int g = 0; g < G; g++) {
-      const int v = g * N_NT + tid;
-      if (v < warm) { r[g] = load_masked(rv, v, xmax, xmin, nan_seen); chunk[v] = r[g]; }
-    }
+  for (int g = 0; g < G; g++) {
+    const int v = g * N_NT + tid;
+    wr[g] = make_uint4(NEG_INF_BITS, NEG_INF_BITS, NEG_INF_BITS, NEG_INF_BITS);
+    if (v < warm) wr[g] = load_masked(rv, v, xmax, xmin, nan_seen);
   }
-  // The stream's first loads go out now, so that they are in flight during the selection below.
-  constexpr int SV = 32 * (8 / VEC);
-  constexpr int NQ = (VEC == 8) ? N_NQ_BF16 : N_NQ_F32;      // steps in flight
+  // ---- the rest of the row is streamed by warps, every warp over its own span, eight logits per
+  // lane and step (two 16-byte vectors of f32, one of bf16). The vectors are staged through a ring
+  // in shared memory by asynchronous 16-byte copies: a thread copies what it will consume itself
+  // (no barrier: it only waits for its own copy groups), NQ steps ahead. Loads into registers
+  // cannot run that far ahead: in a rolled loop they share one scoreboard, so waiting for the
+  // oldest waits for the newest too. The first copies go out now and fly during the selection.
+  constexpr int EPI = 8 / VEC, SV = 32 * EPI;
+  constexpr int NQ = N_RING_BYTES / (EPI * N_NT * 16);       // stages: 6 of bf16, 3 of f32
   const int lane = tid & 31, warp = tid >> 5;
   const int rest = max(rv.nvec - warm, 0);
   const int span = (((rest + N_NW - 1) / N_NW + SV - 1) / SV) * SV;
   const WSpan sp = make_span<T>(rv, warm + warp * span, span, lane);
   unsigned long long pol;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-  uint4 qa[NQ], qb[NQ];
+  const uint32_t ring_addr = smem_addr(dyn) + static_cast<uint32_t>(tid * 16);
+  const uint4* ring = reinterpret_cast<const uint4*>(dyn) + tid;
+  // the copies of step q (none past the warp's last step: an empty group keeps the count right)
+  auto ring_issue = [&](int q) {
+    if (q < sp.nst) {
+      const uint32_t dst = ring_addr + static_cast<uint32_t>((q % NQ) * EPI * N_NT * 16);
+      const int o = q * SV;
 #pragma unroll
-  for (int q = 0; q < NQ; q++) w_load<T, N_PF>(sp, q, pol, qa[q], qb[q]);
+      for (int h = 0; h < EPI; h++)
+        asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;"
+                     :: "r"(dst + h * N_NT * 16), "l"(sp.lane_src + min(o + 32 * h, sp.omax)), "l"(pol) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+#pragma unroll
+  for (int q = 0; q < NQ; q++) ring_issue(q);
   // Threshold from the 256 per-thread maxima of the chunk, each thread counting how many of them
   // order before its own (one barrier; a radix select over so few keys costs several rounds of
   // barriers and of shared atomics that all hit the same few bins).
@@ -412,17 +433,17 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     thr = *s_thr;
     if (thr == LOWEST) tight = false;
   }
-  // candidates of the warm-up chunk
-  for (int v = tid; v < warm; v += N_NT) {
+  // candidates of the warm-up chunk (a logit outside the row is -Inf there: below every threshold)
+#pragma unroll
+  for (int g = 0; g < G; g++) {
     float x[VEC];
-    Elem<T>::unpack(chunk[v], x);
-    const int i0 = v * VEC - rv.shift;
+    Elem<T>::unpack(wr[g], x);
+    const int i0 = (g * N_NT + tid) * VEC - rv.shift;
 #pragma unroll
     for (int c = 0; c < VEC; c++) {
-      const int i = i0 + c;
-      if (x[c] >= thr && i >= 0 && i < V) {
+      if (x[c] >= thr) {
         const int slot = atomicAdd(s_cnt, 1);
-        if (slot < N_CAP) cand[slot] = make_uint2(__float_as_uint(x[c]), static_cast<uint32_t>(i));
+        if (slot < N_CAP) cand[slot] = make_uint2(__float_as_uint(x[c]), static_cast<uint32_t>(i0 + c));
       }
     }
   }
@@ -435,7 +456,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     if (tid == 0) { *s_thr = quotient_class_floor(okey_to_float(kkey), Tm); *s_cnt = 0; }
     __syncthreads();
     thr = *s_thr;                                            // finite: the list holds finite logits only
-    uint2* tmp = reinterpret_cast<uint2*>(chunk);            // 2048 entries
+    uint2* tmp = reinterpret_cast<uint2*>(work);             // 2048 entries
     for (int j = tid; j < cnt; j += N_NT) {
       const uint2 e = cand[j];
       if (__uint_as_float(e.x) >= thr) { const int slot = atomicAdd(s_cnt, 1); if (slot < 2048) tmp[slot] = e; }
@@ -446,18 +467,16 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     __syncthreads();
     return kept;
   };
-  // ---- stream the rest of the row: every warp walks its own span of it, eight logits per lane
-  // and step (two 16-byte vectors of f32, one of bf16), loaded NQ steps ahead in registers. No
-  // barrier per step. A lane whose eight logits hold one at or above the threshold only notes WHERE
-  // (its vector index, 4 bytes in the hit list): unpacking and appending on the spot would cost
-  // the whole warp some hundred instructions on nearly every other step. The noted vectors are read
-  // again (from L2, or HBM at worst) by all threads at once after the stream, or when the hit
-  // list fills: a warp that sees it past H_TRIGGER raises *s_flag; every warp looks at the flag
-  // before each step and comes to the barrier below, where the hits are resolved into the
-  // candidate list and that is pruned to the exact k-th largest; then the warps walk on. Between
-  // the flag going up and a warp seeing it, each of its lanes notes at most one more hit: the
-  // room above H_TRIGGER. Steps that hold the row's edges (at most two per warp) append their
-  // logits directly, masked by index.
+  // ---- the stream. No barrier per step. A lane whose eight logits hold one at or above the
+  // threshold only notes WHERE (its vector index, 4 bytes in the hit list): unpacking and
+  // appending on the spot would cost the whole warp some hundred instructions on nearly every
+  // other step. The noted vectors are read again (from L2, or HBM at worst) by all threads at once
+  // after the stream, or when the hit list fills: a warp that sees it past H_TRIGGER raises
+  // *s_flag; every warp looks at the flag before each step and comes to the barrier below, where
+  // the hits are resolved into the candidate list and that is pruned to the exact k-th largest;
+  // then the warps walk on. Between the flag going up and a warp seeing it, each of its lanes
+  // notes at most one more hit: the room above H_TRIGGER. Steps that hold the row's edges (at
+  // most two per warp) append their logits directly, masked by index.
   constexpr int H_TRIGGER = N_HITS - N_NT;
   volatile int* vflag = s_flag;
   float run = xmax;                                          // NaN-propagating running maximum of this thread
@@ -486,10 +505,9 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   for (;;) {                                                 // uniform: one trip per prune, plus one
 #pragma unroll 1
     while (st < sp.nst && *vflag == 0) {
-      const uint4 ca = qa[0], cb = qb[0];
-#pragma unroll
-      for (int q = 0; q + 1 < NQ; q++) { qa[q] = qa[q + 1]; qb[q] = qb[q + 1]; }
-      w_load<T, N_PF>(sp, st + NQ, pol, qa[NQ - 1], qb[NQ - 1]);
+      asm volatile("cp.async.wait_group %0;" :: "n"(NQ - 1) : "memory");   // the copies of step st have landed
+      const uint4 ca = ring[(st % NQ) * EPI * N_NT];
+      const uint4 cb = (EPI == 2) ? ring[(st % NQ) * EPI * N_NT + N_NT] : ca;
       if (st < sp.clean_hi) {                                // no logit outside the row in this step
         const float hi8 = step_max_nan<T>(ca, cb);
         run = maxnan(run, hi8);
@@ -516,8 +534,10 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
           }
         }
       }
+      ring_issue(st + NQ);                                   // into the slot just read
       st++;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");     // the ring's memory is about to serve as work arrays
     const int more = __syncthreads_or((st < sp.nst) ? 1 : 0);
     const int full = __syncthreads_or(*vflag);               // every thread reads it before anyone can raise it again
     if (full || !more) {
@@ -529,14 +549,24 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
       // portion takes them all; a row whose threshold is far too low (a start well below the rest
       // of the row) notes a hit in every lane-step and needs a few.
       int done = 0;
+      bool careful = false;
       for (;;) {                                             // uniform
         const int c0 = *s_cnt;
         __syncthreads();
         if (c0 > N_CAP) { giveup = true; break; }            // entries were dropped
-        const int take = min(nh - done, (N_CAP - c0) / 8);
+        // first all at once, if they fit at one candidate per hit (nearly always so); taken back
+        // when the list overflowed, and then in portions that fit at eight per hit
+        const int take = min(nh - done, (N_CAP - c0) / (careful ? 8 : 1));
         resolve_hits(done, take);
-        done += take;
         __syncthreads();
+        if (!careful && *s_cnt > N_CAP) {
+          __syncthreads();
+          if (tid == 0) *s_cnt = c0;
+          careful = true;
+          __syncthreads();
+          continue;
+        }
+        done += take;
         if (done >= nh && !full) break;
         const int cnt = prune(*s_cnt);
         if (cnt > N_KEEP) { giveup = true; break; }          // ties at the threshold fill the buffer
@@ -545,6 +575,9 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
       if (giveup) break;
     }
     if (!more) break;
+    __syncthreads();                                         // the work arrays are done with: refill the ring
+#pragma unroll
+    for (int q = 0; q < NQ; q++) ring_issue(st + q);
   }
   nan_seen |= (run != run);
   xmax = run;
@@ -612,7 +645,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   }
   stamp(2);
   finish_small_set<N_NT>(A, row_id, cand, nk, m, Tm, topp_on, mode, plim, A.uniforms[row_id],
-                         reinterpret_cast<unsigned char*>(chunk), sc, s_bcd, dbg, 0u);
+                         work, sc, s_bcd, dbg, 0u);
 }
 
 template <typename T>
@@ -673,6 +706,5 @@ __device__ __forceinline__ uint4 mask_edges(const RowView<T>& rv, int v, uint4 r
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
 }  // namespace gs
