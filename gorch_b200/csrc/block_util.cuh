@@ -132,10 +132,11 @@ __device__ __forceinline__ void scan_excl_d2(double a, double b, double& ea, dou
   eb = __shfl_sync(FULL, sb - wb, w) + ib - b;
 }
 
-// k-th largest (with multiplicity) of the float bit patterns list[j].x, j < n, by
-// MSB-first radix select on order keys. hist: 256 uint32 of scratch; bc: 2 ints.
-template <int NTHREADS>
-__device__ uint32_t select_kth(const uint2* list, int n, int k, uint32_t* hist, int* bc, int tid) {
+// k-th largest (with multiplicity) of the order keys that the threads of the block enumerate:
+// for_each_key(f) calls f(key) for every key of the calling thread (the same keys on every call).
+// MSB-first radix select. hist: 256 uint32 of scratch; bc: 2 ints.
+template <int NTHREADS, typename F>
+__device__ __forceinline__ uint32_t select_kth_of(F&& for_each_key, int k, uint32_t* hist, int* bc, int tid) {
   uint32_t prefix = 0, mask = 0;
   int need = k;
   for (int round = 0; round < 4; round++) {
@@ -143,10 +144,9 @@ __device__ uint32_t select_kth(const uint2* list, int n, int k, uint32_t* hist, 
     __syncthreads();
     if (tid < 256) hist[tid] = 0;
     __syncthreads();
-    for (int j = tid; j < n; j += NTHREADS) {
-      const uint32_t key = okey(__uint_as_float(list[j].x));
+    for_each_key([&](uint32_t key) {
       if ((key & mask) == prefix) atomicAdd(&hist[(key >> sh) & 255u], 1u);
-    }
+    });
     __syncthreads();
     if (tid < 32) {
       int loc[8];
@@ -177,6 +177,14 @@ __device__ uint32_t select_kth(const uint2* list, int n, int k, uint32_t* hist, 
     need = bc[1];
   }
   return prefix;
+}
+
+// The same over the float bit patterns list[j].x, j < n.
+template <int NTHREADS>
+__device__ uint32_t select_kth(const uint2* list, int n, int k, uint32_t* hist, int* bc, int tid) {
+  return select_kth_of<NTHREADS>([&](auto&& f) {
+    for (int j = tid; j < n; j += NTHREADS) f(okey(__uint_as_float(list[j].x)));
+  }, k, hist, bc, tid);
 }
 
 // In-place inclusive scan of a shared array a[0..n), n <= PER * 32 * NWARPS, in index order.

@@ -33,11 +33,12 @@ namespace gs {
 
 constexpr int N_NT = 256;               // narrow kernel threads
 constexpr int N_NW = N_NT / 32;
-constexpr int N_CAP = 2048;             // candidate capacity (entries of 8 B)
-constexpr int N_KEEP = 1024;            // a prune must get below this
+constexpr int N_CTAS_PER_SM = 5;        // 5 x 256 threads of at most 48 registers; 5 x 45 KB of shared memory
+constexpr int N_CAP = 1536;             // candidate capacity (entries of 8 B)
+constexpr int N_KEEP = 768;             // a prune must get below this
 constexpr int N_WARM_ELEMS = 4096;      // logits of the warm-up chunk
-constexpr int N_HITS = 2048;            // hit list: positions of lane-steps that hold a candidate (4 B each)
-// Dynamic shared memory of the narrow kernel, 48 KB: [0, 24 KB) the ring the stream is staged
+constexpr int N_HITS = 1536;            // hit list: positions of lane-steps that hold a candidate (4 B each)
+// Dynamic shared memory of the narrow kernel, 42 KB: [0, 24 KB) the ring the stream is staged
 // through; its upper 16 KB double as the work arrays of the phases that run while no copy is in
 // flight (prune, finish); then the candidate list and the hit list.
 constexpr int N_RING_BYTES = 24576;
@@ -434,18 +435,40 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     if (thr == LOWEST) tight = false;
   }
   // candidates of the warm-up chunk (a logit outside the row is -Inf there: below every threshold)
+  auto warm_candidates = [&]() {
 #pragma unroll
-  for (int g = 0; g < G; g++) {
-    float x[VEC];
-    Elem<T>::unpack(wr[g], x);
-    const int i0 = (g * N_NT + tid) * VEC - rv.shift;
+    for (int g = 0; g < G; g++) {
+      float x[VEC];
+      Elem<T>::unpack(wr[g], x);
+      const int i0 = (g * N_NT + tid) * VEC - rv.shift;
 #pragma unroll
-    for (int c = 0; c < VEC; c++) {
-      if (x[c] >= thr) {
-        const int slot = atomicAdd(s_cnt, 1);
-        if (slot < N_CAP) cand[slot] = make_uint2(__float_as_uint(x[c]), static_cast<uint32_t>(i0 + c));
+      for (int c = 0; c < VEC; c++) {
+        if (x[c] >= thr) {
+          const int slot = atomicAdd(s_cnt, 1);
+          if (slot < N_CAP) cand[slot] = make_uint2(__float_as_uint(x[c]), static_cast<uint32_t>(i0 + c));
+        }
       }
     }
+  };
+  warm_candidates();
+  __syncthreads();
+  if (*s_cnt > N_CAP) {                                      // uniform
+    // A large top_k makes the bound from the maxima a weak one (the top_k-th largest of 256
+    // maxima is near the smallest of them), and more of the chunk passed it than the list holds.
+    // The exact top_k-th largest of the chunk is a bound too; more than top_k pass it only by ties.
+    const uint32_t kkey = bu::select_kth_of<N_NT>([&](auto&& f) {
+#pragma unroll
+      for (int g = 0; g < G; g++) {
+        float x[VEC];
+        Elem<T>::unpack(wr[g], x);
+#pragma unroll
+        for (int c = 0; c < VEC; c++) f(okey(x[c]));
+      }
+    }, topk, s_sel, s_bc, tid);
+    if (tid == 0) { *s_thr = fmaxf(quotient_class_floor(okey_to_float(kkey), Tm), LOWEST); *s_cnt = 0; }
+    __syncthreads();
+    thr = fmaxf(thr, *s_thr);
+    warm_candidates();                                       // a list that ties overflow again ends the row below
   }
   stamp(0);
   bool giveup = false;
@@ -649,7 +672,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
 }
 
 template <typename T>
-__global__ void __launch_bounds__(N_NT, 4) narrow_rows_kernel(BatchArgs BA) {
+__global__ void __launch_bounds__(N_NT, N_CTAS_PER_SM) narrow_rows_kernel(BatchArgs BA) {
   extern __shared__ __align__(16) unsigned char dyn[];
   __shared__ bu::Scratch sc;
   __shared__ uint32_t s_sel[256];
@@ -663,7 +686,11 @@ __global__ void __launch_bounds__(N_NT, 4) narrow_rows_kernel(BatchArgs BA) {
   for (;;) {
     __syncthreads();
     if (threadIdx.x == 0) {
-      // next row of this kernel's kind; rows for the single-CTA kernel are handed over here
+      // next row of this kernel's kind; rows for the single-CTA kernel are handed over here.
+      // (Drawing the ticket ahead - at the start of the current row, or when its stream has ended,
+      // with an L2 prefetch of the next row's start - was measured: the first binds the rows of a
+      // last, partial wave to CTAs before it is known which are free first and costs a third of
+      // the step; the second gains nothing.)
       int w;
       for (;;) {
         w = atomicAdd(&BA.hdr[2], 1);

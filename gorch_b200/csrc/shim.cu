@@ -270,7 +270,7 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
     ba.list_single = base + 15;
     ba.B = B;
     CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
-    const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
+    const unsigned gn = static_cast<unsigned>(B < gs::N_CTAS_PER_SM * c->sm_count ? B : gs::N_CTAS_PER_SM * c->sm_count);
     // at most one row per SM: a 1024-thread CTA finishes its row sooner than a 256-thread one, and no SM
     // would have held a second row anyway. Beyond that the 256-thread instance wins (measured), also
     // because a 1024-thread CTA takes the whole register file and keeps the narrow kernel off its SM
@@ -790,7 +790,7 @@ static int vocab_local_launch(Ctx* c, const void* logits, int dtype, int64_t B, 
   ba.hdr = base; ba.list_single = base + 15;
   ba.B = B;
   CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
-  const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
+  const unsigned gn = static_cast<unsigned>(B < gs::N_CTAS_PER_SM * c->sm_count ? B : gs::N_CTAS_PER_SM * c->sm_count);
   if (dtype == GORCH_CUDA_F32) gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
   else gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
   CUDA_TRY(cudaGetLastError(), errOut);
@@ -971,7 +971,7 @@ int gorch_cuda_topk_dev(GorchCudaCtxRef ctx, const void* x, int dtype, int64_t B
   ba.hdr = base; ba.list_single = base + 15;
   ba.B = B;
   CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
-  const unsigned gn = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
+  const unsigned gn = static_cast<unsigned>(B < gs::N_CTAS_PER_SM * c->sm_count ? B : gs::N_CTAS_PER_SM * c->sm_count);
   if (dtype == GORCH_CUDA_F32) gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
   else gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
   CUDA_TRY(cudaGetLastError(), errOut);
