@@ -134,13 +134,20 @@ __device__ __forceinline__ void scan_excl_d2(double a, double b, double& ea, dou
 
 // k-th largest (with multiplicity) of the order keys that the threads of the block enumerate:
 // for_each_key(f) calls f(key) for every key of the calling thread (the same keys on every call).
-// MSB-first radix select. hist: 256 uint32 of scratch; bc: 2 ints.
+// MSB-first radix select. Every key lies in [lo, hi] (0 and 0xffffffff when nothing is known): the
+// bits that lo and hi share are shared by all keys, so the first digit starts at the highest bit
+// in which they differ. Keys that are close together (logits above a threshold) then spread over
+// the bins of the first round instead of meeting in one or two, and need a round less.
+// hist: 256 uint32 of scratch; bc: 2 ints.
 template <int NTHREADS, typename F>
-__device__ __forceinline__ uint32_t select_kth_of(F&& for_each_key, int k, uint32_t* hist, int* bc, int tid) {
-  uint32_t prefix = 0, mask = 0;
+__device__ __forceinline__ uint32_t select_kth_of(F&& for_each_key, int k, uint32_t lo, uint32_t hi,
+                                                   uint32_t* hist, int* bc, int tid) {
+  if (lo == hi) return lo;
+  const int top = 31 - __clz(lo ^ hi);                        // highest differing bit
+  uint32_t mask = (top == 31) ? 0u : ~((2u << top) - 1u);
+  uint32_t prefix = hi & mask;
   int need = k;
-  for (int round = 0; round < 4; round++) {
-    const int sh = 24 - 8 * round;
+  for (int sh = max(top - 7, 0);; sh = max(sh - 8, 0)) {
     __syncthreads();
     if (tid < 256) hist[tid] = 0;
     __syncthreads();
@@ -172,19 +179,23 @@ __device__ __forceinline__ uint32_t select_kth_of(F&& for_each_key, int k, uint3
       }
     }
     __syncthreads();
-    prefix |= static_cast<uint32_t>(bc[0]) << sh;
+    // a digit that reaches above bit `top` (fewer than eight bits differ) or into the previous
+    // digit repeats bits that are fixed already: the same in every key that is still counted
+    prefix = (prefix & ~(255u << sh)) | (static_cast<uint32_t>(bc[0]) << sh);
     mask |= 255u << sh;
     need = bc[1];
+    if (sh == 0) break;
   }
   return prefix;
 }
 
 // The same over the float bit patterns list[j].x, j < n.
 template <int NTHREADS>
-__device__ uint32_t select_kth(const uint2* list, int n, int k, uint32_t* hist, int* bc, int tid) {
+__device__ uint32_t select_kth(const uint2* list, int n, int k, uint32_t* hist, int* bc, int tid,
+                               uint32_t lo = 0u, uint32_t hi = 0xffffffffu) {
   return select_kth_of<NTHREADS>([&](auto&& f) {
     for (int j = tid; j < n; j += NTHREADS) f(okey(__uint_as_float(list[j].x)));
-  }, k, hist, bc, tid);
+  }, k, lo, hi, hist, bc, tid);
 }
 
 // In-place inclusive scan of a shared array a[0..n), n <= PER * 32 * NWARPS, in index order.

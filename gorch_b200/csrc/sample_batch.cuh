@@ -388,9 +388,11 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   };
 #pragma unroll
   for (int q = 0; q < NQ; q++) ring_issue(q);
-  // Threshold from the 256 per-thread maxima of the chunk, each thread counting how many of them
-  // order before its own (one barrier; a radix select over so few keys costs several rounds of
-  // barriers and of shared atomics that all hit the same few bins).
+  // Threshold from the 256 per-thread maxima of the chunk: every warp sorts its 32 maxima with
+  // shuffles, and every thread then finds the place of its own among all 256 by a binary search
+  // in each of the other warps' sorted lists (two barriers; a radix select over so few keys costs
+  // several rounds of barriers and of shared atomics that all hit the same few bins, and counting
+  // all 256 against each other three times the instructions).
   //  * The top_k-th largest maximum is a BOUND: top_k threads each hold a logit at or above it, so
   //    the top_k-th largest logit of the row is at or above it.
   //  * The r-th largest maximum with r < top_k, r chosen so that about four times top_k logits of
@@ -414,22 +416,38 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
       const int r = static_cast<int>((4ll * topk * welems + V - 1) / V) + 4;
       if (r < topk) { rank = r; tight = true; }
     }
-    const uint32_t mykey = okey(xmax);
-    s_sel[tid] = mykey;
+    uint32_t key = okey(xmax);
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {                      // bitonic network, descending by lane
+#pragma unroll
+      for (int j = k >> 1; j > 0; j >>= 1) {
+        const uint32_t other = __shfl_xor_sync(FULL, key, j);
+        const bool take_max = ((lane & j) == 0) == ((lane & k) == 0);
+        key = take_max ? max(key, other) : min(key, other);
+      }
+    }
+    s_sel[tid] = key;                                        // list of warp w: s_sel[32 w .. 32 w + 31]
     if (tid == 0) *s_thr = LOWEST;
     __syncthreads();
-    int before = 0;                                          // maxima that order before mine: larger, or equal at a lower thread
-    const uint4* k4 = reinterpret_cast<const uint4*>(s_sel);
-#pragma unroll 4
-    for (int j = 0; j < N_NT / 4; j++) {
-      const uint4 kk = k4[j];
-      before += (kk.x > mykey || (kk.x == mykey && 4 * j + 0 < tid)) ? 1 : 0;
-      before += (kk.y > mykey || (kk.y == mykey && 4 * j + 1 < tid)) ? 1 : 0;
-      before += (kk.z > mykey || (kk.z == mykey && 4 * j + 2 < tid)) ? 1 : 0;
-      before += (kk.w > mykey || (kk.w == mykey && 4 * j + 3 < tid)) ? 1 : 0;
+    // place of (key, warp, lane) in the order "larger key first, then lower warp, then lower lane"
+    int before = lane;
+#pragma unroll
+    for (int w = 0; w < N_NW; w++) {
+      if (w == warp) continue;
+      const uint32_t* L = s_sel + 32 * w;
+      const bool ties_first = w < warp;                      // equal keys of a lower warp order before mine
+      int c = 0;
+#pragma unroll
+      for (int step = 16; step >= 1; step >>= 1) {
+        const uint32_t v = L[c + step - 1];
+        if (v > key || (ties_first && v == key)) c += step;
+      }
+      const uint32_t v = L[c];
+      if (v > key || (ties_first && v == key)) c++;
+      before += c;
     }
-    if (before == rank - 1 && mykey > 0x007fffffu)           // at or below -Inf: keep everything
-      *s_thr = fmaxf(quotient_class_floor(xmax, Tm), LOWEST);
+    if (before == rank - 1 && key > 0x007fffffu)             // at or below -Inf: keep everything
+      *s_thr = fmaxf(quotient_class_floor(okey_to_float(key), Tm), LOWEST);
     __syncthreads();
     thr = *s_thr;
     if (thr == LOWEST) tight = false;
@@ -464,7 +482,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
 #pragma unroll
         for (int c = 0; c < VEC; c++) f(okey(x[c]));
       }
-    }, topk, s_sel, s_bc, tid);
+    }, topk, 0u, 0xffffffffu, s_sel, s_bc, tid);
     if (tid == 0) { *s_thr = fmaxf(quotient_class_floor(okey_to_float(kkey), Tm), LOWEST); *s_cnt = 0; }
     __syncthreads();
     thr = fmaxf(thr, *s_thr);
@@ -473,9 +491,10 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   stamp(0);
   bool giveup = false;
   // exact k-th largest of the list -> threshold; keepers move through the chunk buffer
-  auto prune = [&](int cnt) -> int {
+  // (every entry is at or above thr; hi_key: a key no entry exceeds)
+  auto prune = [&](int cnt, uint32_t hi_key) -> int {
     if (cnt <= topk) return cnt;
-    const uint32_t kkey = bu::select_kth<N_NT>(cand, cnt, topk, s_sel, s_bc, tid);
+    const uint32_t kkey = bu::select_kth<N_NT>(cand, cnt, topk, s_sel, s_bc, tid, okey(thr), hi_key);
     if (tid == 0) { *s_thr = quotient_class_floor(okey_to_float(kkey), Tm); *s_cnt = 0; }
     __syncthreads();
     thr = *s_thr;                                            // finite: the list holds finite logits only
@@ -591,7 +610,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
         }
         done += take;
         if (done >= nh && !full) break;
-        const int cnt = prune(*s_cnt);
+        const int cnt = prune(*s_cnt, 0xffffffffu);
         if (cnt > N_KEEP) { giveup = true; break; }          // ties at the threshold fill the buffer
         if (done >= nh) break;
       }
@@ -612,12 +631,13 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     if (A.vs_records || A.tk_k > 0) { redo = true; return; } // uniform: *s_cnt is read after the loop's last barrier
     giveup = true;
   }
-  if (!giveup) {
-    nk = prune(*s_cnt);
-    if (nk > KEEP_MAX) giveup = true;                        // long run of ties at the threshold
-  }
   const int anynan = bu::max_i<N_NW>(nan_seen ? 1 : 0, sc, tid);
   xmax = okey_to_float(static_cast<uint32_t>(bu::max_u64<N_NW>(static_cast<unsigned long long>(okey(xmax)), sc, tid)));
+  if (!giveup) {
+    // the row's maximum bounds the list from above, unless a thread's maximum was lost to a NaN
+    nk = prune(*s_cnt, anynan ? 0xffffffffu : okey(xmax));
+    if (nk > KEEP_MAX) giveup = true;                        // long run of ties at the threshold
+  }
   const float m = scale_t(xmax, Tm);
   dbg.max_scaled = m;
   // A NaN anywhere, or an infinite maximum, makes the softmax sum NaN upstream
