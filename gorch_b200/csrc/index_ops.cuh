@@ -7,7 +7,11 @@
 //   falls into, and one warp rescans that step in index order. The running sum is formed in a
 //   different order than the reference's sequential loop: a row whose uniform lies within 1e-6 of
 //   an edge of the chosen interval is flagged FLAG_BOUNDARY.
-//   TopK (index_ops.go:153-190) is the narrow kernel of sample_batch.cuh with KernelArgs::tk_k set.
+//   TopK (index_ops.go:153-190) is the narrow kernel of sample_batch.cuh with KernelArgs::tk_k set
+//   for k <= 256 (one pass over the row), and topk_large_kernel below for 256 < k <= 16384: an
+//   exact radix select of the k-th largest value over the row (four passes, the row coming from L2
+//   after the first), a gather of everything above it plus the lowest-index ties, and a bitonic
+//   sort of the k results in shared memory.
 #pragma once
 
 #include "sample_batch.cuh"
@@ -158,6 +162,115 @@ __global__ void __launch_bounds__(MN_NT, 4) multinomial_rows_kernel(MultinomialA
       if (u - total <= 1e-6) fl |= FLAG_BOUNDARY;
     }
     if (tid == 0) { M.out_ids[row] = id; if (M.out_flags) M.out_flags[row] = fl; }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// TopK for 256 < k <= TKL_MAX_K. One CTA of 512 threads per row at a time.
+// Order: value descending, equal values by ascending index; NaNs last (the reference's comparator
+// leaves them unspecified), -0 and +0 equal. The values written are the row's own bits.
+// ---------------------------------------------------------------------------
+constexpr int TKL_NT = 512;
+constexpr int TKL_MAX_K = 16384;
+constexpr int TKL_DYN_BYTES = TKL_MAX_K * 8;               // the k results as 64-bit sort keys
+
+struct TopKLargeArgs {
+  const void* x;           // [B, row_stride]
+  int64_t row_stride;
+  int32_t V;
+  int32_t k;
+  float* out_values;       // [B, k]
+  int32_t* out_indices;    // [B, k]
+  uint32_t* out_flags;     // [B] or null
+  int64_t B;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(TKL_NT, 1) topk_large_kernel(TopKLargeArgs A) {
+  extern __shared__ __align__(16) unsigned char dyn[];
+  __shared__ bu::Scratch sc;
+  __shared__ uint32_t hist[256];
+  __shared__ int bc[4];
+  __shared__ int s_cnt;
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(dyn);
+  const int tid = threadIdx.x;
+  const int V = A.V, k = A.k;
+  int P = 1;
+  while (P < k) P <<= 1;                                     // sort size
+  for (int64_t row = blockIdx.x; row < A.B; row += gridDim.x) {
+    const T* xr = static_cast<const T*>(A.x) + row * A.row_stride;
+    RowView<T> rv;
+    rv.init(xr, V);
+    // smallest and largest order key of the row: the select starts at the highest bit in which they
+    // differ, so that the keys spread over its bins (the top byte of a float is the same for nearly
+    // all logits of a row, and 150,000 shared atomics on one counter would take a millisecond)
+    uint32_t kmin = 0xffffffffu, kmax = 0u;
+    for (int v = tid; v < rv.nvec; v += TKL_NT)
+      rv.visit(v, [&](float x, int) { const uint32_t key = okey(x); kmin = min(kmin, key); kmax = max(kmax, key); });
+    kmax = static_cast<uint32_t>(bu::max_u64<TKL_NT / 32>(kmax, sc, tid));
+    kmin = ~static_cast<uint32_t>(bu::max_u64<TKL_NT / 32>(~kmin, sc, tid));
+    // the k-th largest value (as an order key) ...
+    const uint32_t kkey = bu::select_kth_of<TKL_NT>([&](auto&& f) {
+      for (int v = tid; v < rv.nvec; v += TKL_NT) rv.visit(v, [&](float x, int) { f(okey(x)); });
+    }, k, kmin, kmax, hist, bc, tid);
+    // ... how many logits lie above it, and how many equal it
+    int above = 0, ties = 0;
+    for (int v = tid; v < rv.nvec; v += TKL_NT)
+      rv.visit(v, [&](float x, int) { const uint32_t key = okey(x); above += (key > kkey) ? 1 : 0; ties += (key == kkey) ? 1 : 0; });
+    above = bu::sum_i<TKL_NT / 32>(above, sc, tid);
+    ties = bu::sum_i<TKL_NT / 32>(ties, sc, tid);
+    const int need = k - above;                              // 1 <= need <= ties
+    // among equals the lowest indices win: the need-th smallest index of them, when not all are wanted
+    uint32_t last_index = 0xffffffffu;
+    if (need < ties) {                                       // uniform
+      const uint32_t inv = bu::select_kth_of<TKL_NT>([&](auto&& f) {
+        for (int v = tid; v < rv.nvec; v += TKL_NT)
+          rv.visit(v, [&](float x, int i) { if (okey(x) == kkey) f(~static_cast<uint32_t>(i)); });
+      }, need, ~static_cast<uint32_t>(V - 1), 0xffffffffu, hist, bc, tid);
+      last_index = ~inv;
+    }
+    __syncthreads();
+    if (tid == 0) s_cnt = 0;
+    for (int j = tid; j < P; j += TKL_NT) keys[j] = 0ull;    // padding sorts last
+    __syncthreads();
+    for (int v = tid; v < rv.nvec; v += TKL_NT) {
+      rv.visit(v, [&](float x, int i) {
+        const uint32_t key = okey(x);
+        if (key > kkey || (key == kkey && static_cast<uint32_t>(i) <= last_index)) {
+          const int slot = atomicAdd(&s_cnt, 1);
+          if (slot < k) keys[slot] = (static_cast<unsigned long long>(key) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(i));
+        }
+      });
+    }
+    __syncthreads();
+    const bool ok = (s_cnt == k);                            // an invariant of the two selects
+    // bitonic sort, descending (a larger key first: larger value, then lower index)
+    for (int size = 2; size <= P; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        for (int t = tid; t < (P >> 1); t += TKL_NT) {
+          const int lo = 2 * t - (t & (stride - 1));
+          const int hi = lo + stride;
+          const bool desc = ((lo & size) == 0);
+          const unsigned long long a = keys[lo], b = keys[hi];
+          if ((a < b) == desc) { keys[lo] = b; keys[hi] = a; }
+        }
+        __syncthreads();
+      }
+    }
+    float* ov = A.out_values + row * static_cast<int64_t>(k);
+    int32_t* oi = A.out_indices + row * static_cast<int64_t>(k);
+    for (int j = tid; j < k; j += TKL_NT) {
+      if (ok) {
+        const int i = static_cast<int>(~static_cast<uint32_t>(keys[j] & 0xffffffffull));
+        float xv = 0.f;
+        rv.visit(rv.vec_of(i), [&](float x, int ii) { if (ii == i) xv = x; });
+        ov[j] = xv; oi[j] = i;
+      } else {
+        ov[j] = __int_as_float(0x7fc00000); oi[j] = -1;
+      }
+    }
+    if (tid == 0 && A.out_flags) A.out_flags[row] = ok ? 0u : FLAG_INTERNAL;
+    __syncthreads();
   }
 }
 

@@ -589,6 +589,8 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   if ((e = cudaFuncSetAttribute(gs::narrow_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::narrow_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::multinomial_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::MN_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::topk_large_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::TKL_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::topk_large_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::TKL_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::vocab_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::VM_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::w256::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w256::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::w1024::wide_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::w1024::W_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
@@ -949,13 +951,24 @@ int gorch_cuda_topk_dev(GorchCudaCtxRef ctx, const void* x, int dtype, int64_t B
     set_err(errOut, "gorch_cuda: TopK k=%lld out of range [1, %lld]", (long long)k, (long long)V);
     return GORCH_CUDA_ERR_BAD_ARG;
   }
-  if (k > gs::KFAST) {
-    set_err(errOut, "gorch_cuda: TopK supports k <= %d, got %lld", gs::KFAST, (long long)k);
+  if (k > gs::TKL_MAX_K) {
+    set_err(errOut, "gorch_cuda: TopK supports k <= %d, got %lld", gs::TKL_MAX_K, (long long)k);
     return GORCH_CUDA_ERR_LIMIT;
   }
   if (B == 0) return GORCH_CUDA_OK;
   if (!x || !out_values || !out_indices) { set_err(errOut, "gorch_cuda: null pointer argument"); return GORCH_CUDA_ERR_BAD_ARG; }
   CUDA_TRY(cudaSetDevice(c->device), errOut);
+  if (k > gs::KFAST) {                                       // beyond the one-pass kernel's lists: select, gather, sort
+    gs::TopKLargeArgs ta;
+    ta.x = x; ta.row_stride = row_stride; ta.V = static_cast<int32_t>(V); ta.k = static_cast<int32_t>(k);
+    ta.out_values = out_values; ta.out_indices = out_indices; ta.out_flags = out_flags; ta.B = B;
+    const unsigned g = static_cast<unsigned>(B < c->sm_count ? B : c->sm_count);
+    if (dtype == GORCH_CUDA_F32) gs::topk_large_kernel<float><<<g, gs::TKL_NT, gs::TKL_DYN_BYTES, c->stream>>>(ta);
+    else gs::topk_large_kernel<uint16_t><<<g, gs::TKL_NT, gs::TKL_DYN_BYTES, c->stream>>>(ta);
+    CUDA_TRY(cudaGetLastError(), errOut);
+    c->counters.kernel_launches += 1;
+    return GORCH_CUDA_OK;
+  }
   const size_t ints = 16 + static_cast<size_t>(B) + 1;
   rc = ensure(c->worklist, ints * sizeof(int32_t), errOut);
   if (rc) return rc;

@@ -222,10 +222,11 @@ int gorch_cuda_sample_vocab_sharded_dev(GorchCudaCtxRef ctx, const void* logits_
  * the context's stream).
  * TopK (index_ops.go:153-190): the k largest of each row of x [B,V] (f32, or bf16 upcast), values
  * [B,k] descending and their indices [B,k]; equal values by ascending index (upstream's sort is
- * unstable, so that order is unspecified there); NaNs order last. 1 <= k <= min(V, 256). A row with
- * more than 512 logits tied at its k-th value (which includes a row with fewer than k logits above
- * -Inf) gets indices -1 and GORCH_FLAG_INTERNAL in out_flags
- * (may be NULL).
+ * unstable, so that order is unspecified there); NaNs order last. 1 <= k <= min(V, 16384), else
+ * GORCH_CUDA_ERR_LIMIT. k <= 256 is served in one pass over the row; there a row with more than 512
+ * logits tied at its k-th value (which includes a row with fewer than k logits above -Inf) gets
+ * indices -1 and GORCH_FLAG_INTERNAL in out_flags (may be NULL). k > 256 takes a radix select over
+ * the row (several passes, the row coming from L2 after the first) and has no such limit on ties.
  * Multinomial (index_ops.go:203-227): out_ids[b] = first j with uniforms[b] < sum_{i<=j} probs[b,i]
  * (f64 running sum over f32 probabilities), else V-1 (GORCH_FLAG_FALLBACK). The sum is formed in a
  * different order than upstream's loop; rows whose uniform lies within 1e-6 of an edge of the

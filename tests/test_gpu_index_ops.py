@@ -43,6 +43,33 @@ def test_topk_matches_oracle(sampler, oracle, B, V, k):
     assert np.array_equal(idx.astype(np.int64), wi)    # ascending index among equals, as the oracle
 
 
+@pytest.mark.parametrize("B,V,k", [(3, 300, 257), (2, 300, 300), (5, 5000, 1000), (6, 50257, 4096), (150, 151936, 300),
+                                   (3, 151936, 16384), (4, 20000, 5000)])
+def test_topk_large_k_matches_oracle(_sampler_session, oracle, B, V, k):
+    """k beyond the one-pass kernel's lists: radix select of the k-th largest, gather, sort. Ties across
+    the k-th value (lowest indices win), a row of one value only, -Inf and NaN entries (ordered last)."""
+    s = _sampler_session
+    rng = np.random.Generator(np.random.Philox(key=B * 1000003 + V * 17 + k))
+    x = (rng.standard_normal((B, V)) * 2.0).astype(np.float32)
+    x[:, ::3] = np.round(x[:, ::3] * 2) / 2            # heavy ties, also across the k-th value
+    x[0, :] = 1.25                                     # every logit equal: the first k indices
+    if B > 1:
+        x[1, 5::7] = -np.inf
+    vals, idx = s.topk(x, k)
+    wv, wi = oracle.topk(x, k)
+    assert np.array_equal(vals, wv)
+    assert np.array_equal(idx.astype(np.int64), wi)
+    bits = oracle.f32_to_bf16_bits(x)
+    vals, idx = s.topk(bits, k)
+    wv, wi = oracle.topk(oracle.bf16_bits_to_f32(bits), k)
+    assert np.array_equal(vals, wv) and np.array_equal(idx.astype(np.int64), wi)
+
+
+def test_topk_k_limit(_sampler_session):
+    with pytest.raises(GorchCudaError, match="k <= 16384"):
+        _sampler_session.topk(np.zeros((2, 20000), dtype=np.float32), 16385)
+
+
 def test_topk_bf16_rows(sampler, oracle):
     w = workloads.vocab_sharded(8)
     vals, idx = sampler.topk(w.logits, 64)
