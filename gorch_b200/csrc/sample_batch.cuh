@@ -545,6 +545,40 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   };
   __syncthreads();
   for (;;) {                                                 // uniform: one trip per prune, plus one
+    {
+      // The steady part: steps whose own vectors and whose refill (step st + NQ) are clean, so
+      // that no address needs a clamp and no logit a mask. The ring slot, the global source and
+      // the vector index advance by additions (the general loop below pays a division by NQ, two
+      // multiplications and two clamps per step, about as many instructions as the step's work).
+      constexpr uint32_t STAGE = EPI * N_NT * 16;
+      const int steady_end = sp.clean_hi - NQ;
+      uint32_t slot_off = static_cast<uint32_t>(st % NQ) * STAGE;
+      const uint4* gsrc = sp.lane_src + static_cast<int64_t>(st + NQ) * SV;
+      int gv = sp.first + st * SV + lane;
+#pragma unroll 1
+      while (st < steady_end && *vflag == 0) {
+        asm volatile("cp.async.wait_group %0;" :: "n"(NQ - 1) : "memory");   // the copies of step st have landed
+        const uint4* rd = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(ring) + slot_off);
+        const uint4 ca = rd[0];
+        const uint4 cb = (EPI == 2) ? rd[N_NT] : ca;
+        const float hi8 = step_max_nan<T>(ca, cb);
+        run = maxnan(run, hi8);
+        if (hi8 >= thr) {
+          const int slot = atomicAdd(s_hcnt, 1);
+          hits[min(slot, N_HITS - 1)] = gv;
+          if (slot >= H_TRIGGER) *vflag = 1;
+        }
+#pragma unroll
+        for (int h = 0; h < EPI; h++)
+          asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;"
+                       :: "r"(ring_addr + slot_off + h * N_NT * 16), "l"(gsrc + 32 * h), "l"(pol) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        slot_off = (slot_off + STAGE == NQ * STAGE) ? 0u : slot_off + STAGE;
+        gsrc += SV;
+        gv += SV;
+        st++;
+      }
+    }
 #pragma unroll 1
     while (st < sp.nst && *vflag == 0) {
       asm volatile("cp.async.wait_group %0;" :: "n"(NQ - 1) : "memory");   // the copies of step st have landed
