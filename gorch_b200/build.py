@@ -14,7 +14,7 @@ NVCC_FLAGS = [
 ]
 
 SOURCES = ["shim.cu"]
-HEADERS = ["sample_common.cuh", "sample_kernel.cuh", "sample_cluster.cuh", "sample_batch.cuh", "sample_wide.cuh", "row_stream.cuh",
+HEADERS = ["sample_common.cuh", "sample_kernel.cuh", "sample_cluster.cuh", "sample_batch.cuh", "sample_narrow.cuh", "sample_wide.cuh", "row_stream.cuh",
            "sample_vocab.cuh", "index_ops.cuh", "generate_control.cuh", "row_softmax.cuh", "lm_head.cuh", "block_util.cuh", "../../include/gorch_cuda_shim.h"]
 
 

@@ -149,7 +149,7 @@ __device__ __forceinline__ uint32_t select_kth_of(F&& for_each_key, int k, uint3
   int need = k;
   for (int sh = max(top - 7, 0);; sh = max(sh - 8, 0)) {
     __syncthreads();
-    if (tid < 256) hist[tid] = 0;
+    for (int j = tid; j < 256; j += NTHREADS) hist[j] = 0;
     __syncthreads();
     for_each_key([&](uint32_t key) {
       if ((key & mask) == prefix) atomicAdd(&hist[(key >> sh) & 255u], 1u);

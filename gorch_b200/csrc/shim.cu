@@ -80,7 +80,8 @@ struct Ctx {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int timing = 0;
   int variant = 0;        // 0: by batch size, 1: single-CTA kernel, 2: narrow/wide kernels, 3: cluster kernel,
-                          // 4 / 5: as 2 with the wide kernel's 256- / 1024-thread instance forced
+                          // 4 / 5: as 2 with the wide kernel's 256- / 1024-thread instance forced,
+                          // 6 / 7: as 2 with the narrow kernel's 128- / 256-thread instance forced
   int force_cluster = 0;  // 0: choose from the shape
   GorchCudaCounters counters{};
 };
@@ -216,6 +217,24 @@ int check_shape(int dtype, int64_t B, int64_t V, int64_t row_stride, char** errO
 
 size_t elem_size(int dtype) { return dtype == GORCH_CUDA_BF16 ? 2 : 4; }
 
+// The narrow kernel's two instances: 256-thread CTAs (five per SM) while every row gets a CTA slot
+// of its own, 128-thread CTAs (eight per SM) beyond that. Variants 6 / 7 force one of them (tests).
+static cudaError_t launch_narrow(Ctx* c, const gs::BatchArgs& ba, int dtype, int64_t B) {
+  const int64_t slots256 = static_cast<int64_t>(gs::n256::N_CTAS_PER_SM) * c->sm_count;
+  const bool small_ctas = c->variant == 6 || (c->variant != 7 && B > slots256);
+  if (small_ctas) {
+    const int64_t slots = static_cast<int64_t>(gs::n128::N_CTAS_PER_SM) * c->sm_count;
+    const unsigned g = static_cast<unsigned>(B < slots ? B : slots);
+    if (dtype == GORCH_CUDA_F32) gs::n128::narrow_rows_kernel<float><<<g, gs::n128::N_NT, gs::n128::N_DYN_BYTES, c->stream>>>(ba);
+    else gs::n128::narrow_rows_kernel<uint16_t><<<g, gs::n128::N_NT, gs::n128::N_DYN_BYTES, c->stream>>>(ba);
+  } else {
+    const unsigned g = static_cast<unsigned>(B < slots256 ? B : slots256);
+    if (dtype == GORCH_CUDA_F32) gs::n256::narrow_rows_kernel<float><<<g, gs::n256::N_NT, gs::n256::N_DYN_BYTES, c->stream>>>(ba);
+    else gs::n256::narrow_rows_kernel<uint16_t><<<g, gs::n256::N_NT, gs::n256::N_DYN_BYTES, c->stream>>>(ba);
+  }
+  return cudaGetLastError();
+}
+
 int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int64_t row_stride,
                 const GorchSampleCfg* cfgs, const double* uniforms, int32_t* out_ids,
                 uint32_t* out_flags, double* out_probs, GorchSampleDebug* out_debug,
@@ -270,7 +289,6 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
     ba.list_single = base + 15;
     ba.B = B;
     CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
-    const unsigned gn = static_cast<unsigned>(B < gs::N_CTAS_PER_SM * c->sm_count ? B : gs::N_CTAS_PER_SM * c->sm_count);
     // at most one row per SM: a 1024-thread CTA finishes its row sooner than a 256-thread one, and no SM
     // would have held a second row anyway. Beyond that the 256-thread instance wins (measured), also
     // because a 1024-thread CTA takes the whole register file and keeps the narrow kernel off its SM
@@ -294,8 +312,7 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
         else gs::w256::wide_rows_kernel<uint16_t><<<gw, gs::w256::W_NT, gs::w256::W_DYN_BYTES, c->side_stream>>>(ba);
       }
     }
-    if (dtype == GORCH_CUDA_F32) gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-    else gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
+    CUDA_TRY(launch_narrow(c, ba, dtype, B), errOut);
     if (!force_greedy) {
       CUDA_TRY(cudaEventRecord(c->ev_join, c->side_stream), errOut);
       CUDA_TRY(cudaStreamWaitEvent(c->stream, c->ev_join, 0), errOut);
@@ -586,8 +603,10 @@ GorchCudaCtxRef gorch_cuda_create_ctx(int device, char** errOut) {
   if ((e = cudaFuncSetAttribute(gs::sample_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::POOL_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::sample_cluster_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 109 * 1024)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::sample_cluster_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 109 * 1024)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
-  if ((e = cudaFuncSetAttribute(gs::narrow_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
-  if ((e = cudaFuncSetAttribute(gs::narrow_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::n256::narrow_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::n256::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::n256::narrow_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::n256::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::n128::narrow_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::n128::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
+  if ((e = cudaFuncSetAttribute(gs::n128::narrow_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::n128::N_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::multinomial_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::MN_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::topk_large_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::TKL_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
   if ((e = cudaFuncSetAttribute(gs::topk_large_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, gs::TKL_DYN_BYTES)) != cudaSuccess) return fail("cudaFuncSetAttribute", e);
@@ -655,9 +674,9 @@ int gorch_cuda_set_timing(GorchCudaCtxRef ctx, int on) {
 int gorch_cuda_set_kernel_variant(GorchCudaCtxRef ctx, int variant, int cluster_size, char** errOut) {
   Ctx* c = static_cast<Ctx*>(ctx);
   if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
-  if ((variant < 0 || variant > 5) ||
+  if ((variant < 0 || variant > 7) ||
       !(cluster_size == 0 || cluster_size == 1 || cluster_size == 2 || cluster_size == 4 || cluster_size == 8)) {
-    set_err(errOut, "gorch_cuda: variant must be 0..5, cluster_size 0, 1, 2, 4 or 8");
+    set_err(errOut, "gorch_cuda: variant must be 0..7, cluster_size 0, 1, 2, 4 or 8");
     return GORCH_CUDA_ERR_BAD_ARG;
   }
   c->variant = variant;
@@ -792,9 +811,7 @@ static int vocab_local_launch(Ctx* c, const void* logits, int dtype, int64_t B, 
   ba.hdr = base; ba.list_single = base + 15;
   ba.B = B;
   CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
-  const unsigned gn = static_cast<unsigned>(B < gs::N_CTAS_PER_SM * c->sm_count ? B : gs::N_CTAS_PER_SM * c->sm_count);
-  if (dtype == GORCH_CUDA_F32) gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-  else gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
+  CUDA_TRY(launch_narrow(c, ba, dtype, B), errOut);
   CUDA_TRY(cudaGetLastError(), errOut);
   c->counters.kernel_launches += 1;
   return GORCH_CUDA_OK;
@@ -984,9 +1001,7 @@ int gorch_cuda_topk_dev(GorchCudaCtxRef ctx, const void* x, int dtype, int64_t B
   ba.hdr = base; ba.list_single = base + 15;
   ba.B = B;
   CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
-  const unsigned gn = static_cast<unsigned>(B < gs::N_CTAS_PER_SM * c->sm_count ? B : gs::N_CTAS_PER_SM * c->sm_count);
-  if (dtype == GORCH_CUDA_F32) gs::narrow_rows_kernel<float><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
-  else gs::narrow_rows_kernel<uint16_t><<<gn, gs::N_NT, gs::N_DYN_BYTES, c->stream>>>(ba);
+  CUDA_TRY(launch_narrow(c, ba, dtype, B), errOut);
   CUDA_TRY(cudaGetLastError(), errOut);
   c->counters.kernel_launches += 1;
   return GORCH_CUDA_OK;

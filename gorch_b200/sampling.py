@@ -109,7 +109,9 @@ class CudaSampler:
         self._lib.gorch_cuda_set_timing(self._ctx, 1 if on else 0)
 
     def set_kernel_variant(self, variant: int = 0, cluster_size: int = 0) -> None:
-        """0: cluster kernel (default); 1: single-CTA kernel. cluster_size 0 = automatic."""
+        """Test hook: 0 dispatch by batch shape (default); 1 single-CTA kernel; 2 batch kernels; 3 cluster kernel;
+        4 / 5 batch kernels with the wide kernel's 256- / 1024-thread instance; 6 / 7 with the narrow
+        kernel's 128- / 256-thread instance. cluster_size 0 = automatic."""
         err = C.c_void_p()
         _check(self._lib, self._lib.gorch_cuda_set_kernel_variant(self._ctx, int(variant), int(cluster_size), C.byref(err)), err)
 

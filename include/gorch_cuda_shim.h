@@ -112,7 +112,9 @@ int gorch_cuda_get_counters(GorchCudaCtxRef ctx, GorchCudaCounters* out);
  * thread-block cluster per row with the row held in shared memory); 1: one CTA per row re-reading
  * global memory (an independent second implementation); 2: force the large-batch kernels; 3: force
  * the shared-memory cluster kernel; 4 / 5: as 2, with the wide kernel's 256-thread (four CTAs per
- * SM) / 1024-thread (one CTA per SM) instance forced instead of chosen by batch size. cluster_size
+ * SM) / 1024-thread (one CTA per SM) instance forced instead of chosen by batch size; 6 / 7: as 2,
+ * with the narrow kernel's 128-thread (eight CTAs per SM) / 256-thread (five CTAs per SM) instance
+ * forced. cluster_size
  * 0 picks the cluster size of variant 3 from the shape; 1, 2, 4, 8 force it. */
 int gorch_cuda_set_kernel_variant(GorchCudaCtxRef ctx, int variant, int cluster_size, char** errOut);
 

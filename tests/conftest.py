@@ -20,9 +20,10 @@ def oracle():
 
 
 # every GPU test runs against each kernel configuration: the default dispatch, the large-batch
-# kernels (wide kernel instance chosen by the batch, or forced), the shared-memory cluster kernel
+# kernels (wide and narrow kernel instances chosen by the batch, or forced), the shared-memory cluster kernel
 # with its automatic and forced sizes, and the single-CTA kernel
-VARIANTS = {"auto": (0, 0), "batch": (2, 0), "batch_w256": (4, 0), "batch_w1024": (5, 0), "cluster1": (3, 1), "cluster2": (3, 2), "cluster4": (3, 4),
+VARIANTS = {"auto": (0, 0), "batch": (2, 0), "batch_w256": (4, 0), "batch_w1024": (5, 0), "batch_n128": (6, 0), "batch_n256": (7, 0),
+            "cluster1": (3, 1), "cluster2": (3, 2), "cluster4": (3, 4),
             "cluster8": (3, 8), "single_cta": (1, 0)}
 
 

@@ -16,7 +16,7 @@ from tests.parity import compare
 
 pytestmark = pytest.mark.gpu
 
-DISPATCH = {"auto": (0, 0), "batch_w256": (4, 0), "batch_w1024": (5, 0)}
+DISPATCH = {"auto": (0, 0), "batch_w256": (4, 0), "batch_w1024": (5, 0), "batch_n128": (6, 0), "batch_n256": (7, 0)}
 
 _CACHE = {}
 
