@@ -17,10 +17,13 @@
 
 namespace gs {
 
-constexpr int VM_NT = 256;
+constexpr int VM_NT = 128;                                  // eight CTAs per SM: 1184 rows in flight
 constexpr int VM_MAX_RANKS = 16;
 constexpr int VM_LIST = VM_MAX_RANKS * VS_CAND;             // 2048 entries
-constexpr int VM_DYN_BYTES = VM_LIST * 8 + 16384 + KEEP_MAX * 8;
+constexpr int VM_DYN_BYTES = VM_LIST * 8 + 16384 + KEEP_MAX * 8;   // the most a launch asks for
+// dynamic shared memory of a launch: the joined list sized by its ranks and candidates
+__host__ __device__ constexpr int vm_list_entries(int nranks, int cand) { return ((nranks * cand + 15) / 16) * 16; }
+__host__ __device__ constexpr int vm_dyn_bytes(int nranks, int cand) { return vm_list_entries(nranks, cand) * 8 + 16384 + KEEP_MAX * 8; }
 
 struct MergeArgs {
   KernelArgs k;             // V = whole vocabulary; logits unused
@@ -30,7 +33,7 @@ struct MergeArgs {
   int64_t B;
 };
 
-__global__ void __launch_bounds__(VM_NT, 4) vocab_merge_kernel(MergeArgs M) {
+__global__ void __launch_bounds__(VM_NT, 8) vocab_merge_kernel(MergeArgs M) {
   extern __shared__ __align__(16) unsigned char dyn[];
   __shared__ bu::Scratch sc;
   __shared__ uint32_t s_sel[256];
@@ -38,8 +41,9 @@ __global__ void __launch_bounds__(VM_NT, 4) vocab_merge_kernel(MergeArgs M) {
   __shared__ double s_bcd[4];
   __shared__ int s_cnt;
   uint2* list = reinterpret_cast<uint2*>(dyn);                                   // joined candidates
-  unsigned char* work = dyn + VM_LIST * 8;                                        // 16 KB for finish_small_set
-  uint2* kept = reinterpret_cast<uint2*>(dyn + VM_LIST * 8 + 16384);             // KEEP_MAX entries
+  const int list_bytes = vm_list_entries(M.nranks, M.cand) * 8;
+  unsigned char* work = dyn + list_bytes;                                         // 16 KB for finish_small_set
+  uint2* kept = reinterpret_cast<uint2*>(dyn + list_bytes + 16384);              // KEEP_MAX entries
   const KernelArgs& A = M.k;
   const int tid = threadIdx.x;
   constexpr int NW = VM_NT / 32;
@@ -108,7 +112,7 @@ __global__ void __launch_bounds__(VM_NT, 4) vocab_merge_kernel(MergeArgs M) {
     const int topk = cfg.top_k;                              // 0 < top_k <= VS_CAND (checked by the local pass)
     float thr = -INFINITY;
     if (cnt > topk) {
-      const uint32_t kkey = bu::select_kth<VM_NT>(list, cnt, topk, s_sel, s_bc, tid);
+      const uint32_t kkey = bu::select_kth<VM_NT>(list, cnt, topk, s_sel, s_bc, tid, 0u, static_cast<uint32_t>(mx));
       thr = quotient_class_floor(okey_to_float(kkey), Tm);
     }
     __syncthreads();

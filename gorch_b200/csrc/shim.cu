@@ -840,8 +840,8 @@ static int vocab_merge_launch(Ctx* c, const void* all_records, int nranks, int c
   m.nranks = nranks;
   m.cand = cand;
   m.B = B;
-  const unsigned g = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
-  gs::vocab_merge_kernel<<<g, gs::VM_NT, gs::VM_DYN_BYTES, c->stream>>>(m);
+  const unsigned g = static_cast<unsigned>(B < 8 * c->sm_count ? B : 8 * c->sm_count);
+  gs::vocab_merge_kernel<<<g, gs::VM_NT, gs::vm_dyn_bytes(nranks, cand), c->stream>>>(m);
   CUDA_TRY(cudaGetLastError(), errOut);
   c->counters.kernel_launches += 1;
   c->counters.sample_launches += 1;
