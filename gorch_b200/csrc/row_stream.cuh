@@ -14,7 +14,7 @@ constexpr int W_PF = GS_W_PF;           // L2 prefetch distance in steps (passes
 #ifndef GS_N_PF
 #define GS_N_PF 8
 #endif
-constexpr int N_PF = GS_N_PF;           // the same for the narrow kernel's single pass from HBM
+constexpr int N_PF = GS_N_PF;           // the same for single passes from HBM (Multinomial)
 __device__ __forceinline__ uint4 ldg_hint(const uint4* p, unsigned long long pol) {
   uint4 v;
   asm volatile("ld.global.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol));

@@ -7,16 +7,16 @@
 //                          persistent kernel walks ALL rows with its own atomic
 //                          cursor and takes the rows of its kind, so no separate
 //                          classification launch and no per-kind lists exist.
-//   narrow_rows_kernel     256 threads, four CTAs per SM. One streaming pass per
-//                          row: the first 4096 logits give a threshold (k-th
-//                          largest of the 256 per-thread maxima, a lower bound
-//                          of the k-th largest logit); then every warp walks
-//                          its own span of the rest (row_stream.cuh) and appends
-//                          the few logits above the threshold, with no barrier
-//                          per step; the list is pruned to the exact k-th
-//                          largest when a warp sees it half full. Everything
-//                          after the pass happens on a few hundred candidates
-//                          in shared memory.
+//   narrow_rows_kernel     (sample_narrow.cuh, two instances: 256 threads x five CTAs per SM,
+//                          128 threads x eight). One streaming pass per row: the first
+//                          16 logits per thread give a threshold (from the per-thread
+//                          maxima: a lower bound of the k-th largest logit, or a tighter
+//                          estimate that is checked at the row's end); then every warp
+//                          walks its own span of the rest, staged through a ring of
+//                          asynchronous copies in shared memory, and only notes where
+//                          a logit reaches the threshold; the noted vectors are read
+//                          again after the stream, and everything from there on happens
+//                          on a few hundred candidates in shared memory.
 //   wide_rows_kernel       (sample_wide.cuh) rows whose softmax runs over the
 //                          whole vocabulary.
 //

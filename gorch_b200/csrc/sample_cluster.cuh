@@ -132,9 +132,8 @@ template <> struct Neutral<uint16_t> { static constexpr uint32_t word = 0xff80ff
 // Load vector v of the row; lanes outside [0, V) become -Inf. Max, min and the NaN
 // flag cover the valid lanes only.
 template <typename T>
-__device__ __forceinline__ uint4 load_masked(const RowView<T>& rv, int v, float& vmax, float& vmin, bool& nan_seen) {
+__device__ __forceinline__ uint4 mask_and_stats(const RowView<T>& rv, int v, uint4 raw, float& vmax, float& vmin, bool& nan_seen) {
   constexpr int VEC = Elem<T>::VEC;
-  uint4 raw = __ldg(rv.vbase + v);
   float x[VEC];
   Elem<T>::unpack(raw, x);
   if (v > 0 && v < rv.nvec - 1) {
@@ -162,6 +161,10 @@ __device__ __forceinline__ uint4 load_masked(const RowView<T>& rv, int v, float&
     }
   }
   return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <typename T>
+__device__ __forceinline__ uint4 load_masked(const RowView<T>& rv, int v, float& vmax, float& vmin, bool& nan_seen) {
+  return mask_and_stats(rv, v, __ldg(rv.vbase + v), vmax, vmin, nan_seen);
 }
 
 __device__ __forceinline__ void block_min_i2(int& a_min, int& b_min, Ctl& c, int tid) {
@@ -329,9 +332,16 @@ __global__ void __launch_bounds__(NT, 2) sample_cluster_kernel(ClusterArgs CA) {
   // ---- L / pass A: slice -> shared memory; max, min, NaN, one running max per thread
   float xmax = -INFINITY, xmin = INFINITY;
   bool nan_seen = false;
-  for (int v = v0 + tid; v < v1; v += NT) {
-    uint4 raw = load_masked(rv, v, xmax, xmin, nan_seen);
-    slice[v - v0] = raw;
+  // four vectors per thread in flight at a time: a slice of 50 KB is two trips to HBM, not seven
+  for (int vb = v0 + tid; vb < v1; vb += 4 * NT) {
+    uint4 r4[4];
+#pragma unroll
+    for (int q = 0; q < 4; q++) r4[q] = __ldg(rv.vbase + min(vb + q * NT, v1 - 1));
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      const int v = vb + q * NT;
+      if (v < v1) slice[v - v0] = mask_and_stats(rv, v, r4[q], xmax, xmin, nan_seen);
+    }
   }
   const float tmax = xmax;                                  // this thread's group maximum
   const int anynan_loc = block_max_i(nan_seen ? 1 : 0, ctl, tid);

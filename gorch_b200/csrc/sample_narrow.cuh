@@ -134,7 +134,7 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   const double plim = (mode == 0) ? static_cast<double>(cfg.top_p) * 1.5 : static_cast<double>(cfg.top_p);
   dbg.path = 1;
 
-  // ---- warm-up chunk: 16 logits per thread, kept in registers; one running maximum per thread
+  // ---- warm-up chunk: the row's first 16 logits per thread, kept in registers; one running maximum per thread
   float xmax = -INFINITY, xmin = INFINITY;
   bool nan_seen = false;
   if (tid == 0) { *s_cnt = 0; *s_hcnt = 0; *s_flag = 0; }
@@ -178,11 +178,13 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
   };
 #pragma unroll
   for (int q = 0; q < NQ; q++) ring_issue(q);
-  // Threshold from the 256 per-thread maxima of the chunk: every warp sorts its 32 maxima with
-  // shuffles, and every thread then finds the place of its own among all 256 by a binary search
+  // Threshold from the N_NT per-thread maxima of the chunk: every warp sorts its 32 maxima with
+  // shuffles, and every thread then finds the place of its own among all of them by a binary search
   // in each of the other warps' sorted lists (two barriers; a radix select over so few keys costs
   // several rounds of barriers and of shared atomics that all hit the same few bins, and counting
-  // all 256 against each other three times the instructions).
+  // all maxima against each other three times the instructions). A rank beyond N_NT (top_k above
+  // 128 on a short row, 128-thread instance) finds no thread: the threshold stays open and the
+  // overflow path below takes the exact top_k-th largest of the chunk instead.
   //  * The top_k-th largest maximum is a BOUND: top_k threads each hold a logit at or above it, so
   //    the top_k-th largest logit of the row is at or above it.
   //  * The r-th largest maximum with r < top_k, r chosen so that about four times top_k logits of
