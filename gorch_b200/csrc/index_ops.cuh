@@ -21,7 +21,9 @@ namespace gs {
 constexpr int MN_NT = 256;
 constexpr int MN_NW = MN_NT / 32;
 constexpr int MN_MAX_STEPS = 256;                          // steps per warp: rows up to 8 * 256 * 256 = 524288 probabilities
-constexpr int MN_DYN_BYTES = MN_NW * MN_MAX_STEPS * 8;     // 16 KB of step sums
+constexpr int MN_NQ = 3;                                   // steps of the row in flight per thread
+constexpr int MN_RING_OFF = MN_NW * MN_MAX_STEPS * 8;      // after the 16 KB of step sums
+constexpr int MN_DYN_BYTES = MN_RING_OFF + MN_NQ * 2 * MN_NT * 16;   // + 24 KB of ring
 
 struct MultinomialArgs {
   const float* probs;      // [B, row_stride]
@@ -72,20 +74,37 @@ __global__ void __launch_bounds__(MN_NT, 4) multinomial_rows_kernel(MultinomialA
       }
     };
     {
-      uint4 q0a, q0b, q1a, q1b;
-      w_load<float, N_PF>(sp, 0, pol, q0a, q0b);
-      w_load<float, N_PF>(sp, 1, pol, q1a, q1b);
+      // The row is staged through a ring in shared memory by asynchronous 16-byte copies, MN_NQ
+      // steps ahead (a thread copies what it consumes itself and waits only for its own groups):
+      // loads into registers in a rolled loop share one scoreboard and do not run ahead.
+      const uint32_t ring_addr = static_cast<uint32_t>(__cvta_generic_to_shared(dyn + MN_RING_OFF)) + static_cast<uint32_t>(tid * 16);
+      const uint4* ring = reinterpret_cast<const uint4*>(dyn + MN_RING_OFF) + tid;
+      auto issue = [&](int q) {
+        if (q < sp.nst) {
+          const uint32_t dst = ring_addr + static_cast<uint32_t>((q % MN_NQ) * 2 * MN_NT * 16);
+          const int o = q * SV;
+          asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;"
+                       :: "r"(dst), "l"(sp.lane_src + min(o, sp.omax)), "l"(pol) : "memory");
+          asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;"
+                       :: "r"(dst + MN_NT * 16), "l"(sp.lane_src + min(o + 32, sp.omax)), "l"(pol) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      };
+#pragma unroll
+      for (int q = 0; q < MN_NQ; q++) issue(q);
 #pragma unroll 1
       for (int st = 0; st < sp.nst; st++) {
-        const uint4 ca = q0a, cb = q0b;
-        q0a = q1a; q0b = q1b;
-        w_load<float, N_PF>(sp, st + 2, pol, q1a, q1b);
+        asm volatile("cp.async.wait_group %0;" :: "n"(MN_NQ - 1) : "memory");
+        const uint4 ca = ring[(st % MN_NQ) * 2 * MN_NT];
+        const uint4 cb = ring[(st % MN_NQ) * 2 * MN_NT + MN_NT];
         double v[8];
         vals(st, ca, cb, v);
+        issue(st + MN_NQ);                                 // into the slot just read
         double s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
         s = warp_sum_d(s);
         if (lane == 0) stepsum[warp * steps + st] = s;
       }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
     // prefix over the warp-steps in row order: thread t owns steps [t*PER, t*PER+PER)
