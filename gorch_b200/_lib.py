@@ -19,7 +19,8 @@ EXPORTS = [
     "gorch_cuda_buffer_device_ptr", "gorch_cuda_buffer_upload", "gorch_cuda_buffer_download",
     "gorch_cuda_sample_host", "gorch_cuda_sample_dev", "gorch_cuda_sample_dev_static", "gorch_cuda_sample_row",
     "gorch_cuda_argmax_host", "gorch_cuda_argmax_dev",
-    "gorch_cuda_vocab_local_dev", "gorch_cuda_vocab_merge_dev",
+    "gorch_cuda_vocab_local_dev", "gorch_cuda_vocab_merge_dev", "gorch_cuda_vocab_merge_owner_dev", "gorch_cuda_vocab_draw_dev",
+    "gorch_cuda_sample_vocab_sharded_ex_dev",
     "gorch_cuda_comm_unique_id", "gorch_cuda_comm_init", "gorch_cuda_comm_release", "gorch_cuda_sample_vocab_sharded_dev",
     "gorch_cuda_topk_dev", "gorch_cuda_multinomial_dev",
     "gorch_cuda_lm_head_logits_dev", "gorch_cuda_lm_head_status", "gorch_cuda_lm_head_sample_dev",
@@ -89,6 +90,9 @@ def load() -> C.CDLL:
         "gorch_cuda_argmax_dev": (i32, [p, p, i32, i64, i64, i64, p, err]),
         "gorch_cuda_vocab_local_dev": (i32, [p, p, i32, i64, i64, i64, i64, p, p, err]),
         "gorch_cuda_vocab_merge_dev": (i32, [p, p, i32, i64, i64, p, p, p, p, err]),
+        "gorch_cuda_vocab_merge_owner_dev": (i32, [p, p, i32, i32, i64, i64, p, p, p, p, p, err]),
+        "gorch_cuda_vocab_draw_dev": (i32, [p, p, i32, i64, i64, i64, i64, p, p, p, p, err]),
+        "gorch_cuda_sample_vocab_sharded_ex_dev": (i32, [p, p, i32, i64, i64, i64, i64, i64, i32, i32, p, p, p, p, err]),
         "gorch_cuda_comm_unique_id": (i32, [p, err]),
         "gorch_cuda_comm_init": (i32, [p, i32, i32, p, err]),
         "gorch_cuda_comm_release": (i32, [p, err]),

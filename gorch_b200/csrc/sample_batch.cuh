@@ -36,7 +36,8 @@ namespace gs {
 // subset of the union of the ranks' lists, because the global k-th largest is at least every
 // local one.
 constexpr int VS_CAND = 128;
-constexpr uint32_t VS_NONFINITE = 1u, VS_BAD_CFG = 2u, VS_OVERFLOW = 4u, VS_UNSUPPORTED = 8u, VS_NAN_AT_0 = 16u;
+constexpr uint32_t VS_NONFINITE = 1u, VS_BAD_CFG = 2u, VS_OVERFLOW = 4u, VS_UNSUPPORTED = 8u, VS_NAN_AT_0 = 16u,
+                   VS_SUMEXP = 32u;   // a row without top-k: cand[0] holds the slice's sum of exponentials (f64 bits)
 struct VsRecord {
   float xmax;              // largest local logit (not yet divided by the temperature)
   int32_t n;               // entries in cand
@@ -51,6 +52,17 @@ __device__ __forceinline__ VsRecord& vs_record(void* base, int64_t row, int cand
 }
 __device__ __forceinline__ const VsRecord& vs_record(const void* base, int64_t row, int cand) {
   return *reinterpret_cast<const VsRecord*>(static_cast<const unsigned char*>(base) + row * (16 + 8 * static_cast<int64_t>(cand)));
+}
+
+// A row's top-p setting cuts nothing: off, or the mode A rule with 1.5 p >= 1 (generate.go:184-228).
+__device__ __forceinline__ bool vs_cut_inert(const RowCfg& c) {
+  const bool on = c.top_p > 0.0f && c.top_p < 1.0f;
+  return !on || (c.topp_mode == 0 && static_cast<double>(c.top_p) * 1.5 >= 1.0);
+}
+// exp(d), d <= 0, as f64: the table form (2e-11) where it applies, the all-f64 routine elsewhere.
+// The local pass and the owner's draw use the same function, so that their sums agree term by term.
+__device__ __forceinline__ double vs_exp(float d, const double* __restrict__ eb, const double* __restrict__ tab) {
+  return (d > -31.9f) ? exp_fast(d, eb) : exp_safe(d, tab);
 }
 
 struct BatchArgs {

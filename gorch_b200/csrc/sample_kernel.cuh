@@ -68,6 +68,7 @@ template <> struct Elem<float> {
     x[0] = __uint_as_float(r.x); x[1] = __uint_as_float(r.y);
     x[2] = __uint_as_float(r.z); x[3] = __uint_as_float(r.w);
   }
+  __device__ static __forceinline__ float to_float(float v) { return v; }
 };
 template <> struct Elem<uint16_t> {  // bf16 bit patterns; upcast = bits << 16 (tensor.go:96-99)
   static constexpr int VEC = 8;
@@ -77,6 +78,7 @@ template <> struct Elem<uint16_t> {  // bf16 bit patterns; upcast = bits << 16 (
     x[4] = __uint_as_float(r.z << 16); x[5] = __uint_as_float(r.z & 0xffff0000u);
     x[6] = __uint_as_float(r.w << 16); x[7] = __uint_as_float(r.w & 0xffff0000u);
   }
+  __device__ static __forceinline__ float to_float(uint16_t v) { return __uint_as_float(static_cast<uint32_t>(v) << 16); }
 };
 
 // A row seen as 16-byte vectors. Rows need not start on a 16-byte boundary

@@ -31,7 +31,17 @@ struct MergeArgs {
   int32_t nranks;
   int32_t cand;             // candidates per record
   int64_t B;
+  int32_t my_rank;          // rows without top-k: which rank this is (-1: such rows are not served)
+  double* draw_req;         // [B][3] or null: for rows without top-k that this rank owns, what vocab_draw_kernel needs
 };
+
+// Rows without top-k (records carry VS_SUMEXP): the merge adds the slices' sums, rescaled to the
+// row's maximum, in rank order (= index order: the slices are contiguous); the rank in whose slice
+// u * S falls owns the row and finds the token by a pass over its slice (vocab_draw_kernel); the
+// other ranks write -1, and an all-reduce (max) of the ids hands the token to everyone.
+// draw_req[row] = {target in units of the owner's own sum, S in those units, the owner's scaled
+// maximum}; a row this rank does not own gets a NaN target.
+constexpr int VD_NT = 256;
 
 __global__ void __launch_bounds__(VM_NT, 8) vocab_merge_kernel(MergeArgs M) {
   extern __shared__ __align__(16) unsigned char dyn[];
@@ -62,6 +72,8 @@ __global__ void __launch_bounds__(VM_NT, 8) vocab_merge_kernel(MergeArgs M) {
         if (A.out_debug) A.out_debug[row] = dbg;
       }
     };
+    // a row that no draw follows (every row with a top-k, greedy rows, refused rows) says so
+    if (tid == 0 && M.draw_req) M.draw_req[row * 3] = __longlong_as_double(0x7ff8000000000000ll);
     // ---- join the ranks' records
     if (tid == 0) s_cnt = 0;
     __syncthreads();
@@ -83,6 +95,51 @@ __global__ void __launch_bounds__(VM_NT, 8) vocab_merge_kernel(MergeArgs M) {
     const uint32_t vfl = fl_loc;                             // uniform: every thread read every record header
     if (vfl & VS_BAD_CFG) { write_row(-1, FLAG_BAD_CFG); continue; }
     if (vfl & (VS_OVERFLOW | VS_UNSUPPORTED)) { write_row(-1, FLAG_INTERNAL); continue; }
+    if (vfl & VS_SUMEXP) {
+      if (!M.draw_req || M.my_rank < 0) { write_row(-1, FLAG_INTERNAL); continue; }
+      if (tid == 0) {
+        double* req = M.draw_req + row * 3;
+        float mrow = -INFINITY;
+        for (int r = 0; r < M.nranks; r++)
+          mrow = fmaxf(mrow, scale_t(vs_record(M.records, static_cast<int64_t>(r) * M.B + row, M.cand).xmax, Tm));
+        double w[VM_MAX_RANKS], S = 0.0;
+        for (int r = 0; r < M.nranks; r++) {
+          const VsRecord& rec = vs_record(M.records, static_cast<int64_t>(r) * M.B + row, M.cand);
+          const double Sr = __longlong_as_double(static_cast<long long>((static_cast<unsigned long long>(rec.cand[0].y) << 32) | rec.cand[0].x));
+          const float sr = scale_t(rec.xmax, Tm);
+          w[r] = (sr == -INFINITY) ? 0.0 : Sr * exp(static_cast<double>(sr) - static_cast<double>(mrow));
+          S += w[r];
+        }
+        dbg.max_scaled = mrow; dbg.sum_exp = S;
+        int id = -1;
+        uint32_t fl = 0u;
+        if ((vfl & VS_NONFINITE) || !(fabsf(mrow) < INFINITY) || !(S > 0.0) || !(S == S)) {
+          id = A.V - 1; fl = FLAG_NONFINITE | FLAG_FALLBACK;   // generate.go:173-181, 239
+        } else {
+          const double target = A.uniforms[row] * S;          // first index with u < cumulative / S
+          double cum = 0.0;
+          int owner = -1;
+          for (int r = 0; r < M.nranks; r++) {
+            if (target < cum + w[r]) { owner = r; break; }
+            cum += w[r];
+          }
+          if (owner < 0) {
+            id = A.V - 1; fl = FLAG_FALLBACK | ((target - S <= 1e-6 * S) ? FLAG_BOUNDARY : 0u);
+          } else if (owner == M.my_rank) {
+            const VsRecord& rec = vs_record(M.records, static_cast<int64_t>(owner) * M.B + row, M.cand);
+            const float sr = scale_t(rec.xmax, Tm);
+            const double f = exp(static_cast<double>(sr) - static_cast<double>(mrow));
+            req[0] = (target - cum) / f;
+            req[1] = S / f;
+            req[2] = static_cast<double>(sr);
+          }
+        }
+        A.out_ids[row] = id;
+        if (A.out_flags) A.out_flags[row] = fl;
+        if (A.out_debug) A.out_debug[row] = dbg;
+      }
+      continue;
+    }
     // ---- greedy (generate.go:134-144): largest logit, lowest index; a NaN at index 0 is never beaten
     if (Tm == 0.0f) {
       unsigned long long best = 0ull;
@@ -129,6 +186,88 @@ __global__ void __launch_bounds__(VM_NT, 8) vocab_merge_kernel(MergeArgs M) {
     const int mode = cfg.topp_mode;
     const double plim = (mode == 0) ? static_cast<double>(cfg.top_p) * 1.5 : static_cast<double>(cfg.top_p);
     finish_small_set<VM_NT>(A, row, kept, nk, m, Tm, topp_on, mode, plim, A.uniforms[row], work, sc, s_bcd, dbg, 0u);
+  }
+}
+
+struct DrawArgs {
+  const void* logits;       // this rank's slice [B, row_stride]
+  int64_t row_stride;
+  int32_t V;                // slice length
+  int32_t col_offset;       // global index of the slice's first column
+  const RowCfg* cfgs;
+  const double* draw_req;   // [B][3] from the merge
+  const double* eb_table;
+  const double* exp_table;
+  int32_t* out_ids;
+  uint32_t* out_flags;
+  int64_t B;
+};
+
+// The owner's pass over its slice: first index whose running sum of exp(x/T - own maximum), in
+// index order, exceeds the target. Tiles of VD_NT x 4 logits, one block scan per tile.
+template <typename T>
+__global__ void __launch_bounds__(VD_NT, 4) vocab_draw_kernel(DrawArgs D) {
+  __shared__ bu::Scratch sc;
+  __shared__ int s_hit[2];
+  const int tid = threadIdx.x;
+  constexpr int NW = VD_NT / 32, PER = 4;
+  for (int64_t row = blockIdx.x; row < D.B; row += gridDim.x) {
+    const double target = D.draw_req[row * 3];
+    if (!(target == target)) continue;                       // not this rank's row (uniform: all threads read it)
+    const double S = D.draw_req[row * 3 + 1];
+    const float sr = static_cast<float>(D.draw_req[row * 3 + 2]);
+    const float Tm = D.cfgs[row].temperature;
+    const T* xr = static_cast<const T*>(D.logits) + row * D.row_stride;
+    double base = 0.0;
+    int found = -1;
+    double lo = 0.0, hi = 0.0;
+    for (int i0 = 0; i0 < D.V && found < 0; i0 += VD_NT * PER) {   // uniform
+      double e[PER], mine = 0.0;
+#pragma unroll
+      for (int c = 0; c < PER; c++) {
+        const int i = i0 + tid * PER + c;
+        e[c] = 0.0;
+        if (i < D.V) {
+          const float x = Elem<T>::to_float(xr[i]);
+          e[c] = vs_exp(scale_t(x, Tm) - sr, D.eb_table, D.exp_table);
+        }
+        mine += e[c];
+      }
+      double tot;
+      const double ex = bu::scan_excl_d<NW>(mine, tot, sc, tid);
+      const int first = (target < base + ex + mine) ? tid : VD_NT;
+      const int who = bu::min_i<NW>(first, sc, tid);
+      if (who < VD_NT) {
+        if (tid == who) {
+          double run = base + ex;
+          int pick = -1;
+#pragma unroll
+          for (int c = 0; c < PER; c++) {
+            if (pick < 0 && target < run + e[c]) { pick = i0 + tid * PER + c; lo = run; hi = run + e[c]; }
+            if (pick < 0) run += e[c];
+          }
+          s_hit[0] = pick;
+          uint32_t fl = 0u;
+          if ((target - lo) <= 1e-6 * S || (hi - target) <= 1e-6 * S) fl |= FLAG_BOUNDARY;
+          s_hit[1] = static_cast<int>(fl);
+        }
+        __syncthreads();
+        found = s_hit[0];
+        if (tid == 0) {
+          D.out_ids[row] = found + D.col_offset;
+          if (D.out_flags) D.out_flags[row] = static_cast<uint32_t>(s_hit[1]);
+        }
+        __syncthreads();
+      }
+      base += tot;
+    }
+    if (found < 0 && tid == 0) {
+      // the slice's running sum, formed in another order than the local pass's, fell short of the
+      // target by rounding: the slice's last logit with mass is the nearest answer
+      int last = D.V - 1;
+      D.out_ids[row] = last + D.col_offset;
+      if (D.out_flags) D.out_flags[row] = FLAG_BOUNDARY;
+    }
   }
 }
 

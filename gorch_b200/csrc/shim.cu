@@ -74,6 +74,7 @@ struct Ctx {
   Scratch lmh_scratch;       // status word, thresholds, candidate lists, sample logits of the LM-head path
   Scratch lmh_logits;        // [B, V] f32 when rows need the unfused samplers
   Scratch vs_local, vs_all;  // records of the vocab-sharded call: this rank's, and every rank's after the all-gather
+  Scratch vs_req;            // [B][3] doubles: what the owner's draw of a row without top-k needs
   ncclComm_t comm = nullptr; // set by gorch_cuda_comm_init
   int comm_rank = 0, comm_nranks = 0;
   cudaEvent_t ev_vs[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -126,6 +127,7 @@ struct NcclApi {
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
   const char* (*GetErrorString)(ncclResult_t) = nullptr;
 };
 NcclApi g_nccl;
@@ -144,8 +146,9 @@ int load_nccl(char** errOut) {
   a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
   a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
   a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(h, "ncclAllGather"));
+  a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(h, "ncclAllReduce"));
   a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
-  if (!a.GetUniqueId || !a.CommInitRank || !a.CommDestroy || !a.AllGather || !a.GetErrorString) {
+  if (!a.GetUniqueId || !a.CommInitRank || !a.CommDestroy || !a.AllGather || !a.AllReduce || !a.GetErrorString) {
     set_err(errOut, "gorch_cuda: libnccl.so.2 lacks a symbol this library needs");
     return GORCH_CUDA_ERR_NCCL;
   }
@@ -638,6 +641,7 @@ void gorch_cuda_release(GorchCudaCtxRef ctx) {
   if (c->lmh_logits.ptr) cudaFree(c->lmh_logits.ptr);
   if (c->vs_local.ptr) cudaFree(c->vs_local.ptr);
   if (c->vs_all.ptr) cudaFree(c->vs_all.ptr);
+  if (c->vs_req.ptr) cudaFree(c->vs_req.ptr);
   for (cudaEvent_t e : c->ev_vs) if (e) cudaEventDestroy(e);
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
@@ -819,7 +823,7 @@ static int vocab_local_launch(Ctx* c, const void* logits, int dtype, int64_t B, 
 
 static int vocab_merge_launch(Ctx* c, const void* all_records, int nranks, int cand, int64_t B, int64_t V,
                               const GorchSampleCfg* cfgs, const double* uniforms, int32_t* out_ids,
-                              uint32_t* out_flags, char** errOut) {
+                              uint32_t* out_flags, char** errOut, int my_rank = -1, double* draw_req = nullptr) {
   if (nranks < 1 || nranks > gs::VM_MAX_RANKS) {
     set_err(errOut, "gorch_cuda: vocab merge takes 1..%d ranks, got %d", gs::VM_MAX_RANKS, nranks);
     return GORCH_CUDA_ERR_LIMIT;
@@ -840,6 +844,8 @@ static int vocab_merge_launch(Ctx* c, const void* all_records, int nranks, int c
   m.nranks = nranks;
   m.cand = cand;
   m.B = B;
+  m.my_rank = my_rank;
+  m.draw_req = draw_req;
   const unsigned g = static_cast<unsigned>(B < 8 * c->sm_count ? B : 8 * c->sm_count);
   gs::vocab_merge_kernel<<<g, gs::VM_NT, gs::vm_dyn_bytes(nranks, cand), c->stream>>>(m);
   CUDA_TRY(cudaGetLastError(), errOut);
@@ -863,6 +869,45 @@ int gorch_cuda_vocab_merge_dev(GorchCudaCtxRef ctx, const void* all_records, int
   Ctx* c = static_cast<Ctx*>(ctx);
   if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
   return vocab_merge_launch(c, all_records, nranks, gs::VS_CAND, B, V, cfgs, uniforms, out_ids, out_flags, errOut);
+}
+
+int gorch_cuda_vocab_merge_owner_dev(GorchCudaCtxRef ctx, const void* all_records, int nranks, int my_rank, int64_t B,
+                                     int64_t V, const GorchSampleCfg* cfgs, const double* uniforms,
+                                     int32_t* out_ids, uint32_t* out_flags, double* draw_req, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  if (my_rank < 0 || my_rank >= nranks || !draw_req) { set_err(errOut, "gorch_cuda: bad rank or null draw request buffer"); return GORCH_CUDA_ERR_BAD_ARG; }
+  return vocab_merge_launch(c, all_records, nranks, gs::VS_CAND, B, V, cfgs, uniforms, out_ids, out_flags, errOut, my_rank, draw_req);
+}
+
+static int vocab_draw_launch(Ctx* c, const void* logits_slice, int dtype, int64_t B, int64_t Vslice, int64_t row_stride,
+                             int64_t col_offset, const GorchSampleCfg* cfgs, const double* draw_req, int32_t* out_ids,
+                             uint32_t* out_flags, char** errOut) {
+  int rc = check_shape(dtype, B, Vslice, row_stride, errOut);
+  if (rc) return rc;
+  if (B == 0) return GORCH_CUDA_OK;
+  if (!logits_slice || !cfgs || !draw_req || !out_ids) { set_err(errOut, "gorch_cuda: null pointer argument"); return GORCH_CUDA_ERR_BAD_ARG; }
+  CUDA_TRY(cudaSetDevice(c->device), errOut);
+  gs::DrawArgs d;
+  d.logits = logits_slice; d.row_stride = row_stride; d.V = static_cast<int32_t>(Vslice);
+  d.col_offset = static_cast<int32_t>(col_offset);
+  d.cfgs = reinterpret_cast<const gs::RowCfg*>(cfgs); d.draw_req = draw_req;
+  d.eb_table = c->eb_table; d.exp_table = c->exp_table;
+  d.out_ids = out_ids; d.out_flags = out_flags; d.B = B;
+  const unsigned g = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
+  if (dtype == GORCH_CUDA_F32) gs::vocab_draw_kernel<float><<<g, gs::VD_NT, 0, c->stream>>>(d);
+  else gs::vocab_draw_kernel<uint16_t><<<g, gs::VD_NT, 0, c->stream>>>(d);
+  CUDA_TRY(cudaGetLastError(), errOut);
+  c->counters.kernel_launches += 1;
+  return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_vocab_draw_dev(GorchCudaCtxRef ctx, const void* logits_slice, int dtype, int64_t B, int64_t Vslice,
+                              int64_t row_stride, int64_t col_offset, const GorchSampleCfg* cfgs,
+                              const double* draw_req, int32_t* out_ids, uint32_t* out_flags, char** errOut) {
+  Ctx* c = static_cast<Ctx*>(ctx);
+  if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
+  return vocab_draw_launch(c, logits_slice, dtype, B, Vslice, row_stride, col_offset, cfgs, draw_req, out_ids, out_flags, errOut);
 }
 
 int gorch_cuda_comm_unique_id(void* id_bytes, char** errOut) {
@@ -914,10 +959,10 @@ int gorch_cuda_comm_release(GorchCudaCtxRef ctx, char** errOut) {
   return GORCH_CUDA_OK;
 }
 
-int gorch_cuda_sample_vocab_sharded_dev(GorchCudaCtxRef ctx, const void* logits_slice, int dtype, int64_t B,
-                                        int64_t Vslice, int64_t row_stride, int64_t col_offset, int64_t V,
-                                        int max_top_k, const GorchSampleCfg* cfgs, const double* uniforms,
-                                        int32_t* out_ids, uint32_t* out_flags, char** errOut) {
+static int sample_vocab_sharded(GorchCudaCtxRef ctx, const void* logits_slice, int dtype, int64_t B,
+                                int64_t Vslice, int64_t row_stride, int64_t col_offset, int64_t V,
+                                int max_top_k, int rows_without_top_k, const GorchSampleCfg* cfgs, const double* uniforms,
+                                int32_t* out_ids, uint32_t* out_flags, char** errOut) {
   Ctx* c = static_cast<Ctx*>(ctx);
   if (!c) { set_err(errOut, "gorch_cuda: null context"); return GORCH_CUDA_ERR_BAD_ARG; }
   if (!c->comm) { set_err(errOut, "gorch_cuda: no communicator: call gorch_cuda_comm_init first"); return GORCH_CUDA_ERR_NCCL; }
@@ -944,8 +989,24 @@ int gorch_cuda_sample_vocab_sharded_dev(GorchCudaCtxRef ctx, const void* logits_
   // ONE collective: every rank's records to every rank, in rank order, on the context's stream
   NCCL_TRY(g_nccl.AllGather(c->vs_local.ptr, c->vs_all.ptr, static_cast<size_t>(B) * rec_bytes, ncclUint8, c->comm, c->stream), errOut);
   if (c->timing) CUDA_TRY(cudaEventRecord(c->ev_vs[2], c->stream), errOut);
-  rc = vocab_merge_launch(c, c->vs_all.ptr, c->comm_nranks, cand, B, V, cfgs, uniforms, out_ids, out_flags, errOut);
-  if (rc) return rc;
+  if (rows_without_top_k) {
+    // Rows without top-k: the merge names each such row's owner (the rank in whose slice u * S
+    // falls), the owner finds the token in its slice, and an all-reduce (max) of ids and flags
+    // hands it to every rank (the others wrote -1 and 0; rows with a top-k agree on every rank).
+    if (!out_flags) { set_err(errOut, "gorch_cuda: rows without top-k need out_flags"); return GORCH_CUDA_ERR_BAD_ARG; }
+    rc = ensure(c->vs_req, static_cast<size_t>(B) * 3 * sizeof(double), errOut);
+    if (rc) return rc;
+    double* req = static_cast<double*>(c->vs_req.ptr);
+    rc = vocab_merge_launch(c, c->vs_all.ptr, c->comm_nranks, cand, B, V, cfgs, uniforms, out_ids, out_flags, errOut, c->comm_rank, req);
+    if (rc) return rc;
+    rc = vocab_draw_launch(c, logits_slice, dtype, B, Vslice, row_stride, col_offset, cfgs, req, out_ids, out_flags, errOut);
+    if (rc) return rc;
+    NCCL_TRY(g_nccl.AllReduce(out_ids, out_ids, static_cast<size_t>(B), ncclInt32, ncclMax, c->comm, c->stream), errOut);
+    NCCL_TRY(g_nccl.AllReduce(out_flags, out_flags, static_cast<size_t>(B), ncclUint32, ncclMax, c->comm, c->stream), errOut);
+  } else {
+    rc = vocab_merge_launch(c, c->vs_all.ptr, c->comm_nranks, cand, B, V, cfgs, uniforms, out_ids, out_flags, errOut);
+    if (rc) return rc;
+  }
   if (c->timing) {
     CUDA_TRY(cudaEventRecord(c->ev_vs[3], c->stream), errOut);
     CUDA_TRY(cudaEventSynchronize(c->ev_vs[3]), errOut);
@@ -955,6 +1016,22 @@ int gorch_cuda_sample_vocab_sharded_dev(GorchCudaCtxRef ctx, const void* logits_
     CUDA_TRY(cudaEventElapsedTime(&c->counters.last_kernel_ms, c->ev_vs[0], c->ev_vs[3]), errOut);
   }
   return GORCH_CUDA_OK;
+}
+
+int gorch_cuda_sample_vocab_sharded_dev(GorchCudaCtxRef ctx, const void* logits_slice, int dtype, int64_t B,
+                                        int64_t Vslice, int64_t row_stride, int64_t col_offset, int64_t V,
+                                        int max_top_k, const GorchSampleCfg* cfgs, const double* uniforms,
+                                        int32_t* out_ids, uint32_t* out_flags, char** errOut) {
+  return sample_vocab_sharded(ctx, logits_slice, dtype, B, Vslice, row_stride, col_offset, V, max_top_k, 0, cfgs, uniforms,
+                              out_ids, out_flags, errOut);
+}
+
+int gorch_cuda_sample_vocab_sharded_ex_dev(GorchCudaCtxRef ctx, const void* logits_slice, int dtype, int64_t B,
+                                           int64_t Vslice, int64_t row_stride, int64_t col_offset, int64_t V,
+                                           int max_top_k, int rows_without_top_k, const GorchSampleCfg* cfgs,
+                                           const double* uniforms, int32_t* out_ids, uint32_t* out_flags, char** errOut) {
+  return sample_vocab_sharded(ctx, logits_slice, dtype, B, Vslice, row_stride, col_offset, V, max_top_k, rows_without_top_k,
+                              cfgs, uniforms, out_ids, out_flags, errOut);
 }
 
 int gorch_cuda_topk_dev(GorchCudaCtxRef ctx, const void* x, int dtype, int64_t B, int64_t V,

@@ -270,13 +270,59 @@ class CudaSampler:
 
     def sample_vocab_sharded_ptrs(self, logits_ptr: int, dtype: int, B: int, Vslice: int, row_stride: int,
                                   col_offset: int, V: int, max_top_k: int, cfgs_ptr: int, uniforms_ptr: int,
-                                  ids_ptr: int, flags_ptr: int | None = None) -> None:
-        """gorch_cuda_sample_vocab_sharded_dev: device pointers; local pass, all-gather, merge."""
+                                  ids_ptr: int, flags_ptr: int | None = None, rows_without_top_k: bool = False) -> None:
+        """gorch_cuda_sample_vocab_sharded_dev: device pointers; local pass, all-gather, merge.
+        rows_without_top_k: the batch may hold rows with top_k == 0 (gorch_cuda_sample_vocab_sharded_ex_dev:
+        the owners then draw from their slices and two small all-reduces hand the tokens round)."""
         err = C.c_void_p()
-        rc = self._lib.gorch_cuda_sample_vocab_sharded_dev(self._ctx, logits_ptr, dtype, B, Vslice, row_stride,
-                                                           col_offset, V, int(max_top_k), cfgs_ptr, uniforms_ptr,
-                                                           ids_ptr, flags_ptr, C.byref(err))
+        if rows_without_top_k:
+            rc = self._lib.gorch_cuda_sample_vocab_sharded_ex_dev(self._ctx, logits_ptr, dtype, B, Vslice, row_stride,
+                                                                  col_offset, V, int(max_top_k), 1, cfgs_ptr, uniforms_ptr,
+                                                                  ids_ptr, flags_ptr, C.byref(err))
+        else:
+            rc = self._lib.gorch_cuda_sample_vocab_sharded_dev(self._ctx, logits_ptr, dtype, B, Vslice, row_stride,
+                                                               col_offset, V, int(max_top_k), cfgs_ptr, uniforms_ptr,
+                                                               ids_ptr, flags_ptr, C.byref(err))
         _check(self._lib, rc, err)
+
+    def vocab_merge_draw(self, all_records, my_rank: int, logits_slice, col_offset: int, cfgs, uniforms, V: int):
+        """Steps 2 and 3 of one rank on host arrays, rows without top-k included: records
+        [nranks, B, VS_RECORD_BYTES] -> gorch_cuda_vocab_merge_owner_dev -> gorch_cuda_vocab_draw_dev over
+        this rank's slice -> (ids, flags) as this rank holds them before the max-reduction over the ranks
+        (-1 / 0 in the rows without top-k that another rank owns)."""
+        rec = np.ascontiguousarray(all_records, dtype=np.uint8)
+        nranks, B = rec.shape[0], rec.shape[1]
+        x, dtype = _logits_arg(logits_slice)
+        Vs = x.shape[1]
+        cfgs = np.ascontiguousarray(cfgs, dtype=CFG_DTYPE)
+        uniforms = np.ascontiguousarray(uniforms, dtype=np.float64)
+        ids = np.empty(B, dtype=np.int32)
+        flags = np.zeros(B, dtype=np.uint32)
+        bufs = []
+        try:
+            b_rec = self._buf(rec.nbytes); bufs.append(b_rec)
+            b_log = self._buf(max(x.nbytes, 16)); bufs.append(b_log)
+            b_cfg = self._buf(cfgs.nbytes); bufs.append(b_cfg)
+            b_uni = self._buf(uniforms.nbytes); bufs.append(b_uni)
+            b_ids = self._buf(ids.nbytes); bufs.append(b_ids)
+            b_flg = self._buf(flags.nbytes); bufs.append(b_flg)
+            b_req = self._buf(B * 24); bufs.append(b_req)
+            self._upload(b_rec, rec); self._upload(b_log, x); self._upload(b_cfg, cfgs); self._upload(b_uni, uniforms)
+            ptr = self._lib.gorch_cuda_buffer_device_ptr
+            err = C.c_void_p()
+            rc = self._lib.gorch_cuda_vocab_merge_owner_dev(self._ctx, ptr(b_rec), nranks, int(my_rank), B, int(V), ptr(b_cfg),
+                                                            ptr(b_uni), ptr(b_ids), ptr(b_flg), ptr(b_req), C.byref(err))
+            _check(self._lib, rc, err)
+            rc = self._lib.gorch_cuda_vocab_draw_dev(self._ctx, ptr(b_log), dtype, B, Vs, Vs, int(col_offset), ptr(b_cfg),
+                                                     ptr(b_req), ptr(b_ids), ptr(b_flg), C.byref(err))
+            _check(self._lib, rc, err)
+            self.sync()
+            self._download(b_ids, ids)
+            self._download(b_flg, flags)
+        finally:
+            for b in bufs:
+                self._lib.gorch_cuda_buffer_free(b)
+        return ids, flags
 
     def vocab_local(self, logits_slice, cfgs, col_offset: int) -> np.ndarray:
         """Step 1 on host arrays: this rank's [B, Vslice] columns -> records [B, VS_RECORD_BYTES] (uint8)."""

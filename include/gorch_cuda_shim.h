@@ -181,7 +181,10 @@ int gorch_cuda_sample_dev_static(GorchCudaCtxRef ctx, const void* logits, int dt
 /* Vocab-sharded sampling (no counterpart in the reference, which runs on one device): every
  * rank holds the same B rows but only the columns [col_offset, col_offset + Vslice) of the
  * vocabulary. Rows must have 0 < top_k <= GORCH_VS_CAND (the top-k bounds what has to cross the
- * link) or temperature 0; other rows come back with id -1 and GORCH_FLAG_INTERNAL.
+ * link) or temperature 0; rows with top_k == 0 and no effective top-p cut (top_p off, or the
+ * model/generate.go rule with 1.5 top_p >= 1) are served by the calls that name a row's owner
+ * (gorch_cuda_vocab_merge_owner_dev, gorch_cuda_sample_vocab_sharded_ex_dev); all other rows come
+ * back with id -1 and GORCH_FLAG_INTERNAL.
  *   1. every rank: gorch_cuda_vocab_local_dev fills B records of GORCH_VS_RECORD_BYTES (local
  *      maximum, and every local logit at or above the local top_k-th largest with its global
  *      index: 16 header bytes + GORCH_VS_CAND pairs of (f32 bits, u32 index));
@@ -198,6 +201,24 @@ int gorch_cuda_vocab_local_dev(GorchCudaCtxRef ctx, const void* logits, int dtyp
 int gorch_cuda_vocab_merge_dev(GorchCudaCtxRef ctx, const void* all_records, int nranks, int64_t B,
                                int64_t V, const GorchSampleCfg* cfgs, const double* uniforms,
                                int32_t* out_ids, uint32_t* out_flags, char** errOut);
+/* Rows without top-k (plain softmax sampling over the whole vocabulary): a slice's record holds its
+ * maximum and its sum of exponentials relative to that maximum (generate.go:167-181 on the slice).
+ * gorch_cuda_vocab_merge_owner_dev is gorch_cuda_vocab_merge_dev that also serves such rows: it adds
+ * the slices' sums, rescaled to the row's maximum, in rank order, and names the rank in whose
+ * slice uniform * sum falls the row's owner; rank my_rank's draw_req [B][3] doubles then tells
+ * gorch_cuda_vocab_draw_dev, which runs on every rank over its own slice, which rows it owns and
+ * where in its slice's running sum the token lies; it writes the token into out_ids / out_flags of
+ * the rows it owns. The other ranks hold -1 and 0 there: a max-reduction of out_ids and out_flags
+ * over the ranks gives every rank every token (rows with a top-k already agree). The sums are
+ * formed per slice, so such a row's token can differ from the one-device result when the uniform
+ * lies within 1e-6 of an edge of the chosen interval (GORCH_FLAG_BOUNDARY). */
+int gorch_cuda_vocab_merge_owner_dev(GorchCudaCtxRef ctx, const void* all_records, int nranks, int my_rank,
+                                     int64_t B, int64_t V, const GorchSampleCfg* cfgs, const double* uniforms,
+                                     int32_t* out_ids, uint32_t* out_flags, double* draw_req, char** errOut);
+int gorch_cuda_vocab_draw_dev(GorchCudaCtxRef ctx, const void* logits_slice, int dtype, int64_t B,
+                              int64_t Vslice, int64_t row_stride, int64_t col_offset,
+                              const GorchSampleCfg* cfgs, const double* draw_req, int32_t* out_ids,
+                              uint32_t* out_flags, char** errOut);
 
 /* The three steps above as ONE call, with the collective inside the library (no counterpart in the
  * reference): local pass -> ncclAllGather of the records on the context's stream -> merge. Every
@@ -219,6 +240,15 @@ int gorch_cuda_sample_vocab_sharded_dev(GorchCudaCtxRef ctx, const void* logits_
                                         int64_t Vslice, int64_t row_stride, int64_t col_offset, int64_t V,
                                         int max_top_k, const GorchSampleCfg* cfgs, const double* uniforms,
                                         int32_t* out_ids, uint32_t* out_flags, char** errOut);
+/* The same with rows_without_top_k != 0 for batches that hold rows with top_k == 0: after the
+ * merge the owners draw from their slices and two small ncclAllReduce (max) calls, over out_ids
+ * and out_flags (required here), hand the tokens to every rank. With rows_without_top_k == 0 it is
+ * the call above. */
+int gorch_cuda_sample_vocab_sharded_ex_dev(GorchCudaCtxRef ctx, const void* logits_slice, int dtype, int64_t B,
+                                           int64_t Vslice, int64_t row_stride, int64_t col_offset, int64_t V,
+                                           int max_top_k, int rows_without_top_k, const GorchSampleCfg* cfgs,
+                                           const double* uniforms, int32_t* out_ids, uint32_t* out_flags,
+                                           char** errOut);
 
 /* The reference's tensor-level index ops as batched device ops (device pointers, asynchronous on
  * the context's stream).

@@ -128,7 +128,7 @@ def test_masked_slices(sampler, oracle, world):
     check(sampler, oracle, logits, cfgs, rng.random(B), world)
 
 
-def _fused_call(s, logits, cfgs, uniforms, max_top_k):
+def _fused_call(s, logits, cfgs, uniforms, max_top_k, rows_without_top_k=False):
     """gorch_cuda_sample_vocab_sharded_dev on this process's one rank (device buffers of the library)."""
     from gorch_b200.config import DTYPE_BF16, DTYPE_F32
     B, V = logits.shape
@@ -143,7 +143,8 @@ def _fused_call(s, logits, cfgs, uniforms, max_top_k):
         b_flg = s._buf(B * 4); bufs.append(b_flg)
         s._upload(b_log, np.ascontiguousarray(logits)); s._upload(b_cfg, cfgs); s._upload(b_uni, uniforms)
         ptr = lib.gorch_cuda_buffer_device_ptr
-        s.sample_vocab_sharded_ptrs(ptr(b_log), code, B, V, V, 0, V, max_top_k, ptr(b_cfg), ptr(b_uni), ptr(b_ids), ptr(b_flg))
+        s.sample_vocab_sharded_ptrs(ptr(b_log), code, B, V, V, 0, V, max_top_k, ptr(b_cfg), ptr(b_uni), ptr(b_ids), ptr(b_flg),
+                                    rows_without_top_k=rows_without_top_k)
         s.sync()
         ids = np.empty(B, dtype=np.int32); flags = np.empty(B, dtype=np.uint32)
         s._download(b_ids, ids); s._download(b_flg, flags)
@@ -170,6 +171,17 @@ def test_collective_inside_the_library_one_rank(_sampler_session, oracle):
         # a top_k above what the record was sized for is reported, not mis-sampled
         ids, flags = _fused_call(s, w.logits, w.cfgs, w.uniforms, 16)
         assert (ids == -1).all() and (flags & FLAG_INTERNAL).all()
+        # rows without top-k through the same call: merge of the sums, the owner's draw, the two all-reduces
+        rng = np.random.Generator(np.random.Philox(key=31))
+        x = (rng.standard_normal((40, 30011)) * 2.5).astype(np.float32)
+        cf = np.zeros(40, dtype=CFG_DTYPE)
+        for i in range(40):
+            cf[i] = [(1.0, 0, 0.0, 0), (0.8, 40, 0.0, 0), (0.7, 0, 0.9, 0), (0.0, 0, 0.0, 0)][i % 4]
+        uu = rng.random(40)
+        ids, flags = _fused_call(s, x, cf, uu, 40, rows_without_top_k=True)
+        check_ids(oracle, x, cf, uu, ids, flags)
+        ids, flags = _fused_call(s, x, cf, uu, 40)               # without the flag such rows are refused, the others served
+        assert np.all(ids[0::2] == -1) and np.all(ids[1::2] >= 0)
         # timing of the phases
         s.set_timing(True)
         _fused_call(s, w.logits, w.cfgs, w.uniforms, 64)
@@ -178,3 +190,69 @@ def test_collective_inside_the_library_one_rank(_sampler_session, oracle):
         assert c["vs_local_ms"] > 0 and c["vs_merge_ms"] > 0 and c["vs_gather_ms"] >= 0
     finally:
         s.comm_release()
+
+
+def run_sharded_with_owner_draw(sampler, logits, cfgs, uniforms, world):
+    """As run_sharded, for batches that hold rows without top-k: every rank merges with its own rank
+    number, draws from its own slice for the rows it owns, and the ranks' ids / flags are joined by
+    the maximum, as the all-reduce inside gorch_cuda_sample_vocab_sharded_ex_dev does."""
+    V = logits.shape[1]
+    recs, slices = [], []
+    for r in range(world):
+        lo, hi = workloads.shard_vocab(V, r, world)
+        slices.append((lo, np.ascontiguousarray(logits[:, lo:hi])))
+        recs.append(sampler.vocab_local(slices[-1][1], cfgs, lo))
+    allrec = np.stack(recs)
+    ids = np.full(logits.shape[0], -(2 ** 31), dtype=np.int64)
+    flags = np.zeros(logits.shape[0], dtype=np.uint32)
+    per_rank = []
+    for r in range(world):
+        i_r, f_r = sampler.vocab_merge_draw(allrec, r, slices[r][1], slices[r][0], cfgs, uniforms, V)
+        per_rank.append(i_r)
+        ids = np.maximum(ids, i_r)
+        flags = np.maximum(flags, f_r)
+    return ids.astype(np.int32), flags, per_rank
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_rows_without_top_k(sampler, oracle, world, bf16):
+    """Plain softmax sampling over a sharded vocabulary (top_k == 0, no effective top-p cut) beside
+    top-k and greedy rows: the slices' sums of exponentials are merged, the owner draws."""
+    rng = np.random.Generator(np.random.Philox(key=0xABCD + world + (100 if bf16 else 0)))
+    B, V = 60, 20011
+    x = (rng.standard_normal((B, V)) * 2.5).astype(np.float32)
+    x[3, :] = -np.inf; x[3, 17000:17010] = 1.0          # all mass in one late slice
+    x[4, 0] = 30.0                                       # nearly all mass at index 0
+    logits = workloads.f32_to_bf16_bits(x) if bf16 else x
+    cfgs = np.zeros(B, dtype=CFG_DTYPE)
+    for i in range(B):
+        cfgs[i] = [(1.0, 0, 0.0, 0), (0.7, 0, 0.9, 0), (1.3, 0, 1.0, 1), (0.8, 40, 0.0, 0), (0.0, 0, 0.0, 0), (0.9, 0, 0.0, 1)][i % 6]
+    u = rng.random(B)
+    u[6] = 0.0; u[12] = 1.0 - 2.0 ** -53
+    ids, flags, per_rank = run_sharded_with_owner_draw(sampler, logits, cfgs, u, world)
+    check_ids(oracle, logits, cfgs, u, ids, flags)
+    soft = np.array([i % 6 in (0, 1, 2, 5) for i in range(B)])
+    owners = np.stack([p[soft] >= 0 for p in per_rank]).sum(axis=0)
+    assert np.all(owners == 1), "every row without top-k has exactly one owner"
+
+
+def test_rows_without_top_k_but_with_a_cut_are_refused(sampler):
+    rng = np.random.Generator(np.random.Philox(key=5))
+    x = (rng.standard_normal((4, 4096)) * 2.0).astype(np.float32)
+    cfgs = np.zeros(4, dtype=CFG_DTYPE)
+    cfgs[:] = (1.0, 0, 0.9, 1)                           # mode B nucleus over the whole vocabulary: not served when sharded
+    ids, flags, _ = run_sharded_with_owner_draw(sampler, x, cfgs, rng.random(4), 2)
+    assert np.all(ids == -1) and np.all(flags & FLAG_INTERNAL)
+
+
+def test_nonfinite_rows_without_top_k(sampler):
+    B, V = 3, 4096
+    x = np.zeros((B, V), np.float32)
+    x[0, 3000] = np.nan
+    x[1, 10] = np.inf
+    x[2, :] = -np.inf
+    cfgs = np.zeros(B, dtype=CFG_DTYPE)
+    cfgs[:] = (1.0, 0, 0.0, 0)
+    ids, flags, _ = run_sharded_with_owner_draw(sampler, x, cfgs, np.full(B, 0.5), 4)
+    assert ids.tolist() == [V - 1] * 3                   # generate.go:173-181, 239: the walk falls through
