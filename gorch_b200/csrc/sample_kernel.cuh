@@ -55,6 +55,7 @@ struct KernelArgs {
   void* vs_records;        // vocab-sharded local pass (narrow kernel only): [B] VsRecord to fill instead of drawing
   int32_t vs_col_offset;   // global index of this slice's first column
   int32_t vs_cand;         // candidates per record (records are 16 + 8 * vs_cand bytes apart), at most VS_CAND
+  int32_t vs_sumexp;       // rows without top-k are served (their records come from vocab_sumexp_kernel)
   float* tk_values;        // TopK op (narrow kernel only): [B, tk_k] values, descending; null otherwise
   int32_t* tk_indices;     // [B, tk_k] indices (ties: ascending index)
   int32_t tk_k;            // 0: not a TopK launch

@@ -124,33 +124,8 @@ __device__ void narrow_row(const BatchArgs& BA, const int64_t row_id, unsigned c
     write_row(-1, FLAG_BAD_CFG);
     return;
   }
-  if (A.vs_records && cfg.top_k == 0 && vs_cut_inert(cfg)) {
-    // Vocab-sharded row without top-k and without an effective top-p cut (plain softmax sampling):
-    // what the merge needs from a slice is its maximum and its sum of exponentials relative to
-    // that maximum (generate.go:167-181 on the slice). Two passes over the slice, the second from L2.
-    float vmax = -INFINITY;
-    bool nan_loc = false;
-    for (int v = tid; v < rv.nvec; v += N_NT)
-      rv.visit(v, [&](float x, int) { vmax = fmaxf(vmax, x); nan_loc |= (x != x); });
-    const int slice_nan = bu::max_i<N_NW>(nan_loc ? 1 : 0, sc, tid);
-    const float smax_x = okey_to_float(static_cast<uint32_t>(bu::max_u64<N_NW>(static_cast<unsigned long long>(okey(vmax)), sc, tid)));
-    const float sm = scale_t(smax_x, Tm);
-    double acc = 0.0;
-    if (!slice_nan && fabsf(sm) < INFINITY) {
-      for (int v = tid; v < rv.nvec; v += N_NT)
-        rv.visit(v, [&](float x, int) { acc += vs_exp(scale_t(x, Tm) - sm, BA.eb_table, A.exp_table); });
-    }
-    const double Sr = bu::sum_d<N_NW>(acc, sc, tid);
-    if (tid == 0) {
-      VsRecord& rec = vs_record(A.vs_records, row_id, A.vs_cand);
-      rec.xmax = smax_x; rec.n = 0; rec.pad = 0;
-      // a slice of -Inf only (a masked part of the vocabulary) carries no mass and no verdict
-      rec.flags = VS_SUMEXP | ((slice_nan || sm == INFINITY || sm != sm) ? VS_NONFINITE : 0u);
-      const unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong((sm == -INFINITY) ? 0.0 : Sr));
-      rec.cand[0] = make_uint2(static_cast<uint32_t>(bits), static_cast<uint32_t>(bits >> 32));
-    }
-    return;
-  }
+  // a vocab-sharded row without top-k: vocab_sumexp_kernel fills its record, when the caller asked for that
+  if (A.vs_records && A.vs_sumexp && cfg.top_k == 0 && vs_cut_inert(cfg)) return;
   if (A.vs_records && !(cfg.top_k > 0 && cfg.top_k <= A.vs_cand)) {   // the merge needs a top-k to bound the lists
     vs_flag_only(VS_UNSUPPORTED);
     return;

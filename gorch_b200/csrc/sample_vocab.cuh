@@ -189,6 +189,47 @@ __global__ void __launch_bounds__(VM_NT, 8) vocab_merge_kernel(MergeArgs M) {
   }
 }
 
+// The local pass of a vocab-sharded row without top-k and without an effective top-p cut (plain
+// softmax sampling): what the merge needs from a slice is its maximum and its sum of exponentials
+// relative to that maximum (generate.go:167-181 on the slice). Two passes over the slice, the
+// second from L2. A kernel of its own, beside the narrow kernel's launch, so that the narrow kernel
+// (whose registers are spoken for) stays as it is for every other caller.
+template <typename T>
+__global__ void __launch_bounds__(VD_NT, 4) vocab_sumexp_kernel(KernelArgs A, const double* eb_table, int64_t B) {
+  __shared__ bu::Scratch sc;
+  const int tid = threadIdx.x;
+  constexpr int NW = VD_NT / 32;
+  for (int64_t row = blockIdx.x; row < B; row += gridDim.x) {
+    const RowCfg cfg = A.cfgs[row];
+    const float Tm = cfg.temperature;
+    if (!(Tm > 0.0f) || !(Tm < INFINITY) || cfg.top_k != 0 || !vs_cut_inert(cfg)) continue;   // the narrow kernel's rows
+    RowView<T> rv;
+    rv.init(static_cast<const T*>(A.logits) + row * A.row_stride, A.V);
+    float vmax = -INFINITY;
+    bool nan_loc = false;
+    for (int v = tid; v < rv.nvec; v += VD_NT)
+      rv.visit(v, [&](float x, int) { vmax = fmaxf(vmax, x); nan_loc |= (x != x); });
+    const int slice_nan = bu::max_i<NW>(nan_loc ? 1 : 0, sc, tid);
+    const float smax_x = okey_to_float(static_cast<uint32_t>(bu::max_u64<NW>(static_cast<unsigned long long>(okey(vmax)), sc, tid)));
+    const float sm = scale_t(smax_x, Tm);
+    double acc = 0.0;
+    if (!slice_nan && fabsf(sm) < INFINITY) {
+      for (int v = tid; v < rv.nvec; v += VD_NT)
+        rv.visit(v, [&](float x, int) { acc += vs_exp(scale_t(x, Tm) - sm, eb_table, A.exp_table); });
+    }
+    const double Sr = bu::sum_d<NW>(acc, sc, tid);
+    if (tid == 0) {
+      VsRecord& rec = vs_record(A.vs_records, row, A.vs_cand);
+      rec.xmax = smax_x; rec.n = 0; rec.pad = 0;
+      // a slice of -Inf only (a masked part of the vocabulary) carries no mass and no verdict
+      rec.flags = VS_SUMEXP | ((slice_nan || sm == INFINITY || sm != sm) ? VS_NONFINITE : 0u);
+      const unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong((sm == -INFINITY) ? 0.0 : Sr));
+      rec.cand[0] = make_uint2(static_cast<uint32_t>(bits), static_cast<uint32_t>(bits >> 32));
+    }
+    __syncthreads();
+  }
+}
+
 struct DrawArgs {
   const void* logits;       // this rank's slice [B, row_stride]
   int64_t row_stride;
@@ -219,7 +260,7 @@ __global__ void __launch_bounds__(VD_NT, 4) vocab_draw_kernel(DrawArgs D) {
     const float Tm = D.cfgs[row].temperature;
     const T* xr = static_cast<const T*>(D.logits) + row * D.row_stride;
     double base = 0.0;
-    int found = -1;
+    int found = -1, lastpos = -1;                           // lastpos: this thread's last logit with mass
     double lo = 0.0, hi = 0.0;
     for (int i0 = 0; i0 < D.V && found < 0; i0 += VD_NT * PER) {   // uniform
       double e[PER], mine = 0.0;
@@ -230,6 +271,7 @@ __global__ void __launch_bounds__(VD_NT, 4) vocab_draw_kernel(DrawArgs D) {
         if (i < D.V) {
           const float x = Elem<T>::to_float(xr[i]);
           e[c] = vs_exp(scale_t(x, Tm) - sr, D.eb_table, D.exp_table);
+          if (e[c] > 0.0) lastpos = i;
         }
         mine += e[c];
       }
@@ -261,12 +303,14 @@ __global__ void __launch_bounds__(VD_NT, 4) vocab_draw_kernel(DrawArgs D) {
       }
       base += tot;
     }
-    if (found < 0 && tid == 0) {
+    if (found < 0) {                                         // uniform
       // the slice's running sum, formed in another order than the local pass's, fell short of the
       // target by rounding: the slice's last logit with mass is the nearest answer
-      int last = D.V - 1;
-      D.out_ids[row] = last + D.col_offset;
-      if (D.out_flags) D.out_flags[row] = FLAG_BOUNDARY;
+      const int last = bu::max_i<NW>(lastpos, sc, tid);
+      if (tid == 0) {
+        D.out_ids[row] = max(last, 0) + D.col_offset;
+        if (D.out_flags) D.out_flags[row] = FLAG_BOUNDARY;
+      }
     }
   }
 }

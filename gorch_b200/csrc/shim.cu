@@ -268,6 +268,7 @@ int launch_rows(Ctx* c, const void* logits, int dtype, int64_t B, int64_t V, int
   a.vs_records = nullptr;
   a.vs_col_offset = 0;
   a.vs_cand = gs::VS_CAND;
+  a.vs_sumexp = 0;
   a.row_done = row_done;
   a.tk_values = nullptr;
   a.tk_indices = nullptr;
@@ -780,7 +781,8 @@ int gorch_cuda_sample_dev(GorchCudaCtxRef ctx, const void* logits, int dtype, in
 }
 
 static int vocab_local_launch(Ctx* c, const void* logits, int dtype, int64_t B, int64_t Vslice, int64_t row_stride,
-                              int64_t col_offset, const GorchSampleCfg* cfgs, void* records, int cand, char** errOut) {
+                              int64_t col_offset, const GorchSampleCfg* cfgs, void* records, int cand, char** errOut,
+                              bool sumexp_rows = true) {
   int rc = check_shape(dtype, B, Vslice, row_stride, errOut);
   if (rc) return rc;
   static_assert(sizeof(gs::VsRecord) == GORCH_VS_RECORD_BYTES, "record layout");
@@ -810,14 +812,21 @@ static int vocab_local_launch(Ctx* c, const void* logits, int dtype, int64_t B, 
   ba.k.out_ids = nullptr; ba.k.out_flags = nullptr; ba.k.out_probs = nullptr; ba.k.out_debug = nullptr;
   ba.k.exp_table = c->exp_table; ba.k.row_offset = 0; ba.k.worklist = nullptr;
   ba.k.vs_records = records; ba.k.vs_col_offset = static_cast<int32_t>(col_offset); ba.k.vs_cand = cand;
+  ba.k.vs_sumexp = sumexp_rows ? 1 : 0;
   ba.k.tk_values = nullptr; ba.k.tk_indices = nullptr; ba.k.tk_k = 0; ba.k.row_done = nullptr;
   ba.eb_table = c->eb_table;
   ba.hdr = base; ba.list_single = base + 15;
   ba.B = B;
   CUDA_TRY(cudaMemsetAsync(base, 0, 16 * sizeof(int32_t), c->stream), errOut);
   CUDA_TRY(launch_narrow(c, ba, dtype, B), errOut);
-  CUDA_TRY(cudaGetLastError(), errOut);
   c->counters.kernel_launches += 1;
+  if (sumexp_rows) {                                         // the records of rows without top-k: disjoint rows, same stream
+    const unsigned g = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
+    if (dtype == GORCH_CUDA_F32) gs::vocab_sumexp_kernel<float><<<g, gs::VD_NT, 0, c->stream>>>(ba.k, c->eb_table, B);
+    else gs::vocab_sumexp_kernel<uint16_t><<<g, gs::VD_NT, 0, c->stream>>>(ba.k, c->eb_table, B);
+    c->counters.kernel_launches += 1;
+  }
+  CUDA_TRY(cudaGetLastError(), errOut);
   return GORCH_CUDA_OK;
 }
 
@@ -839,6 +848,7 @@ static int vocab_merge_launch(Ctx* c, const void* all_records, int nranks, int c
   m.k.out_ids = out_ids; m.k.out_flags = out_flags; m.k.out_probs = nullptr; m.k.out_debug = nullptr;
   m.k.exp_table = c->exp_table; m.k.row_offset = 0; m.k.worklist = nullptr; m.k.vs_records = nullptr; m.k.vs_col_offset = 0;
   m.k.vs_cand = cand;
+  m.k.vs_sumexp = 0;
   m.k.tk_values = nullptr; m.k.tk_indices = nullptr; m.k.tk_k = 0; m.k.row_done = nullptr;
   m.records = all_records;
   m.nranks = nranks;
@@ -983,7 +993,8 @@ static int sample_vocab_sharded(GorchCudaCtxRef ctx, const void* logits_slice, i
   rc = ensure(c->vs_all, static_cast<size_t>(B) * rec_bytes * static_cast<size_t>(c->comm_nranks), errOut);
   if (rc) return rc;
   if (c->timing) CUDA_TRY(cudaEventRecord(c->ev_vs[0], c->stream), errOut);
-  rc = vocab_local_launch(c, logits_slice, dtype, B, Vslice, row_stride, col_offset, cfgs, c->vs_local.ptr, cand, errOut);
+  rc = vocab_local_launch(c, logits_slice, dtype, B, Vslice, row_stride, col_offset, cfgs, c->vs_local.ptr, cand, errOut,
+                          rows_without_top_k != 0);
   if (rc) return rc;
   if (c->timing) CUDA_TRY(cudaEventRecord(c->ev_vs[1], c->stream), errOut);
   // ONE collective: every rank's records to every rank, in rank order, on the context's stream
@@ -1072,7 +1083,7 @@ int gorch_cuda_topk_dev(GorchCudaCtxRef ctx, const void* x, int dtype, int64_t B
   ba.k.force_greedy = 0; ba.k.cfgs = nullptr; ba.k.uniforms = nullptr;
   ba.k.out_ids = nullptr; ba.k.out_flags = out_flags; ba.k.out_probs = nullptr; ba.k.out_debug = nullptr;
   ba.k.exp_table = c->exp_table; ba.k.row_offset = 0; ba.k.worklist = nullptr;
-  ba.k.vs_records = nullptr; ba.k.vs_col_offset = 0;
+  ba.k.vs_records = nullptr; ba.k.vs_col_offset = 0; ba.k.vs_sumexp = 0;
   ba.k.tk_values = out_values; ba.k.tk_indices = out_indices; ba.k.tk_k = static_cast<int32_t>(k); ba.k.row_done = nullptr;
   ba.eb_table = c->eb_table;
   ba.hdr = base; ba.list_single = base + 15;
@@ -1395,7 +1406,7 @@ int gorch_cuda_lm_head_sample_dev(GorchCudaCtxRef ctx, const void* x, int64_t ld
   memset(&fa, 0, sizeof fa);
   fa.k.V = static_cast<int32_t>(V); fa.k.row_stride = V;
   fa.k.cfgs = reinterpret_cast<const gs::RowCfg*>(cfgs); fa.k.uniforms = uniforms;
-  fa.k.out_ids = out_ids; fa.k.out_flags = out_flags; fa.k.exp_table = c->exp_table; fa.k.vs_cand = gs::VS_CAND;
+  fa.k.out_ids = out_ids; fa.k.out_flags = out_flags; fa.k.exp_table = c->exp_table; fa.k.vs_cand = gs::VS_CAND; fa.k.vs_sumexp = 0;
   fa.sample = reinterpret_cast<const float*>(base + off_smp); fa.nsample = nsample; fa.fuse_top_k = fuse_top_k;
   fa.thr = reinterpret_cast<float*>(base + off_thr);
   fa.cand = reinterpret_cast<const uint2*>(base + off_cand);
