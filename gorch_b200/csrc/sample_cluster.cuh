@@ -4,7 +4,7 @@
 // shared memory, so HBM is read exactly once per logit; later passes read shared
 // memory. Cross-CTA reductions go through distributed shared memory: a peer
 // stores into the consumer's shared memory, then a cluster barrier publishes it.
-// Nothing in this file loads with multicast.
+// Every CTA loads its own slice with plain vector loads.
 //
 // Row semantics: model/generate.go:134-260 (mode A), model/qwen/generate.go:
 // 77-181 (mode B). Per row:
