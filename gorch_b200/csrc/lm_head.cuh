@@ -36,11 +36,12 @@ constexpr int LMH_BK = 64;               // K per stage: 64 bf16 = one 128-byte 
 constexpr int LMH_STAGES = 5;
 constexpr int LMH_NT = 192;              // warp 0 producer, warp 1 issuer, warps 2-5 epilogue
 constexpr int LMH_STAGE_BYTES = (LMH_BM + LMH_BN) * LMH_BK * 2;     // 32 KB
-constexpr int LMH_ROWS_S = 8192;         // rows whose running maximum a CTA keeps in shared memory
-constexpr int LMH_DYN_BYTES = LMH_STAGES * LMH_STAGE_BYTES + 1024 + LMH_ROWS_S * 8;  // ring (+ room to align it to 1024 bytes) + row maxima and NaN bits
+constexpr int LMH_ROWS_S = 4096;         // rows whose running maximum, NaN bits and candidate count a CTA keeps in shared memory
+constexpr int LMH_DYN_BYTES = LMH_STAGES * LMH_STAGE_BYTES + 1024 + LMH_ROWS_S * 12;  // ring (+ room to align it to 1024 bytes) + the per-row words
 constexpr int LMH_TMEM_COLS = 256;       // two accumulators of 128 f32 columns
 constexpr uint32_t LMH_WAIT_LIMIT = 4000000u;
-constexpr int LMH_CAND_CAP = 2048;       // candidates per row of the fused sampling path (entries of 8 bytes)
+constexpr int LMH_CAND_CAP = 2048;       // candidates per row that the finish kernel takes (entries of 8 bytes)
+constexpr int LMH_SEG = 32;              // candidates per row and CTA: every CTA of the projection has its own segment of a row's list
 
 constexpr uint32_t LMH_ERR_TIMEOUT = 1u;
 
@@ -60,8 +61,8 @@ struct LmHeadArgs {
   int32_t compact;         // 1: tile i goes to columns [i * 128, ...) of out_logits (the sample of tiles)
   // fused sampling (all null when unused)
   const float* thr;        // [B] candidate threshold per row (raw logit units)
-  uint2* cand;             // [B, LMH_CAND_CAP] (logit bits, index)
-  int32_t* cand_cnt;       // [B]
+  uint2* cand;             // [B, gridDim.x, LMH_SEG] (logit bits, index); needs B <= LMH_ROWS_S
+  int32_t* cand_cnt;       // [B, gridDim.x], written by every CTA for every row
   uint32_t* rowmax_key;    // [B] order key of the row maximum (atomicMax)
   int32_t* row_nan;        // [B] a NaN was seen
   uint32_t* status;        // [1] LMH_ERR_* bits
@@ -134,8 +135,9 @@ __global__ void __launch_bounds__(LMH_NT, 1) lm_head_kernel(const __grid_constan
   // thread, so no atomics here); flushed to global memory once at the end
   float* rowmax_s = reinterpret_cast<float*>(lmh_dyn + LMH_STAGES * LMH_STAGE_BYTES + 1024);
   int* rownan_s = reinterpret_cast<int*>(rowmax_s + LMH_ROWS_S);
+  int* rowcnt_s = rownan_s + LMH_ROWS_S;
   const bool rows_in_smem = A.rowmax_key != nullptr && A.B <= LMH_ROWS_S;
-  if (rows_in_smem) for (int r = tid; r < A.B; r += LMH_NT) { rowmax_s[r] = -INFINITY; rownan_s[r] = 0; }
+  if (rows_in_smem) for (int r = tid; r < A.B; r += LMH_NT) { rowmax_s[r] = -INFINITY; rownan_s[r] = 0; rowcnt_s[r] = 0; }
   volatile int* abort_flag = &abort_s;
   const int nkc = A.K / LMH_BK;                                        // K chunks per tile
   const int nbt = (A.B + LMH_BM - 1) / LMH_BM;                         // batch tiles
@@ -253,9 +255,12 @@ __global__ void __launch_bounds__(LMH_NT, 1) lm_head_kernel(const __grid_constan
                   if (j >= nvalid) continue;
                   if (x != x) nan_bits |= (v0 + c + j == 0) ? 3 : 1;
                   vmax = fmaxf(vmax, x);
-                  if (x >= thr) {
-                    const int slot = atomicAdd(&A.cand_cnt[row], 1);
-                    if (slot < LMH_CAND_CAP) A.cand[static_cast<int64_t>(row) * LMH_CAND_CAP + slot] = make_uint2(r[j], static_cast<uint32_t>(v0 + c + j));
+                  if (x >= thr && rows_in_smem) {
+                    // this CTA's own segment of the row's list, and a count that only this thread
+                    // touches: nothing to wait for (an atomic on a count shared by all CTAs made
+                    // every warp wait in nearly every chunk, a quarter more time for the kernel)
+                    const int slot = rowcnt_s[row]++;
+                    if (slot < LMH_SEG) A.cand[(static_cast<int64_t>(row) * gridDim.x + blockIdx.x) * LMH_SEG + slot] = make_uint2(r[j], static_cast<uint32_t>(v0 + c + j));
                   }
                 }
               }
@@ -287,6 +292,7 @@ __global__ void __launch_bounds__(LMH_NT, 1) lm_head_kernel(const __grid_constan
       const float v = rowmax_s[r];
       if (v > -INFINITY) atomicMax(&A.rowmax_key[r], okey(v));
       if (rownan_s[r]) atomicOr(&A.row_nan[r], rownan_s[r]);
+      if (A.cand_cnt) A.cand_cnt[static_cast<int64_t>(r) * gridDim.x + blockIdx.x] = rowcnt_s[r];
     }
   }
   if (abort_s) {
@@ -311,11 +317,11 @@ __global__ void __launch_bounds__(LMH_NT, 1) lm_head_kernel(const __grid_constan
 //      logits of the whole row (at least 256, at most a third of the list) are expected above it: an
 //      estimate, not a bound;
 //   3. the projection over all tiles: the epilogue appends every logit at or above the row's
-//      threshold to the row's candidate list (no [B, V] logits are written);
+//      threshold to this CTA's segment of the row's candidate list (no [B, V] logits are written);
 //   4. lmh_finish_kernel: the exact top_k-th largest of the candidates with ties kept
 //      (model/generate.go:157-164), then softmax / top-p / draw on the kept set exactly as the
 //      one-GPU narrow kernel does. A row whose estimate failed (fewer than top_k candidates, or more
-//      than the list holds) or whose config the fused path does not serve is counted in nfail; the
+//      than a segment or the list holds) or whose config the fused path does not serve is counted in nfail; the
 //      host then recomputes the batch through the unfused path.
 constexpr int LMH_SAMPLE_TILES_MIN = 8, LMH_SAMPLE_TILES_MAX = 32;   // the sample: 1/32 of the tiles, within these bounds
 constexpr int LMH_F_NT = 256;
@@ -327,8 +333,9 @@ struct LmhSampleArgs {
   int32_t nsample;
   int32_t fuse_top_k;       // rows with 0 < top_k <= fuse_top_k (or temperature 0) are served
   float* thr;               // [B]
-  const uint2* cand;        // [B, LMH_CAND_CAP]
-  const int32_t* cand_cnt;  // [B]
+  const uint2* cand;        // [B, nseg, LMH_SEG]
+  const int32_t* cand_cnt;  // [B, nseg]
+  int32_t nseg;             // CTAs of the projection that filled the lists
   const uint32_t* rowmax_key;
   const int32_t* row_nan;
   int32_t* nfail;           // [1]
@@ -399,12 +406,25 @@ __global__ void __launch_bounds__(LMH_F_NT, 4) lmh_finish_kernel(LmhSampleArgs M
     auto give_up = [&]() { if (tid == 0) atomicAdd(M.nfail, 1); write_row(-1, FLAG_INTERNAL); };
     if (!lmh_row_served(cfg, A.V, M.fuse_top_k)) { give_up(); continue; }
     if (Tm != 0.0f && (!(Tm > 0.0f) || !(Tm < INFINITY))) { write_row(-1, FLAG_BAD_CFG); continue; }
-    const int cnt = M.cand_cnt[row];
+    // the row's candidates: one segment per CTA of the projection
+    if (tid == 0) s_cnt = 0;
+    __syncthreads();
+    int over = 0;
+    for (int c = tid; c < M.nseg; c += LMH_F_NT) {
+      const int n = M.cand_cnt[row * M.nseg + c];
+      if (n > LMH_SEG) over = 1;
+      const int take = min(n, LMH_SEG);
+      const int base = atomicAdd(&s_cnt, take);
+      if (base + take <= LMH_CAND_CAP) {
+        const uint2* seg = M.cand + (row * M.nseg + c) * LMH_SEG;
+        for (int j = 0; j < take; j++) list[base + j] = seg[j];
+      }
+    }
+    over = __syncthreads_or(over);
+    const int cnt = s_cnt;
     const int nanb = M.row_nan[row];
     const int keff = (Tm == 0.0f) ? 1 : cfg.top_k;
-    if (cnt > LMH_CAND_CAP || (cnt < keff && !(nanb & 1))) { give_up(); continue; }   // the estimate failed for this row
-    for (int j = tid; j < cnt; j += LMH_F_NT) list[j] = M.cand[row * LMH_CAND_CAP + j];
-    __syncthreads();
+    if (over || cnt > LMH_CAND_CAP || (cnt < keff && !(nanb & 1))) { give_up(); continue; }   // the estimate failed for this row
     // ---- greedy (generate.go:134-144): largest logit, lowest index; a NaN at index 0 is never beaten
     if (Tm == 0.0f) {
       unsigned long long best = 0ull;

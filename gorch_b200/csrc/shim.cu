@@ -1381,20 +1381,23 @@ int gorch_cuda_lm_head_sample_dev(GorchCudaCtxRef ctx, const void* x, int64_t ld
     if ((r2 = launch_lm_head(c, u, errOut))) return r2;
     return launch_rows(c, c->lmh_logits.ptr, GORCH_CUDA_F32, B, V, ld, cfgs, uniforms, out_ids, out_flags, nullptr, nullptr, 0, errOut);
   };
-  if (fuse_top_k < 1 || fuse_top_k > gs::KFAST || ntile < 4 * gs::LMH_SAMPLE_TILES_MIN) return unfused();
+  if (fuse_top_k < 1 || fuse_top_k > gs::KFAST || ntile < 4 * gs::LMH_SAMPLE_TILES_MIN || B > gs::LMH_ROWS_S) return unfused();
   int stiles = ntile / 32;
   if (stiles < gs::LMH_SAMPLE_TILES_MIN) stiles = gs::LMH_SAMPLE_TILES_MIN;
   if (stiles > gs::LMH_SAMPLE_TILES_MAX) stiles = gs::LMH_SAMPLE_TILES_MAX;
 
   // ---- the fused form: scratch = [status, nfail | thr | rowmax | nan | count | sample logits | candidates]
   const int nsample = stiles * gs::LMH_BN;
-  const size_t off_thr = 256, off_max = off_thr + 4 * B, off_nan = off_max + 4 * B, off_cnt = off_nan + 4 * B;
-  const size_t off_smp = (off_cnt + 4 * B + 255) & ~static_cast<size_t>(255);
-  const size_t off_cand = (off_smp + sizeof(float) * B * nsample + 255) & ~static_cast<size_t>(255);
-  const size_t total = off_cand + sizeof(uint2) * static_cast<size_t>(B) * gs::LMH_CAND_CAP;
+  // (candidates: one segment of LMH_SEG entries per row and CTA of the projection, and its count)
+  const size_t nseg = static_cast<size_t>(ntile < c->sm_count ? ntile : c->sm_count);
+  const size_t off_thr = 256, off_max = off_thr + 4 * B, off_nan = off_max + 4 * B;
+  const size_t off_smp = (off_nan + 4 * B + 255) & ~static_cast<size_t>(255);
+  const size_t off_cnt = (off_smp + sizeof(float) * B * nsample + 255) & ~static_cast<size_t>(255);
+  const size_t off_cand = (off_cnt + 4 * static_cast<size_t>(B) * nseg + 255) & ~static_cast<size_t>(255);
+  const size_t total = off_cand + sizeof(uint2) * static_cast<size_t>(B) * nseg * gs::LMH_SEG;
   if ((rc = ensure(c->lmh_scratch, total, errOut))) return rc;
   unsigned char* base = static_cast<unsigned char*>(c->lmh_scratch.ptr);
-  CUDA_TRY(cudaMemsetAsync(base, 0, off_smp, c->stream), errOut);          // status, nfail, maxima, NaN bits, counts
+  CUDA_TRY(cudaMemsetAsync(base, 0, off_smp, c->stream), errOut);          // status, nfail, maxima, NaN bits (every CTA of the projection writes its counts)
   // 1. a sample of the vocabulary's tiles (all of them full tiles)
   gs::LmHeadArgs sa = a;
   sa.tile0 = 0; sa.tile_step = (ntile - 1) / stiles; sa.ntile = stiles;
@@ -1414,6 +1417,7 @@ int gorch_cuda_lm_head_sample_dev(GorchCudaCtxRef ctx, const void* x, int64_t ld
   fa.rowmax_key = reinterpret_cast<const uint32_t*>(base + off_max);
   fa.row_nan = reinterpret_cast<const int32_t*>(base + off_nan);
   fa.nfail = reinterpret_cast<int32_t*>(base + 4);
+  fa.nseg = static_cast<int32_t>(nseg);
   fa.B = B;
   const unsigned g = static_cast<unsigned>(B < 4 * c->sm_count ? B : 4 * c->sm_count);
   gs::lmh_threshold_kernel<<<g, gs::LMH_F_NT, 0, c->stream>>>(fa);

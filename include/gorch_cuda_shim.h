@@ -366,7 +366,8 @@ int gorch_cuda_lm_head_status(GorchCudaCtxRef ctx, uint32_t* status, char** errO
  * projection's epilogue fills, and the [B, V] logits are never written; the call then blocks until
  * the ids are there, and if a row could not be finished that way (top_k off or above fuse_top_k, or
  * a row whose largest logits a sample of the vocabulary misjudged) the whole batch is redone through
- * the unfused form. fuse_top_k == 0 (or a vocabulary below 4096 columns): the unfused form at once:
+ * the unfused form. fuse_top_k == 0 (or a vocabulary below 4096 columns, or more than 4096 rows): the
+ * unfused form at once:
  * logits into scratch memory of the context, then the kernels of gorch_cuda_sample_dev
  * (asynchronous). */
 int gorch_cuda_lm_head_sample_dev(GorchCudaCtxRef ctx, const void* x, int64_t ldx, const void* w, int64_t ldw,
