@@ -315,4 +315,17 @@ __global__ void __launch_bounds__(VD_NT, 4) vocab_draw_kernel(DrawArgs D) {
   }
 }
 
+// done[b] = 0 for the rows that the gathered-rows path samples: sampling rows without top-k whose
+// top-p cut is active, and with owner_draw off every sampling row without top-k; 1 for all others
+// (they have their token from the records).
+__global__ void vocab_gather_mask_kernel(const RowCfg* cfgs, int32_t V, int64_t B, bool owner_draw, int32_t* done) {
+  const int64_t b = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (b >= B) return;
+  const RowCfg c = cfgs[b];
+  const float T = c.temperature;
+  const bool sampling = T > 0.0f && T < INFINITY;
+  const bool topk_off = !(c.top_k > 0 && c.top_k < V);
+  done[b] = (sampling && topk_off && !(owner_draw && vs_cut_inert(c))) ? 0 : 1;
+}
+
 }  // namespace gs

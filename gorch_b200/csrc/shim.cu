@@ -75,6 +75,7 @@ struct Ctx {
   Scratch lmh_logits;        // [B, V] f32 when rows need the unfused samplers
   Scratch vs_local, vs_all;  // records of the vocab-sharded call: this rank's, and every rank's after the all-gather
   Scratch vs_req;            // [B][3] doubles: what the owner's draw of a row without top-k needs
+  Scratch vs_rows, vs_done;  // whole rows [B][V padded] and the mask of rows that do not need them (vocab-sharded rows without top-k that are gathered)
   ncclComm_t comm = nullptr; // set by gorch_cuda_comm_init
   int comm_rank = 0, comm_nranks = 0;
   cudaEvent_t ev_vs[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -643,6 +644,8 @@ void gorch_cuda_release(GorchCudaCtxRef ctx) {
   if (c->vs_local.ptr) cudaFree(c->vs_local.ptr);
   if (c->vs_all.ptr) cudaFree(c->vs_all.ptr);
   if (c->vs_req.ptr) cudaFree(c->vs_req.ptr);
+  if (c->vs_rows.ptr) cudaFree(c->vs_rows.ptr);
+  if (c->vs_done.ptr) cudaFree(c->vs_done.ptr);
   for (cudaEvent_t e : c->ev_vs) if (e) cudaEventDestroy(e);
   if (c->ev0) cudaEventDestroy(c->ev0);
   if (c->ev1) cudaEventDestroy(c->ev1);
@@ -994,13 +997,13 @@ static int sample_vocab_sharded(GorchCudaCtxRef ctx, const void* logits_slice, i
   if (rc) return rc;
   if (c->timing) CUDA_TRY(cudaEventRecord(c->ev_vs[0], c->stream), errOut);
   rc = vocab_local_launch(c, logits_slice, dtype, B, Vslice, row_stride, col_offset, cfgs, c->vs_local.ptr, cand, errOut,
-                          rows_without_top_k != 0);
+                          (rows_without_top_k & 1) != 0);
   if (rc) return rc;
   if (c->timing) CUDA_TRY(cudaEventRecord(c->ev_vs[1], c->stream), errOut);
   // ONE collective: every rank's records to every rank, in rank order, on the context's stream
   NCCL_TRY(g_nccl.AllGather(c->vs_local.ptr, c->vs_all.ptr, static_cast<size_t>(B) * rec_bytes, ncclUint8, c->comm, c->stream), errOut);
   if (c->timing) CUDA_TRY(cudaEventRecord(c->ev_vs[2], c->stream), errOut);
-  if (rows_without_top_k) {
+  if (rows_without_top_k & 1) {
     // Rows without top-k: the merge names each such row's owner (the rank in whose slice u * S
     // falls), the owner finds the token in its slice, and an all-reduce (max) of ids and flags
     // hands it to every rank (the others wrote -1 and 0; rows with a top-k agree on every rank).
@@ -1016,6 +1019,35 @@ static int sample_vocab_sharded(GorchCudaCtxRef ctx, const void* logits_slice, i
     NCCL_TRY(g_nccl.AllReduce(out_flags, out_flags, static_cast<size_t>(B), ncclUint32, ncclMax, c->comm, c->stream), errOut);
   } else {
     rc = vocab_merge_launch(c, c->vs_all.ptr, c->comm_nranks, cand, B, V, cfgs, uniforms, out_ids, out_flags, errOut);
+    if (rc) return rc;
+  }
+  if (rows_without_top_k & 2) {
+    // Rows without top-k that the records cannot serve (a top-p cut over the whole vocabulary; with
+    // bit 0 clear every row without top-k): the rows themselves are brought together — every rank
+    // puts its slice into a zeroed [B, V] buffer and an all-reduce (sum) fills in the others' (x + 0
+    // is x in any order; a -0 may come out as +0, which no comparison or exponential tells apart) —
+    // and the ordinary kernels sample those rows on every rank, all others masked out. Correct, not
+    // fast: V * B elements cross the links twice.
+    if (!out_flags) { set_err(errOut, "gorch_cuda: gathered rows need out_flags"); return GORCH_CUDA_ERR_BAD_ARG; }
+    const size_t es = elem_size(dtype);
+    const int64_t ldv = (V + 15) & ~15ll;
+    rc = ensure(c->vs_rows, static_cast<size_t>(B) * ldv * es, errOut);
+    if (rc) return rc;
+    rc = ensure(c->vs_done, static_cast<size_t>(B) * sizeof(int32_t), errOut);
+    if (rc) return rc;
+    CUDA_TRY(cudaMemsetAsync(c->vs_rows.ptr, 0, static_cast<size_t>(B) * ldv * es, c->stream), errOut);
+    CUDA_TRY(cudaMemcpy2DAsync(static_cast<unsigned char*>(c->vs_rows.ptr) + static_cast<size_t>(col_offset) * es, ldv * es,
+                               logits_slice, static_cast<size_t>(row_stride) * es, static_cast<size_t>(Vslice) * es,
+                               static_cast<size_t>(B), cudaMemcpyDeviceToDevice, c->stream), errOut);
+    const ncclDataType_t nt = dtype == GORCH_CUDA_F32 ? ncclFloat32 : static_cast<ncclDataType_t>(9);   // 9: ncclBfloat16
+    NCCL_TRY(g_nccl.AllReduce(c->vs_rows.ptr, c->vs_rows.ptr, static_cast<size_t>(B) * ldv, nt, ncclSum, c->comm, c->stream), errOut);
+    const unsigned gm = static_cast<unsigned>((B + 255) / 256);
+    gs::vocab_gather_mask_kernel<<<gm, 256, 0, c->stream>>>(reinterpret_cast<const gs::RowCfg*>(cfgs), static_cast<int32_t>(V), B,
+                                                            (rows_without_top_k & 1) != 0, static_cast<int32_t*>(c->vs_done.ptr));
+    CUDA_TRY(cudaGetLastError(), errOut);
+    c->counters.kernel_launches += 1;
+    rc = launch_rows(c, c->vs_rows.ptr, dtype, B, V, ldv, cfgs, uniforms, out_ids, out_flags, nullptr, nullptr, 0, errOut, nullptr,
+                     static_cast<const int32_t*>(c->vs_done.ptr));
     if (rc) return rc;
   }
   if (c->timing) {

@@ -91,13 +91,15 @@ def init_vocab_comm(sampler, rank: int, world: int) -> None:
 
 
 def sample_vocab_sharded_device(sampler, d_slice, d_cfgs, d_uniforms, d_ids, d_flags, V: int, rank: int, world: int,
-                                max_top_k: int = 0, rows_without_top_k: bool = False) -> None:
+                                max_top_k: int = 0, rows_without_top_k: bool = False, gather_rows: bool = False) -> None:
     """The device-resident form: `d_slice` [B, hi - lo] (float32, or int16/uint16 holding bf16),
     `d_cfgs` [B, 16] bytes, `d_uniforms` [B] float64, `d_ids` / `d_flags` [B] int32 are torch CUDA
     tensors; local pass, ncclAllGather and merge all run on the sampler's stream inside
     gorch_cuda_sample_vocab_sharded_dev (init_vocab_comm first). Asynchronous. rows_without_top_k: the
     batch may hold rows with top_k == 0 (and no effective top-p cut): their owners draw from their
-    slices and two small all-reduces inside the call hand the tokens to every rank."""
+    slices and two small all-reduces inside the call hand the tokens to every rank. gather_rows: rows with
+    top_k == 0 and an active top-p cut (with rows_without_top_k off: every row with top_k == 0) are sampled
+    from whole rows that one more all-reduce brings to every rank."""
     import torch
     lo, hi = shard_vocab(V, rank, world)
     B = int(d_slice.shape[0])
@@ -106,4 +108,4 @@ def sample_vocab_sharded_device(sampler, d_slice, d_cfgs, d_uniforms, d_ids, d_f
     code = 0 if d_slice.dtype == torch.float32 else 1
     sampler.sample_vocab_sharded_ptrs(d_slice.data_ptr(), code, B, hi - lo, int(d_slice.stride(0)), lo, V, max_top_k,
                                       d_cfgs.data_ptr(), d_uniforms.data_ptr(), d_ids.data_ptr(), d_flags.data_ptr(),
-                                      rows_without_top_k=rows_without_top_k)
+                                      rows_without_top_k=rows_without_top_k, gather_rows=gather_rows)

@@ -270,14 +270,19 @@ class CudaSampler:
 
     def sample_vocab_sharded_ptrs(self, logits_ptr: int, dtype: int, B: int, Vslice: int, row_stride: int,
                                   col_offset: int, V: int, max_top_k: int, cfgs_ptr: int, uniforms_ptr: int,
-                                  ids_ptr: int, flags_ptr: int | None = None, rows_without_top_k: bool = False) -> None:
+                                  ids_ptr: int, flags_ptr: int | None = None, rows_without_top_k: bool = False,
+                                  gather_rows: bool = False) -> None:
         """gorch_cuda_sample_vocab_sharded_dev: device pointers; local pass, all-gather, merge.
-        rows_without_top_k: the batch may hold rows with top_k == 0 (gorch_cuda_sample_vocab_sharded_ex_dev:
-        the owners then draw from their slices and two small all-reduces hand the tokens round)."""
+        rows_without_top_k: the batch may hold rows with top_k == 0 and no effective top-p cut
+        (gorch_cuda_sample_vocab_sharded_ex_dev, bit 0: the owners then draw from their slices and two small
+        all-reduces hand the tokens round). gather_rows (bit 1): rows with top_k == 0 that this cannot
+        serve (an active top-p cut; every such row when rows_without_top_k is off) are sampled from
+        whole rows that an all-reduce brings to every rank: correct, not fast."""
         err = C.c_void_p()
-        if rows_without_top_k:
+        if rows_without_top_k or gather_rows:
+            mode = (1 if rows_without_top_k else 0) | (2 if gather_rows else 0)
             rc = self._lib.gorch_cuda_sample_vocab_sharded_ex_dev(self._ctx, logits_ptr, dtype, B, Vslice, row_stride,
-                                                                  col_offset, V, int(max_top_k), 1, cfgs_ptr, uniforms_ptr,
+                                                                  col_offset, V, int(max_top_k), mode, cfgs_ptr, uniforms_ptr,
                                                                   ids_ptr, flags_ptr, C.byref(err))
         else:
             rc = self._lib.gorch_cuda_sample_vocab_sharded_dev(self._ctx, logits_ptr, dtype, B, Vslice, row_stride,

@@ -240,10 +240,16 @@ int gorch_cuda_sample_vocab_sharded_dev(GorchCudaCtxRef ctx, const void* logits_
                                         int64_t Vslice, int64_t row_stride, int64_t col_offset, int64_t V,
                                         int max_top_k, const GorchSampleCfg* cfgs, const double* uniforms,
                                         int32_t* out_ids, uint32_t* out_flags, char** errOut);
-/* The same with rows_without_top_k != 0 for batches that hold rows with top_k == 0: after the
- * merge the owners draw from their slices and two small ncclAllReduce (max) calls, over out_ids
- * and out_flags (required here), hand the tokens to every rank. With rows_without_top_k == 0 it is
- * the call above. */
+/* The same for batches that hold rows with top_k == 0; rows_without_top_k is a set of bits, 0 being
+ * the call above. Bit 0: rows whose top-p cut removes nothing (off, or generate.go's rule with
+ * 1.5 p >= 1) are served from the slices' sums: after the merge the owners draw from their slices
+ * and two small ncclAllReduce (max) calls, over out_ids and out_flags, hand the tokens to every
+ * rank. Bit 1: the rows with top_k == 0 that are left (an active cut over the whole vocabulary:
+ * qwen/generate.go:123-153; with bit 0 clear every sampling row with top_k == 0) are sampled from
+ * whole rows: every rank's slice goes into a [B, V] scratch buffer, one ncclAllReduce (sum) fills
+ * in the others', and gorch_cuda_sample_dev's kernels take those rows on every rank. That is
+ * correct and not fast (B * V elements cross the links), and it needs scratch memory for B whole
+ * rows. out_flags is required with either bit. */
 int gorch_cuda_sample_vocab_sharded_ex_dev(GorchCudaCtxRef ctx, const void* logits_slice, int dtype, int64_t B,
                                            int64_t Vslice, int64_t row_stride, int64_t col_offset, int64_t V,
                                            int max_top_k, int rows_without_top_k, const GorchSampleCfg* cfgs,

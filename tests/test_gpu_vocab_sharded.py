@@ -128,7 +128,7 @@ def test_masked_slices(sampler, oracle, world):
     check(sampler, oracle, logits, cfgs, rng.random(B), world)
 
 
-def _fused_call(s, logits, cfgs, uniforms, max_top_k, rows_without_top_k=False):
+def _fused_call(s, logits, cfgs, uniforms, max_top_k, rows_without_top_k=False, gather_rows=False):
     """gorch_cuda_sample_vocab_sharded_dev on this process's one rank (device buffers of the library)."""
     from gorch_b200.config import DTYPE_BF16, DTYPE_F32
     B, V = logits.shape
@@ -144,7 +144,7 @@ def _fused_call(s, logits, cfgs, uniforms, max_top_k, rows_without_top_k=False):
         s._upload(b_log, np.ascontiguousarray(logits)); s._upload(b_cfg, cfgs); s._upload(b_uni, uniforms)
         ptr = lib.gorch_cuda_buffer_device_ptr
         s.sample_vocab_sharded_ptrs(ptr(b_log), code, B, V, V, 0, V, max_top_k, ptr(b_cfg), ptr(b_uni), ptr(b_ids), ptr(b_flg),
-                                    rows_without_top_k=rows_without_top_k)
+                                    rows_without_top_k=rows_without_top_k, gather_rows=gather_rows)
         s.sync()
         ids = np.empty(B, dtype=np.int32); flags = np.empty(B, dtype=np.uint32)
         s._download(b_ids, ids); s._download(b_flg, flags)
@@ -182,6 +182,17 @@ def test_collective_inside_the_library_one_rank(_sampler_session, oracle):
         check_ids(oracle, x, cf, uu, ids, flags)
         ids, flags = _fused_call(s, x, cf, uu, 40)               # without the flag such rows are refused, the others served
         assert np.all(ids[0::2] == -1) and np.all(ids[1::2] >= 0)
+        # rows without top-k whose top-p cut is active: from whole rows, gathered by an all-reduce
+        for i in range(40):
+            cf[i] = [(1.0, 0, 0.9, 1), (0.8, 40, 0.0, 0), (0.7, 0, 0.5, 0), (0.0, 0, 0.0, 0), (1.3, 0, 0.0, 0)][i % 5]
+        for owner in (True, False):
+            ids, flags = _fused_call(s, x, cf, uu, 40, rows_without_top_k=owner, gather_rows=True)
+            check_ids(oracle, x, cf, uu, ids, flags)
+        xb = workloads.f32_to_bf16_bits(x[:, :30008])            # bf16 rows, a width that is a multiple of 8
+        ids, flags = _fused_call(s, xb, cf, uu, 40, rows_without_top_k=True, gather_rows=True)
+        check_ids(oracle, xb, cf, uu, ids, flags)
+        ids, flags = _fused_call(s, x, cf, uu, 40, rows_without_top_k=True)   # without it the rows with a cut are refused
+        assert np.all(ids[0::5] == -1) and np.all(ids[2::5] == -1) and np.all(ids[1::5] >= 0) and np.all(ids[4::5] >= 0)
         # timing of the phases
         s.set_timing(True)
         _fused_call(s, w.logits, w.cfgs, w.uniforms, 64)
