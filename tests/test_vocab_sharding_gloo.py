@@ -57,3 +57,43 @@ def test_slice_width_is_checked():
     logits, cfgs, uniforms = _case(2, 10)
     with pytest.raises(ValueError):
         sample_vocab_sharded(StandInSampler(), logits[:, :4], cfgs, uniforms, 10, 0, 2)
+
+
+class _RecordingLib:
+    """Stands in for libgorchcuda.so in the two vocab-sharded entry points: records the call."""
+    def __init__(self):
+        self.calls = []
+
+    def gorch_cuda_sample_vocab_sharded_dev(self, ctx, logits, dtype, B, Vslice, stride, off, V, max_k, cfgs, uni, ids, flags, err):
+        self.calls.append(("plain", B, Vslice, stride, off, V, max_k, None))
+        return 0
+
+    def gorch_cuda_sample_vocab_sharded_ex_dev(self, ctx, logits, dtype, B, Vslice, stride, off, V, max_k, bits, cfgs, uni, ids, flags, err):
+        self.calls.append(("ex", B, Vslice, stride, off, V, max_k, bits))
+        return 0
+
+
+def test_device_form_passes_the_slice_and_the_bits_for_rows_without_top_k():
+    """The host side of the device-resident call: this rank's column range, and which of the two
+    ways of serving rows without top-k the caller asked for (bit 0: the owner's draw, bit 1: whole
+    rows gathered), reach the C ABI unchanged."""
+    import torch
+    from gorch_b200.distributed import sample_vocab_sharded_device
+    from gorch_b200.sampling import CudaSampler
+    from gorch_b200 import workloads
+    s = object.__new__(CudaSampler)                    # no GPU here: only the argument plumbing runs
+    s._lib, s._ctx = _RecordingLib(), None
+    B, V, world = 3, 1001, 4
+    for rank in range(world):
+        lo, hi = workloads.shard_vocab(V, rank, world)
+        d = torch.zeros(B, hi - lo)
+        cf, u = torch.zeros(B, 16, dtype=torch.uint8), torch.zeros(B, dtype=torch.float64)
+        ids, fl = torch.zeros(B, dtype=torch.int32), torch.zeros(B, dtype=torch.int32)
+        for owner, gather, want in [(False, False, None), (True, False, 1), (False, True, 2), (True, True, 3)]:
+            sample_vocab_sharded_device(s, d, cf, u, ids, fl, V, rank, world, max_top_k=40,
+                                        rows_without_top_k=owner, gather_rows=gather)
+            kind, b, vs, stride, off, v, k, bits = s._lib.calls[-1]
+            assert (b, vs, stride, off, v, k) == (B, hi - lo, hi - lo, lo, V, 40)
+            assert (kind, bits) == (("plain", None) if want is None else ("ex", want))
+    with pytest.raises(ValueError):
+        sample_vocab_sharded_device(s, torch.zeros(B, 5), cf, u, ids, fl, V, 0, world)
